@@ -1,0 +1,133 @@
+/*
+ * nvk.h -- C ABI of the B200 (sm_100a) attention / paged-KV kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its work on the given
+ * CUDA stream of the CURRENT device and returns without synchronising.  Unless stated
+ * otherwise no entry point allocates, frees, synchronises or reads device data on the host, so
+ * all of them may be recorded into a CUDA graph.  Device-side behaviour on bad data follows the
+ * reference: invalid slots are skipped, empty contexts produce zero rows, block-table entries
+ * beyond ceil(len / block_size) are never dereferenced (and ids outside the cache read as 0).
+ *
+ * Return value: NVK_OK, or an error code; nvk_last_error() then returns a thread-local
+ * message.  The C++ operator layer maps NVK_ERR_INVALID_ARGUMENT / NVK_ERR_UNSUPPORTED to
+ * std::invalid_argument and NVK_ERR_CUDA to std::runtime_error, which is the reference's
+ * error convention (src/kernels/kvcache.cu:160-178, src/utils/cuda_common.cpp:39-43).
+ *
+ * dtype codes follow the reference's ScalarType order (include/utils/tensor.h:21-28).
+ * The stream argument is a cudaStream_t passed as void* (NULL = legacy default stream).
+ */
+#ifndef NVK_H
+#define NVK_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVK_OK 0
+#define NVK_ERR_INVALID_ARGUMENT 1
+#define NVK_ERR_CUDA 2
+#define NVK_ERR_UNSUPPORTED 3
+
+#define NVK_F16 0
+#define NVK_BF16 1
+#define NVK_F32 2
+#define NVK_I32 3
+#define NVK_I64 4
+#define NVK_I8 5
+
+/* ABI revision of this header. */
+int nvk_abi_version(void);
+
+/* Message of the last failing call made by the calling thread ("" if none). */
+const char* nvk_last_error(void);
+
+/*
+ * Replaces nano_vllm::store_kvcache (include/kernels/kvcache.h:7-12; kernels
+ * src/kernels/kvcache.cu:19-47 and :53-80).
+ *   key, value        [num_tokens, row_elems] contiguous, `dtype` in {F16, BF16, F32}
+ *   k_cache, v_cache  [cache_rows, row_elems], same dtype
+ *   slot_mapping      [num_tokens] of `slot_dtype` in {I32, I64}
+ * cache row slot_mapping[t] receives row t; rows with slot < 0 or slot >= cache_rows are
+ * skipped.  Pure byte copy (bit-exact).  num_tokens must be >= 1 (the reference throws on an
+ * empty slot_mapping, kvcache.cu:164-167).
+ */
+int nvk_store_kvcache(const void* key, const void* value, void* k_cache, void* v_cache,
+                      const void* slot_mapping, int slot_dtype, int64_t num_tokens,
+                      int64_t row_elems, int64_t cache_rows, int dtype, void* stream);
+
+/*
+ * Replaces nano_vllm::fused_split_norm_rope_store (include/kernels/split_qkv.h:22-33; kernel
+ * src/kernels/split_qkv.cu:62-154): split packed qkv rows, per-head RMSNorm of q and k
+ * (fp32, eps inside the rsqrt, weight in model dtype), neox RoPE from the fp32 table
+ * cos_sin_cache [max_positions, head_dim] = [cos | sin] (rows outside [0, max_positions) stay
+ * un-rotated), q -> q_out [rows, Hq, D], k and v -> cache row slot_mapping[row] when that slot
+ * is >= 0 (and < cache_rows: the reference checks only the lower bound, writing out of bounds
+ * otherwise).  dtype in {F16, BF16}; positions and slot_mapping are int32.
+ */
+int nvk_fused_split_norm_rope_store(const void* qkv, const int32_t* positions,
+                                    const void* q_norm_weight, const void* k_norm_weight,
+                                    float norm_eps, const float* cos_sin_cache,
+                                    int64_t max_positions, const int32_t* slot_mapping,
+                                    void* k_cache, void* v_cache, int64_t cache_rows,
+                                    int64_t rows, int num_q_heads, int num_kv_heads,
+                                    int head_dim, void* q_out, int dtype, void* stream);
+
+/*
+ * Scratch size for nvk_decode_attention_paged (split-K partial results).  Depends only on
+ * host-known sizes, never on context_lens, so the value is stable across graph replays.
+ */
+size_t nvk_decode_attention_workspace_bytes(int64_t batch, int num_heads, int num_kv_heads,
+                                            int head_dim, int64_t max_blocks, int block_size);
+
+/*
+ * Replaces nano_vllm::launch_decode_attention_paged (include/kernels/attention.h:31-41; kernel
+ * src/kernels/attention.cu:313-405) and flash_attn_decode_kvcache
+ * (include/kernels/flash_attn.h:39-50).
+ *   query, output   [batch, num_heads, head_dim]
+ *   k_cache,v_cache [num_cache_blocks, block_size, num_kv_heads, head_dim]
+ *   context_lens    [batch] int32 (includes the token being generated)
+ *   block_tables    [batch, max_blocks] int32, zero padded
+ *   out[b,h] = softmax(scale * q[b,h] . K[b, h*Hkv/Hq]^T) V over context_lens[b] keys; key k of
+ *   sequence b lives in cache row block_tables[b][k / block_size] * block_size + k % block_size.
+ *   context_lens[b] <= 0 gives a zero row.
+ * workspace may be NULL (then every sequence is processed by one thread block per KV head);
+ * otherwise it must hold nvk_decode_attention_workspace_bytes(...) bytes, 16-byte aligned.
+ * dtype F16/BF16 with head_dim 128 take the tensor-core path; other shapes and F32 take the
+ * general SIMT path.
+ */
+int nvk_decode_attention_paged(const void* query, const void* k_cache, const void* v_cache,
+                               const int32_t* context_lens, const int32_t* block_tables,
+                               int64_t batch, int64_t max_blocks, int64_t num_cache_blocks,
+                               int num_heads, int num_kv_heads, int head_dim, int block_size,
+                               float scale, void* output, int dtype, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+/*
+ * Replaces nano_vllm::launch_prefill_attention_dense / launch_prefill_attention_paged
+ * (include/kernels/attention.h:7-29; kernels src/kernels/attention.cu:114-202 and :205-302)
+ * and flash_attn_varlen_fwd (include/kernels/flash_attn.h:15-26).
+ *   query, output  [total_q, num_heads, head_dim]
+ *   dense keys:    key, value [total_k, num_kv_heads, head_dim], block_tables == NULL
+ *   paged keys:    k_cache, v_cache [num_cache_blocks, block_size, num_kv_heads, head_dim] and
+ *                  block_tables [num_seqs, max_blocks] int32; key/value ignored
+ *   cu_seqlens_q, cu_seqlens_k  [num_seqs + 1] int32; both NULL (dense only) = one sequence
+ * Causal mask, bottom-right aligned: query i of a sequence sees keys
+ * 0 .. (k_len - q_len) + i  (attention.cu:147, :244); rows with no visible key are zero.
+ * max_seqlen_q may be 0 when unknown.
+ */
+int nvk_prefill_attention_varlen(const void* query, const void* key, const void* value,
+                                 const void* k_cache, const void* v_cache,
+                                 const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                 const int32_t* block_tables, int64_t num_seqs, int64_t total_q,
+                                 int64_t total_k, int64_t max_blocks, int64_t num_cache_blocks,
+                                 int max_seqlen_q, int num_heads, int num_kv_heads, int head_dim,
+                                 int block_size, float scale, void* output, int dtype,
+                                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVK_H */

@@ -1,0 +1,204 @@
+"""Python test/bench driver over the C ABI of ``libnvk.so`` (``include/nvk.h``).
+
+The product is the shared library; this module only loads it with ``ctypes`` and passes raw
+device pointers of torch tensors (torch is plumbing: device memory and streams).  The function
+names and argument order mirror the reference's operator API
+(include/kernels/kvcache.h:7-12, include/kernels/attention.h:7-41,
+include/kernels/split_qkv.h:22-33).  There is no fallback: if the CUDA library is missing or a
+call fails, an exception is raised (``ValueError`` for invalid arguments, ``RuntimeError`` for
+CUDA errors -- the reference throws std::invalid_argument / std::runtime_error).
+
+The directory name contains a hyphen, so import it with :func:`load_package` from
+``__graft_entry__`` (or ``importlib``) rather than with an ``import`` statement.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libnvk.so")
+
+F16, BF16, F32, I32, I64, I8 = 0, 1, 2, 3, 4, 5
+OK, ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_UNSUPPORTED = 0, 1, 2, 3
+
+EXPORTED_SYMBOLS = (
+    "nvk_abi_version", "nvk_last_error", "nvk_store_kvcache", "nvk_fused_split_norm_rope_store",
+    "nvk_decode_attention_workspace_bytes", "nvk_decode_attention_paged",
+    "nvk_prefill_attention_varlen",
+)
+
+_lib = None
+launch_count = 0  # kernels launched through this module (claimed by the benchmark)
+
+
+class NvkLibraryMissing(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """Loads ``libnvk.so``; raises if it has not been built (no CPU or library fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NvkLibraryMissing(
+                f"{LIB_PATH} not found: build it with `python nano-vllm-cpp_b200/build.py` "
+                "(or __graft_entry__.build()); there is no fallback path")
+        L = ctypes.CDLL(LIB_PATH)
+        L.nvk_last_error.restype = ctypes.c_char_p
+        L.nvk_abi_version.restype = ctypes.c_int
+        L.nvk_decode_attention_workspace_bytes.restype = ctypes.c_size_t
+        L.nvk_decode_attention_workspace_bytes.argtypes = [
+            ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int]
+        _lib = L
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc == OK:
+        return
+    msg = lib().nvk_last_error().decode()
+    if rc in (ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def _dtype_code(t) -> int:
+    import torch
+    return {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, torch.int32: I32,
+            torch.int64: I64, torch.int8: I8}[t.dtype]
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(name, t):
+    if t is None:
+        raise ValueError(f"{name} must be defined")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must live on CUDA")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def store_kvcache(key, value, k_cache, v_cache, slot_mapping) -> None:
+    """``store_kvcache`` (include/kernels/kvcache.h:7-12): in-place scatter into the paged cache."""
+    global launch_count
+    for n, t in (("key", key), ("value", value), ("k_cache", k_cache), ("v_cache", v_cache),
+                 ("slot_mapping", slot_mapping)):
+        _require_cuda(n, t)
+    if not (key.dtype == value.dtype == k_cache.dtype == v_cache.dtype):
+        raise ValueError("key and value must have the same dtype")
+    n = slot_mapping.numel()
+    if n <= 0:
+        raise ValueError("slot_mapping must contain at least one element")
+    if key.numel() % n or key.numel() != value.numel():
+        raise ValueError("key cannot be flattened by the provided leading count")
+    row = key.numel() // n
+    if k_cache.numel() % row or k_cache.numel() != v_cache.numel():
+        raise ValueError("k_cache does not contain an integer number of cache rows")
+    _check(lib().nvk_store_kvcache(
+        _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping),
+        ctypes.c_int(_dtype_code(slot_mapping)), ctypes.c_int64(n), ctypes.c_int64(row),
+        ctypes.c_int64(k_cache.numel() // row), ctypes.c_int(_dtype_code(key)), _stream()))
+    launch_count += 1
+
+
+def fused_split_norm_rope_store(qkv, positions, q_norm_weight, k_norm_weight, norm_eps, cos_sin_cache,
+                                slot_mapping, k_cache, v_cache, num_q_heads, num_kv_heads, head_dim,
+                                q_out) -> None:
+    """``fused_split_norm_rope_store`` (include/kernels/split_qkv.h:22-33)."""
+    global launch_count
+    for n, t in (("qkv", qkv), ("positions", positions), ("q_norm_weight", q_norm_weight),
+                 ("k_norm_weight", k_norm_weight), ("cos_sin_cache", cos_sin_cache),
+                 ("slot_mapping", slot_mapping), ("k_cache", k_cache), ("v_cache", v_cache), ("q_out", q_out)):
+        _require_cuda(n, t)
+    row = num_kv_heads * head_dim
+    _check(lib().nvk_fused_split_norm_rope_store(
+        _ptr(qkv), _ptr(positions), _ptr(q_norm_weight), _ptr(k_norm_weight), ctypes.c_float(norm_eps),
+        _ptr(cos_sin_cache), ctypes.c_int64(cos_sin_cache.shape[0]), _ptr(slot_mapping), _ptr(k_cache),
+        _ptr(v_cache), ctypes.c_int64(k_cache.numel() // row), ctypes.c_int64(qkv.shape[0]),
+        ctypes.c_int(num_q_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim), _ptr(q_out),
+        ctypes.c_int(_dtype_code(qkv)), _stream()))
+    launch_count += 1
+
+
+def decode_attention_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size) -> int:
+    return int(lib().nvk_decode_attention_workspace_bytes(batch, num_heads, num_kv_heads, head_dim,
+                                                          max_blocks, block_size))
+
+
+def launch_decode_attention_paged(query, k_cache, v_cache, context_lens, block_tables, num_kv_heads,
+                                  head_dim, block_size, scale, output, workspace=None) -> None:
+    """``launch_decode_attention_paged`` (include/kernels/attention.h:31-41).
+
+    ``workspace`` (a uint8 CUDA tensor of ``decode_attention_workspace_bytes`` bytes) plays the role
+    of the allocator argument of ``flash_attn_decode_kvcache`` (include/kernels/flash_attn.h:39-50).
+    """
+    global launch_count
+    for n, t in (("query", query), ("k_cache", k_cache), ("v_cache", v_cache),
+                 ("context_lens", context_lens), ("block_tables", block_tables), ("output", output)):
+        _require_cuda(n, t)
+    if context_lens.dtype.itemsize != 4 or block_tables.dtype.itemsize != 4:
+        raise ValueError("context_lens and block_tables must be int32")
+    batch, num_heads = query.shape[0], query.shape[1]
+    num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
+    _check(lib().nvk_decode_attention_paged(
+        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(context_lens), _ptr(block_tables),
+        ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
+        ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
+        ctypes.c_int(block_size), ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)),
+        _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size() if workspace is not None else 0),
+        _stream()))
+    ws_need = decode_attention_workspace_bytes(batch, num_heads, num_kv_heads, head_dim,
+                                               block_tables.shape[1], block_size)
+    launch_count += 2 if (workspace is not None and ws_need > 0) else 1
+
+
+def _prefill(query, key, value, k_cache, v_cache, cu_q, cu_k, block_tables, num_kv_heads, head_dim,
+             block_size, scale, output, max_seqlen_q=0) -> None:
+    global launch_count
+    _require_cuda("query", query)
+    _require_cuda("output", output)
+    num_seqs = (cu_q.numel() - 1) if cu_q is not None else 1
+    total_k = key.shape[0] if key is not None else 0
+    max_blocks = block_tables.shape[1] if block_tables is not None else 0
+    ncb = (k_cache.numel() // (block_size * num_kv_heads * head_dim)) if k_cache is not None else 0
+    for t in (cu_q, cu_k, block_tables):
+        if t is not None and t.dtype.itemsize != 4:
+            raise ValueError("cu_seqlens and block_tables must be int32")
+    _check(lib().nvk_prefill_attention_varlen(
+        _ptr(query), _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(cu_q), _ptr(cu_k),
+        _ptr(block_tables), ctypes.c_int64(num_seqs), ctypes.c_int64(query.shape[0]), ctypes.c_int64(total_k),
+        ctypes.c_int64(max_blocks), ctypes.c_int64(ncb), ctypes.c_int(max_seqlen_q),
+        ctypes.c_int(query.shape[1]), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
+        ctypes.c_int(block_size), ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)),
+        _stream()))
+    launch_count += 1
+
+
+def launch_prefill_attention_dense(query, cu_seqlens_q, key, value, cu_seqlens_k, num_kv_heads, head_dim,
+                                   scale, output) -> None:
+    """``launch_prefill_attention_dense`` (include/kernels/attention.h:7-16)."""
+    _require_cuda("key", key)
+    _require_cuda("value", value)
+    _prefill(query, key, value, None, None, cu_seqlens_q, cu_seqlens_k, None, num_kv_heads, head_dim, 1,
+             scale, output)
+
+
+def launch_prefill_attention_paged(query, cu_seqlens_q, k_cache, v_cache, cu_seqlens_k, block_tables,
+                                   num_kv_heads, head_dim, block_size, scale, output) -> None:
+    """``launch_prefill_attention_paged`` (include/kernels/attention.h:18-29)."""
+    if cu_seqlens_q is None or cu_seqlens_k is None:
+        raise ValueError("paged prefill attention requires cu_seqlens_q and cu_seqlens_k")
+    _require_cuda("k_cache", k_cache)
+    _require_cuda("v_cache", v_cache)
+    _require_cuda("block_tables", block_tables)
+    _prefill(query, None, None, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables, num_kv_heads,
+             head_dim, block_size, scale, output)

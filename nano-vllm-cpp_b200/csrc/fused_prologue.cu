@@ -1,0 +1,122 @@
+// Decode prologue for sm_100a: split packed qkv rows, RMSNorm + neox RoPE on the q and k heads,
+// q -> q_out, k / v -> paged cache rows.
+//
+// Replaces fused_split_norm_rope_store_kernel (src/kernels/split_qkv.cu:62-154 of the
+// reference: a 128-thread block per (row, head), one element per thread, a block reduction and a
+// shared-memory exchange per head).  Here one WARP owns one (row, head): each lane holds D/32
+// contiguous elements (one 4/8/16-byte load), the sum of squares is a shuffle reduction and the
+// rotation partner (d +- D/2) lives in lane ^ 16, so there is no shared memory and no barrier.
+// HBM-bound: rows * (Hq + 2 Hkv) * D elements read, the same number written.
+#include "nvk_internal.cuh"
+
+namespace nvk {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+template <int V> struct VecOf;
+template <> struct VecOf<2> { using type = uint32_t; };
+template <> struct VecOf<4> { using type = uint2; };
+template <> struct VecOf<8> { using type = uint4; };
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+fused_prologue_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ positions,
+                      const T* __restrict__ q_weight, const T* __restrict__ k_weight, float eps,
+                      const float* __restrict__ cos_sin, int max_positions,
+                      const int32_t* __restrict__ slot_mapping, T* __restrict__ k_cache,
+                      T* __restrict__ v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv,
+                      T* __restrict__ q_out) {
+    constexpr int D = V * 32;
+    using Vec = typename VecOf<V>::type;
+    const int lane = threadIdx.x & 31;
+    const int heads = hq + 2 * hkv;
+    const int64_t work = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (work >= rows * heads) return;
+    const int64_t row = work / heads;
+    const int head = static_cast<int>(work - row * heads);
+    const bool is_q = head < hq;
+    const bool is_k = !is_q && head < hq + hkv;
+
+    const T* src = qkv + (row * heads + head) * D + lane * V;
+    union { Vec v; T e[V]; } in, outv;
+    in.v = *reinterpret_cast<const Vec*>(src);
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + (row * hq + head) * D;
+    } else {
+        const int64_t slot = slot_mapping[row];
+        if (slot < 0 || slot >= cache_rows) return;   // whole warp leaves together
+        const int kv = is_k ? head - hq : head - hq - hkv;
+        dst = (is_k ? k_cache : v_cache) + (slot * hkv + kv) * D;
+    }
+
+    if (is_q || is_k) {
+        float x[V];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) { x[i] = ElemTraits<T>::to_float(in.e[i]); ss += x[i] * x[i]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv_rms = rsqrtf(ss / static_cast<float>(D) + eps);
+        const T* w = (is_q ? q_weight : k_weight) + lane * V;
+#pragma unroll
+        for (int i = 0; i < V; ++i) x[i] = x[i] * inv_rms * ElemTraits<T>::to_float(w[i]);
+        const int pos = positions[row];
+        const bool rotate = pos >= 0 && pos < max_positions;
+        const float* table = cos_sin + static_cast<int64_t>(rotate ? pos : 0) * D + (lane & 15) * V;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
+            if (rotate) {
+                const float c = table[i], s = table[i + D / 2];
+                x[i] = lane < 16 ? x[i] * c - partner * s : x[i] * c + partner * s;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) outv.e[i] = ElemTraits<T>::from_float(x[i]);
+    } else {
+        outv.v = in.v;   // v heads: plain copy
+    }
+    *reinterpret_cast<Vec*>(dst + lane * V) = outv.v;
+}
+
+template <typename T>
+int launch_typed(const void* qkv, const int32_t* positions, const void* qw, const void* kw, float eps,
+                 const float* cos_sin, int64_t max_positions, const int32_t* slot_mapping, void* k_cache,
+                 void* v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv, int d, void* q_out,
+                 cudaStream_t stream) {
+    const int64_t work = rows * (hq + 2 * hkv);
+    const int64_t blocks = (work + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    if (blocks > 0x7fffffffLL) return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: too many rows");
+    const dim3 grid(static_cast<unsigned>(blocks));
+#define NVK_LAUNCH(V)                                                                                          \
+    fused_prologue_kernel<T, V><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                                     \
+        static_cast<const T*>(qkv), positions, static_cast<const T*>(qw), static_cast<const T*>(kw), eps,     \
+        cos_sin, static_cast<int>(max_positions), slot_mapping, static_cast<T*>(k_cache),                      \
+        static_cast<T*>(v_cache), cache_rows, rows, hq, hkv, static_cast<T*>(q_out))
+    switch (d) {
+        case 64: NVK_LAUNCH(2); break;
+        case 128: NVK_LAUNCH(4); break;
+        case 256: NVK_LAUNCH(8); break;
+        default: return fail(NVK_ERR_UNSUPPORTED, "fused_split_norm_rope_store: head_dim must be 64, 128 or 256 (got %d)", d);
+    }
+#undef NVK_LAUNCH
+    return check_launch("fused_split_norm_rope_store kernel launch");
+}
+
+}  // namespace
+
+int launch_fused_prologue(const void* qkv, const int32_t* positions, const void* qw, const void* kw, float eps,
+                          const float* cos_sin, int64_t max_positions, const int32_t* slot_mapping,
+                          void* k_cache, void* v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv,
+                          int d, void* q_out, int dtype, cudaStream_t stream) {
+    if (dtype == NVK_BF16)
+        return launch_typed<__nv_bfloat16>(qkv, positions, qw, kw, eps, cos_sin, max_positions, slot_mapping,
+                                           k_cache, v_cache, cache_rows, rows, hq, hkv, d, q_out, stream);
+    return launch_typed<__half>(qkv, positions, qw, kw, eps, cos_sin, max_positions, slot_mapping, k_cache,
+                                v_cache, cache_rows, rows, hq, hkv, d, q_out, stream);
+}
+
+}  // namespace nvk

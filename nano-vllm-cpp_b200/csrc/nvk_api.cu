@@ -1,0 +1,151 @@
+// extern "C" entry points declared in include/nvk.h: argument validation (the checks the
+// reference performs in src/kernels/kvcache.cu:146-190, src/kernels/attention.cu:679-681 and
+// src/kernels/kernel_types.cu:24-110) and dispatch to the kernels of this library.
+#include "nvk_internal.cuh"
+
+#include <string>
+
+namespace nvk {
+
+namespace {
+thread_local std::string g_last_error;
+}
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e == cudaSuccess) return NVK_OK;
+    return fail(NVK_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+namespace {
+
+bool is_compute_dtype(int dtype) { return dtype == NVK_F16 || dtype == NVK_BF16 || dtype == NVK_F32; }
+
+}  // namespace
+}  // namespace nvk
+
+using namespace nvk;
+
+extern "C" {
+
+int nvk_abi_version(void) { return 1; }
+
+const char* nvk_last_error(void) { return g_last_error.c_str(); }
+
+int nvk_store_kvcache(const void* key, const void* value, void* k_cache, void* v_cache,
+                      const void* slot_mapping, int slot_dtype, int64_t num_tokens, int64_t row_elems,
+                      int64_t cache_rows, int dtype, void* stream) {
+    if (!key || !value || !k_cache || !v_cache || !slot_mapping)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache: key, value, k_cache, v_cache and slot_mapping must be defined");
+    if (!is_compute_dtype(dtype)) return fail(NVK_ERR_INVALID_ARGUMENT, "key must be float16, bfloat16, or float32");
+    if (slot_dtype != NVK_I32 && slot_dtype != NVK_I64)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "slot_mapping must be int32 or int64");
+    if (num_tokens <= 0) return fail(NVK_ERR_INVALID_ARGUMENT, "slot_mapping must contain at least one element");
+    if (row_elems <= 0) return fail(NVK_ERR_INVALID_ARGUMENT, "key cannot be flattened by the provided leading count");
+    if (cache_rows <= 0) return fail(NVK_ERR_INVALID_ARGUMENT, "k_cache does not contain an integer number of cache rows");
+    return launch_store_kvcache(key, value, k_cache, v_cache, slot_mapping, slot_dtype == NVK_I64, num_tokens,
+                                row_elems * static_cast<int64_t>(dtype_size(dtype)), cache_rows,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int nvk_fused_split_norm_rope_store(const void* qkv, const int32_t* positions, const void* q_norm_weight,
+                                    const void* k_norm_weight, float norm_eps, const float* cos_sin_cache,
+                                    int64_t max_positions, const int32_t* slot_mapping, void* k_cache,
+                                    void* v_cache, int64_t cache_rows, int64_t rows, int num_q_heads,
+                                    int num_kv_heads, int head_dim, void* q_out, int dtype, void* stream) {
+    if (dtype != NVK_F16 && dtype != NVK_BF16)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store only supports bf16/fp16");
+    if (!qkv || !positions || !q_norm_weight || !k_norm_weight || !cos_sin_cache || !slot_mapping || !k_cache ||
+        !v_cache || !q_out)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: all tensors must be defined");
+    if (rows < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || max_positions <= 0 || cache_rows <= 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: sizes must be positive");
+    if (rows == 0) return NVK_OK;
+    if (!aligned_to(qkv, 16) || !aligned_to(q_out, 16) || !aligned_to(k_cache, 16) || !aligned_to(v_cache, 16) ||
+        !aligned_to(q_norm_weight, 16) || !aligned_to(k_norm_weight, 16) || !aligned_to(cos_sin_cache, 4))
+        return fail(NVK_ERR_UNSUPPORTED, "fused_split_norm_rope_store: tensors must be 16-byte aligned");
+    return launch_fused_prologue(qkv, positions, q_norm_weight, k_norm_weight, norm_eps, cos_sin_cache,
+                                 max_positions, slot_mapping, k_cache, v_cache, cache_rows, rows, num_q_heads,
+                                 num_kv_heads, head_dim, q_out, dtype, static_cast<cudaStream_t>(stream));
+}
+
+size_t nvk_decode_attention_workspace_bytes(int64_t batch, int num_heads, int num_kv_heads, int head_dim,
+                                            int64_t max_blocks, int block_size) {
+    return decode_mma_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size);
+}
+
+int nvk_decode_attention_paged(const void* query, const void* k_cache, const void* v_cache,
+                               const int32_t* context_lens, const int32_t* block_tables, int64_t batch,
+                               int64_t max_blocks, int64_t num_cache_blocks, int num_heads, int num_kv_heads,
+                               int head_dim, int block_size, float scale, void* output, int dtype,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    if (!query || !k_cache || !v_cache || !context_lens || !block_tables || !output)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention requires KV cache, context_lens, and block_tables");
+    if (!is_compute_dtype(dtype)) return fail(NVK_ERR_INVALID_ARGUMENT, "unsupported dtype for decode_attention_paged");
+    if (batch < 0 || max_blocks <= 0 || num_cache_blocks <= 0 || num_heads <= 0 || num_kv_heads <= 0 ||
+        head_dim <= 0 || block_size <= 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "attention dimensions must be positive");
+    if (num_heads % num_kv_heads != 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
+    if (batch == 0) return NVK_OK;
+    DecodeArgs a{query, k_cache, v_cache, context_lens, block_tables, output, batch, max_blocks, num_cache_blocks,
+                 num_heads, num_kv_heads, head_dim, block_size, scale, dtype, workspace, workspace_bytes,
+                 static_cast<cudaStream_t>(stream)};
+    if (decode_mma_supported(a)) {
+        if (workspace != nullptr) {
+            const size_t need = decode_mma_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size);
+            if (workspace_bytes < need)
+                return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention: workspace of %zu bytes given, %zu needed",
+                            workspace_bytes, need);
+            if (!aligned_to(workspace, 16))
+                return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention: workspace must be 16-byte aligned");
+        }
+        return launch_decode_mma(a);
+    }
+    return launch_rowwise_decode(a);
+}
+
+int nvk_prefill_attention_varlen(const void* query, const void* key, const void* value, const void* k_cache,
+                                 const void* v_cache, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                 const int32_t* block_tables, int64_t num_seqs, int64_t total_q, int64_t total_k,
+                                 int64_t max_blocks, int64_t num_cache_blocks, int max_seqlen_q, int num_heads,
+                                 int num_kv_heads, int head_dim, int block_size, float scale, void* output,
+                                 int dtype, void* stream) {
+    if (!query || !output) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill attention: query and output must be defined");
+    if (!is_compute_dtype(dtype)) return fail(NVK_ERR_INVALID_ARGUMENT, "unsupported dtype for prefill attention");
+    if (num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || total_q < 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "attention dimensions must be positive");
+    if (num_heads % num_kv_heads != 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
+    const bool paged = block_tables != nullptr;
+    if (paged) {
+        if (!cu_seqlens_q || !cu_seqlens_k)
+            return fail(NVK_ERR_INVALID_ARGUMENT, "paged prefill attention requires cu_seqlens_q and cu_seqlens_k");
+        if (!k_cache || !v_cache) return fail(NVK_ERR_INVALID_ARGUMENT, "paged prefill attention requires k_cache and v_cache");
+        if (max_blocks <= 0 || num_cache_blocks <= 0 || block_size <= 0)
+            return fail(NVK_ERR_INVALID_ARGUMENT, "paged prefill attention: block sizes must be positive");
+    } else {
+        if (!key || !value) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill attention: key and value must be defined");
+        if (total_k < 0) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill attention: total_k must be non-negative");
+        if ((cu_seqlens_q == nullptr) != (cu_seqlens_k == nullptr)) { cu_seqlens_q = nullptr; cu_seqlens_k = nullptr; }
+    }
+    if (cu_seqlens_q && num_seqs <= 0) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill attention: num_seqs must be positive");
+    if (total_q == 0) return NVK_OK;
+    PrefillArgs a{query, key, value, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables, output, num_seqs,
+                  total_q, total_k, max_blocks, num_cache_blocks, max_seqlen_q, num_heads, num_kv_heads, head_dim,
+                  block_size, scale, dtype, static_cast<cudaStream_t>(stream)};
+    if (prefill_mma_supported(a)) return launch_prefill_mma(a);
+    return launch_rowwise_prefill(a);
+}
+
+}  // extern "C"
