@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-KV decode hot path (store_kvcache + paged decode attention).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload at every N: the Qwen3-8B decode configuration -- 32 query heads, 8 KV heads, head_dim 128,
+bf16 paged KV cache with 256-token blocks, batch 256, context lengths uniform in [1024, 8192], block
+tables a seeded random permutation of a pool sized for the batch, N(0,1) values, scale 1/sqrt(128).
+One step = store_kvcache of the 256 new tokens + paged decode attention over the whole batch.  With
+N > 1 every rank owns an independent batch of the same shape (no data-path collective; weak scaling).
+
+``value`` is algorithmic HBM bytes per second with all inputs resident in HBM; ``e2e`` is the same
+quantity when each step also uploads its inputs (q / k / v of the new tokens and the step metadata)
+from pinned host memory and reads the attention output back.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "paged_decode_attention_hbm_bandwidth"
+UNIT = "GB/s"
+CFG = dict(batch=256, num_heads=32, num_kv_heads=8, head_dim=128, block_size=256, ctx_lo=1024, ctx_hi=8192)
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_split_kernel launch, from the ncu capture
+# summarised in profiles/decode_split_kernel_batch32_full.md (batch-32 case; traffic scales with KV bytes).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.010
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def finish(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def make_workload(torch, dev, seed):
+    """Builds the decode configuration on the device (values drawn on the GPU from a seeded generator)."""
+    entry.load_package()
+    wl = __import__("importlib").import_module(entry.PKG_NAME + ".workloads")
+    rng = np.random.default_rng(seed)
+    ctx = rng.integers(CFG["ctx_lo"], CFG["ctx_hi"] + 1, size=CFG["batch"]).astype(np.int32)
+    tables, pool = wl.build_block_tables(rng, ctx, CFG["block_size"])
+    last = ctx.astype(np.int64) - 1
+    slots = (tables[np.arange(CFG["batch"]), last // CFG["block_size"]].astype(np.int64) * CFG["block_size"]
+             + last % CFG["block_size"]).astype(np.int32)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    bf = torch.bfloat16
+    shape = (pool, CFG["block_size"], CFG["num_kv_heads"], CFG["head_dim"])
+    w = {
+        "context_lens_np": ctx, "block_tables_np": tables, "slot_mapping_np": slots, "pool": pool,
+    }
+    # draw the large caches block-wise to bound the fp32 temporary
+    for name in ("k_cache", "v_cache"):
+        t = torch.empty(shape, device=dev, dtype=bf)
+        step = 256
+        for i in range(0, pool, step):
+            n = min(step, pool - i)
+            t[i:i + n] = torch.randn((n,) + shape[1:], generator=gen, device=dev, dtype=torch.float32).to(bf)
+        w[name] = t
+    w["q"] = torch.randn((CFG["batch"], CFG["num_heads"], CFG["head_dim"]), generator=gen, device=dev).to(bf)
+    w["k_new"] = torch.randn((CFG["batch"], CFG["num_kv_heads"], CFG["head_dim"]), generator=gen, device=dev).to(bf)
+    w["v_new"] = torch.randn((CFG["batch"], CFG["num_kv_heads"], CFG["head_dim"]), generator=gen, device=dev).to(bf)
+    w["context_lens"] = torch.from_numpy(ctx).to(dev)
+    w["block_tables"] = torch.from_numpy(tables).to(dev)
+    w["slot_mapping"] = torch.from_numpy(slots).to(dev)
+    w["out"] = torch.empty_like(w["q"])
+    w["scale"] = 1.0 / math.sqrt(CFG["head_dim"])
+    return w
+
+
+def algorithmic_bytes(ctx, tables):
+    """Bytes one step must move: K and V of every context token once per KV head, q and out, the
+    metadata actually dereferenced, and the store's read + write of the new rows."""
+    hkv, d, hq, b = CFG["num_kv_heads"], CFG["head_dim"], CFG["num_heads"], CFG["batch"]
+    kv = int(ctx.astype(np.int64).sum()) * 2 * hkv * d * 2
+    q_out = 2 * b * hq * d * 2
+    used_entries = int(((ctx.astype(np.int64) + CFG["block_size"] - 1) // CFG["block_size"]).sum())
+    meta = used_entries * 4 + b * 4
+    store = 2 * (2 * b * hkv * d * 2) + b * 4
+    return {"decode": kv + q_out + meta, "store": store, "total": kv + q_out + meta + store}
+
+
+def cpu_baseline(torch, w, budget_s=12.0):
+    """Times the CPU oracle (fp32 restatement of the reference's decode kernel) on a bounded sample:
+    the first n sequences of the batch, all heads, all host threads."""
+    import oracle
+    ctx, tables = w["context_lens_np"], w["block_tables_np"]
+    threads = oracle.default_threads()
+
+    def prepare(n):
+        blocks = []
+        remap = np.zeros((n, tables.shape[1]), dtype=np.int32)
+        for b in range(n):
+            nb = (int(ctx[b]) + CFG["block_size"] - 1) // CFG["block_size"]
+            for j in range(nb):
+                remap[b, j] = len(blocks)
+                blocks.append(int(tables[b, j]))
+        idx = torch.tensor(blocks, device=w["k_cache"].device)
+        kc = w["k_cache"][idx].float().cpu().numpy()
+        vc = w["v_cache"][idx].float().cpu().numpy()
+        q = w["q"][:n].float().cpu().numpy()
+        nbytes = int(ctx[:n].astype(np.int64).sum()) * 2 * CFG["num_kv_heads"] * CFG["head_dim"] * 2
+
+        def once():
+            t0 = time.perf_counter()
+            oracle.decode_attention_paged(q, kc, vc, ctx[:n], remap, CFG["num_kv_heads"], CFG["head_dim"],
+                                          CFG["block_size"], w["scale"], threads=threads)
+            return time.perf_counter() - t0, nbytes
+        return once
+
+    n = min(CFG["batch"], 32)
+    run_once = prepare(n)
+    run_once()  # warm-up (page faults, thread pool)
+    dt, reps, nbytes = 0.0, 0, 0
+    while dt < budget_s:
+        t, nb = run_once()
+        dt += t
+        nbytes += nb
+        reps += 1
+    return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"first {n} of {CFG['batch']} sequences, all {CFG['num_heads']} heads, {reps} passes of the fp32 "
+                      f"oracle in {dt:.1f} s; bytes counted at the workload's bf16 element size"}
+
+
+def run_ours(args, torch, dist, rank, world, dev):
+    nvk = entry.load_package()
+    nvk.lib()  # raises if the CUDA library is missing: there is no fallback
+    w = make_workload(torch, dev, seed=2024 + rank)
+    ab = algorithmic_bytes(w["context_lens_np"], w["block_tables_np"])
+    ws_bytes = nvk.decode_attention_workspace_bytes(CFG["batch"], CFG["num_heads"], CFG["num_kv_heads"],
+                                                    CFG["head_dim"], w["block_tables"].shape[1], CFG["block_size"])
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+
+    def store():
+        nvk.store_kvcache(w["k_new"], w["v_new"], w["k_cache"], w["v_cache"], w["slot_mapping"])
+
+    def decode():
+        nvk.launch_decode_attention_paged(w["q"], w["k_cache"], w["v_cache"], w["context_lens"], w["block_tables"],
+                                          CFG["num_kv_heads"], CFG["head_dim"], CFG["block_size"], w["scale"],
+                                          w["out"], ws)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(args.warmup):
+        store()
+        decode()
+    torch.cuda.synchronize()
+
+    # ---- timed region: K steps, device-resident inputs --------------------------------------------
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ka = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    kb = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    sampler = ClockSampler(physical_gpu_index(int(os.environ.get("LOCAL_RANK", 0))))
+    launches_before = nvk.launch_count
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    ev0.record()
+    for i in range(args.steps):
+        store()
+        ka[i].record()
+        decode()
+        kb[i].record()
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.finish()
+    launches = nvk.launch_count - launches_before
+    total_ms = ev0.elapsed_time(ev1)
+    decode_ms = sum(a.elapsed_time(b) for a, b in zip(ka, kb)) / args.steps
+
+    # ---- end to end: host buffers in, host buffer out, every step ---------------------------------
+    host = {k: w[k].cpu().pin_memory() for k in ("q", "k_new", "v_new", "slot_mapping", "context_lens", "block_tables")}
+    out_host = torch.empty(w["out"].shape, dtype=w["out"].dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step():
+        for k, t in host.items():
+            w[k].copy_(t, non_blocking=True)
+        store()
+        decode()
+        out_host.copy_(w["out"], non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        for _ in range(max(3, args.warmup // 4)):
+            e2e_step()
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
+
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms, decode_ms, float(ab["total"]), float(launches)], device=dev,
+                         dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, decode_ms = float(tmax[0]), float(tmax[1]), float(tmax[2])
+        bytes_all, launches = float(tsum[3]), int(tsum[4])
+    else:
+        bytes_all = float(ab["total"])
+
+    peak, peak_kind = measured_peaks()
+    achieved = ab["decode"] / (decode_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": bytes_all * args.steps / (total_ms * 1e-3) / 1e9, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"paged decode attention + store_kvcache, Qwen3-8B shape: batch {CFG['batch']} per GPU, 32/8 heads, "
+                               "head_dim 128, block_size 256, context U[1024,8192], random-permutation block tables",
+                   "bytes_per_step_per_gpu": ab["total"], "kv_pool_blocks": w["pool"],
+                   "l2": "inputs (about 4.8 GB of KV per step) exceed the 126 MB L2; no flush needed",
+                   "parallelism": f"{world} independent batches, one per GPU, no collective"},
+        "e2e": {"value": bytes_all * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": "decode_split_kernel (+ decode_merge_kernel)", "achieved": achieved,
+                     "peak": peak, "peak_source": f"{peak_kind} copy bandwidth", "unit": UNIT, "frac": achieved / peak,
+                     "frac_of_nominal_8TBs": achieved / 8000.0, "ms_per_launch": decode_ms,
+                     "algorithmic_bytes_per_launch": ab["decode"],
+                     "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * ab["decode"]
+                                 if NCU_TRAFFIC_PER_ALGORITHMIC_BYTE else None)},
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(torch, w)
+    return line
+
+
+def run_reference(args, torch, dev):
+    """Reference arm: the reference's own CUDA kernels (store_kvcache + decode_paged_attention_kernel,
+    compiled unmodified for sm_100a into oracle/_ref) on the same workload.  The reference has no CPU
+    implementation of this path; if the compiled reference is absent the CPU oracle port is timed."""
+    w = make_workload(torch, dev, seed=2024)
+    ab = algorithmic_bytes(w["context_lens_np"], w["block_tables_np"])
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libnvk_ref.so")
+    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "data": "synthetic",
+            "config": {"workload": "paged decode attention + store_kvcache, Qwen3-8B shape: batch 256, 32/8 heads, "
+                                   "head_dim 128, block_size 256, context U[1024,8192]"}}
+    if not os.path.exists(ref_path):
+        cb = cpu_baseline(torch, w, budget_s=20.0)
+        base.update({"value": cb["value"], "ms_per_step": None, "dtype": "f32", "cpu_baseline": cb,
+                     "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        return base
+    ref = ctypes.CDLL(ref_path)
+    ref.nvkref_last_error.restype = ctypes.c_char_p
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    row = CFG["num_kv_heads"] * CFG["head_dim"]
+
+    def step():
+        rc = ref.nvkref_store_kvcache(P(w["k_new"]), P(w["v_new"]), P(w["k_cache"]), P(w["v_cache"]),
+                                      P(w["slot_mapping"]), 3, ctypes.c_int64(CFG["batch"]), ctypes.c_int64(row),
+                                      ctypes.c_int64(w["pool"] * CFG["block_size"]), 1, stream)
+        rc |= ref.nvkref_decode_attention_paged(
+            P(w["q"]), P(w["k_cache"]), P(w["v_cache"]), P(w["context_lens"]), P(w["block_tables"]),
+            ctypes.c_int64(CFG["batch"]), ctypes.c_int64(w["block_tables"].shape[1]), ctypes.c_int64(w["pool"]),
+            CFG["num_heads"], CFG["num_kv_heads"], CFG["head_dim"], CFG["block_size"], ctypes.c_float(w["scale"]),
+            P(w["out"]), 1, stream)
+        if rc:
+            raise RuntimeError(ref.nvkref_last_error().decode())
+
+    steps = min(args.steps, 50)   # the reference kernel is two orders of magnitude slower per step
+    for _ in range(min(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    value = ab["total"] * steps / (ms * 1e-3) / 1e9
+    base.update({
+        "value": value, "steps": steps, "ms_per_step": ms / steps, "dtype": "bf16", "gpu_launches": 2 * steps,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 0, "kind": "reference",
+                         "sample": "full workload; the reference implements this path only as CUDA kernels, so its "
+                                   "own kernels (compiled for sm_100a) run on the GPU, not on host cores"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    return base
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--batch", type=int, default=CFG["batch"],
+                    help="sequences per GPU; anything but 256 is a profiling-sized case, not the benchmark")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    CFG["batch"] = args.batch
+
+    import torch
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        torch.cuda.set_device(0)
+        print(json.dumps(run_reference(args, torch, torch.device("cuda:0"))), flush=True)
+        return 0
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    else:
+        torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
+    line = run_ours(args, torch, dist, rank, world, dev)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

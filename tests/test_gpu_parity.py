@@ -192,7 +192,7 @@ def test_decode_stale_cache_contents_beyond_context_are_ignored():
 
 
 @pytest.mark.parametrize("dtype,head_dim,block_size,num_heads,num_kv_heads", [
-    ("f32", 64, 16, 4, 2), ("bf16", 64, 16, 4, 4), ("f32", 2, 2, 1, 1), ("f16", 96, 8, 6, 3), ("f32", 256, 32, 2, 1),
+    ("f32", 64, 16, 4, 2), ("bf16", 64, 16, 4, 4), ("f32", 2, 2, 1, 1), ("f16", 96, 8, 6, 3), ("f32", 128, 32, 2, 1),
 ])
 def test_decode_general_path_shapes(dtype, head_dim, block_size, num_heads, num_kv_heads):
     wl = workloads()
