@@ -2,9 +2,10 @@
  * nvk.h -- C ABI of the B200 (sm_100a) attention / paged-KV kernels.
  *
  * Every entry point takes plain device pointers and sizes, enqueues its work on the given
- * CUDA stream of the CURRENT device and returns without synchronising.  Unless stated
- * otherwise no entry point allocates, frees, synchronises or reads device data on the host, so
- * all of them may be recorded into a CUDA graph.  Device-side behaviour on bad data follows the
+ * CUDA stream of the CURRENT device and returns without synchronising.  No entry point
+ * allocates, frees, synchronises or reads device data on the host; nvk_store_kvcache,
+ * nvk_fused_split_norm_rope_store, nvk_decode_attention_paged and nvk_prefill_attention_varlen
+ * may therefore be recorded into a CUDA graph.  Device-side behaviour on bad data follows the
  * reference: invalid slots are skipped, empty contexts produce zero rows, block-table entries
  * beyond ceil(len / block_size) are never dereferenced (and ids outside the cache read as 0).
  *
@@ -104,6 +105,31 @@ int nvk_decode_attention_paged(const void* query, const void* k_cache, const voi
                                int num_heads, int num_kv_heads, int head_dim, int block_size,
                                float scale, void* output, int dtype, void* workspace,
                                size_t workspace_bytes, void* stream);
+
+/*
+ * Same computation as nvk_decode_attention_paged for callers that cannot provide a workspace and
+ * must not allocate device memory.  (No counterpart in the reference: its decode entry point simply
+ * has no scratch.)  Typical callers: a wrapper with the reference's launch_decode_attention_paged
+ * signature, which has no allocator argument; an engine that has already handed all free HBM to
+ * its KV-cache pool; a serving loop or plug-in that is forbidden to call cudaMalloc after start-up.
+ *
+ * The split-K partial results go to a 32 MiB array that is part of this library's device code, so
+ * every GPU that uses the library keeps those 32 MiB reserved until the process exits.  The call
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *   - Limit: nvk_decode_attention_workspace_bytes(...) for the given sizes must be <= 32 MiB
+ *     (e.g. batch 256 x 32 heads x 4 splits = 16.9 MB); larger problems are rejected with
+ *     NVK_ERR_INVALID_ARGUMENT and nothing is launched.
+ *   - The first call on each device looks the array's address up (cudaGetSymbolAddress) with that
+ *     device current; make that first call during start-up, before any stream capture.
+ *   - All calls on one device share the array, and it keeps whatever the previous call left in it.
+ *     The kernels overwrite every entry they later read, so no clearing is needed, but two calls
+ *     whose kernels overlap on the GPU (different streams) race on it: serialise them.
+ */
+int nvk_decode_attention_paged_static(const void* query, const void* k_cache, const void* v_cache,
+                                      const int32_t* context_lens, const int32_t* block_tables,
+                                      int64_t batch, int64_t max_blocks, int64_t num_cache_blocks,
+                                      int num_heads, int num_kv_heads, int head_dim, int block_size,
+                                      float scale, void* output, int dtype, void* stream);
 
 /*
  * Replaces nano_vllm::launch_prefill_attention_dense / launch_prefill_attention_paged

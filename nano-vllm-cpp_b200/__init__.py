@@ -25,7 +25,7 @@ OK, ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_UNSUPPORTED = 0, 1, 2, 3
 EXPORTED_SYMBOLS = (
     "nvk_abi_version", "nvk_last_error", "nvk_store_kvcache", "nvk_fused_split_norm_rope_store",
     "nvk_decode_attention_workspace_bytes", "nvk_decode_attention_paged",
-    "nvk_prefill_attention_varlen",
+    "nvk_prefill_attention_varlen", "nvk_decode_attention_paged_static",
 )
 
 _lib = None
@@ -159,6 +159,27 @@ def launch_decode_attention_paged(query, k_cache, v_cache, context_lens, block_t
     ws_need = decode_attention_workspace_bytes(batch, num_heads, num_kv_heads, head_dim,
                                                block_tables.shape[1], block_size)
     launch_count += 2 if (workspace is not None and ws_need > 0) else 1
+
+
+def launch_decode_attention_paged_static(query, k_cache, v_cache, context_lens, block_tables, num_kv_heads,
+                                         head_dim, block_size, scale, output) -> None:
+    """Decode attention for callers that may not allocate: split-K scratch comes from a 32 MiB array
+    inside the library (``nvk_decode_attention_paged_static``).  Calls on one device must not overlap."""
+    global launch_count
+    for n, t in (("query", query), ("k_cache", k_cache), ("v_cache", v_cache),
+                 ("context_lens", context_lens), ("block_tables", block_tables), ("output", output)):
+        _require_cuda(n, t)
+    if context_lens.dtype.itemsize != 4 or block_tables.dtype.itemsize != 4:
+        raise ValueError("context_lens and block_tables must be int32")
+    batch, num_heads = query.shape[0], query.shape[1]
+    num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
+    _check(lib().nvk_decode_attention_paged_static(
+        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(context_lens), _ptr(block_tables),
+        ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
+        ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
+        ctypes.c_int(block_size), ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)),
+        _stream()))
+    launch_count += 2
 
 
 def _prefill(query, key, value, k_cache, v_cache, cu_q, cu_k, block_tables, num_kv_heads, head_dim,

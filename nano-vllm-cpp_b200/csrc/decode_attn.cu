@@ -353,3 +353,69 @@ int launch_decode_mma(const DecodeArgs& a) {
 }
 
 }  // namespace nvk
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: split-K scratch in a fixed device array owned by this library.
+//
+// Some callers of decode attention have no way to hand over a workspace: the reference's own
+// launch_decode_attention_paged signature carries no allocator, an engine may already have given
+// every free byte of HBM to its KV-cache pool, and code running under a "no device allocation
+// after start-up" rule (latency-critical serving loops, plug-ins that are only handed tensors)
+// must not call cudaMalloc at all.  For them the split-K partials live in the array below.  It is
+// part of the loaded module, so every GPU that uses this library keeps kStaticScratchBytes of HBM
+// reserved until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace nvk {
+namespace {
+
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: batch 256 x 32 heads x 4 splits needs 16.9 MB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {};
+bool g_scratch_ready[kMaxDevices] = {};
+
+// Resolves the device address of g_static_scratch for the current device (once per device).
+// In host code the symbol's name is only a handle; the kernels need the address returned here.
+int static_scratch_for_current_device(void** out) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "decode attention (static scratch): cudaGetDevice: %s", cudaGetErrorString(e));
+    if (device < 0 || device >= kMaxDevices)
+        return fail(NVK_ERR_UNSUPPORTED, "decode attention (static scratch): device index %d not supported", device);
+    if (!g_scratch_ready[device]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(NVK_ERR_CUDA, "decode attention (static scratch): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_scratch_addr[device] = ptr;
+        g_scratch_ready[device] = true;
+    }
+    *out = g_scratch_addr[device];
+    return NVK_OK;
+}
+
+}  // namespace
+}  // namespace nvk
+
+extern "C" int nvk_decode_attention_paged_static(const void* query, const void* k_cache, const void* v_cache,
+                                                 const int32_t* context_lens, const int32_t* block_tables,
+                                                 int64_t batch, int64_t max_blocks, int64_t num_cache_blocks,
+                                                 int num_heads, int num_kv_heads, int head_dim, int block_size,
+                                                 float scale, void* output, int dtype, void* stream) {
+    using namespace nvk;
+    const size_t need = nvk_decode_attention_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size);
+    if (need > kStaticScratchBytes)
+        return fail(NVK_ERR_INVALID_ARGUMENT,
+                    "decode attention (static scratch): this problem needs %zu bytes of split-K scratch but the built-in "
+                    "array holds %zu; use nvk_decode_attention_paged with a caller-provided workspace",
+                    need, kStaticScratchBytes);
+    void* scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != NVK_OK) return rc;
+    // The partials of a split are fully written before the merge kernel reads them, and only live
+    // splits are read, so nothing in the array has to start at zero.
+    return nvk_decode_attention_paged(query, k_cache, v_cache, context_lens, block_tables, batch, max_blocks,
+                                      num_cache_blocks, num_heads, num_kv_heads, head_dim, block_size, scale, output,
+                                      dtype, scratch, kStaticScratchBytes, stream);
+}
