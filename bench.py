@@ -375,6 +375,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue"],
+                    help="decode is the benchmark; the others time the remaining kernels of the path (1 GPU)")
+    ap.add_argument("--seqs", type=int, default=16, help="prefill workload: number of sequences")
+    ap.add_argument("--qmax", type=int, default=4096, help="prefill workload: longest new-token run")
     ap.add_argument("--batch", type=int, default=CFG["batch"],
                     help="sequences per GPU; anything but 256 is a profiling-sized case, not the benchmark")
     args = ap.parse_args()
@@ -391,6 +395,24 @@ def main():
             return 0
         torch.cuda.set_device(0)
         print(json.dumps(run_reference(args, torch, torch.device("cuda:0"))), flush=True)
+        return 0
+
+    if args.workload != "decode":
+        if rank != 0:
+            return 0
+        torch.cuda.set_device(local_rank)
+        nvk = entry.load_package()
+        nvk.lib()
+        kb = __import__("importlib").import_module(entry.PKG_NAME + ".kernel_bench")
+        dev = torch.device(f"cuda:{local_rank}")
+        steps = min(args.steps, 50)
+        if args.workload == "prefill":
+            line = kb.bench_prefill(nvk, torch, dev, steps, args.warmup, args.seqs, min(512, args.qmax), args.qmax)
+        elif args.workload == "store":
+            line = kb.bench_store(nvk, torch, dev, steps, args.warmup)
+        else:
+            line = kb.bench_prologue(nvk, torch, dev, steps, args.warmup)
+        print(json.dumps(line), flush=True)
         return 0
 
     dist = None

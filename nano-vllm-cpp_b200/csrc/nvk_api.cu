@@ -144,6 +144,7 @@ int nvk_prefill_attention_varlen(const void* query, const void* key, const void*
     PrefillArgs a{query, key, value, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables, output, num_seqs,
                   total_q, total_k, max_blocks, num_cache_blocks, max_seqlen_q, num_heads, num_kv_heads, head_dim,
                   block_size, scale, dtype, static_cast<cudaStream_t>(stream)};
+    if (prefill_tc_supported(a)) return launch_prefill_tc(a);
     if (prefill_mma_supported(a)) return launch_prefill_mma(a);
     return launch_rowwise_prefill(a);
 }

@@ -75,6 +75,9 @@ size_t decode_mma_workspace_bytes(int64_t batch, int num_heads, int num_kv_heads
 int launch_decode_mma(const DecodeArgs& a);
 bool prefill_mma_supported(const PrefillArgs& a);
 int launch_prefill_mma(const PrefillArgs& a);
+// tcgen05 / TMEM / TMA path (F16/BF16, head_dim 128, paged block_size % 128 == 0).
+bool prefill_tc_supported(const PrefillArgs& a);
+int launch_prefill_tc(const PrefillArgs& a);
 
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__
