@@ -75,5 +75,48 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST_DIR = os.path.join(HERE, "host")
+HOST_LIB = os.path.join(HERE, "libnvk_host.so")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+
+def _gxx() -> str:
+    for cand in ("/usr/bin/g++", shutil.which("g++")):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("g++ not found")
+
+
+def build_host(force: bool = False) -> str:
+    """Builds the C++ operator layer (``libnvk_host.so``: Tensor, Context, operators, Attention layer,
+    step metadata) on top of ``libnvk.so`` and its two test programs under ``build/``."""
+    build()
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    srcs = sorted(os.path.join(HOST_DIR, "src", f) for f in os.listdir(os.path.join(HOST_DIR, "src")) if f.endswith(".cpp"))
+    hdrs = [os.path.join(dp, f) for dp, _, fs in os.walk(os.path.join(HOST_DIR, "include")) for f in fs]
+    hdrs.append(os.path.join(os.path.dirname(HERE), "include", "nvk.h"))
+    newest = max(os.path.getmtime(f) for f in srcs + hdrs + [LIB])
+    inc = ["-I", os.path.join(HOST_DIR, "include"), "-I", os.path.join(os.path.dirname(HERE), "include"),
+           "-I", os.path.join(CUDA_HOME, "include")]
+    common = [_gxx(), "-std=c++17", "-O2", "-fPIC", "-Wall", "-Wextra", *inc]
+    link = ["-L", HERE, "-L", os.path.join(CUDA_HOME, "lib64"), "-lnvk", "-lcudart", "-Wl,-rpath,$ORIGIN"]
+    if force or not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
+        res = subprocess.run([*common, "-shared", "-o", HOST_LIB, *srcs, *link], capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"host layer build failed:\n{res.stdout}\n{res.stderr}")
+    tests_dir = os.path.join(HOST_DIR, "tests")
+    for name in sorted(f[:-4] for f in os.listdir(tests_dir) if f.endswith(".cpp")):
+        exe = os.path.join(OBJ_DIR, name)
+        src = os.path.join(tests_dir, name + ".cpp")
+        dep = max(os.path.getmtime(src), os.path.getmtime(os.path.join(tests_dir, "check.h")), os.path.getmtime(HOST_LIB))
+        if force or not os.path.exists(exe) or os.path.getmtime(exe) < dep:
+            res = subprocess.run([*common, "-o", exe, src, "-L", HERE, "-L", os.path.join(CUDA_HOME, "lib64"),
+                                  "-lnvk_host", "-lnvk", "-lcudart", "-Wl,-rpath,$ORIGIN/.."], capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"host test build failed ({name}):\n{res.stdout}\n{res.stderr}")
+    return HOST_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_host(force="--force" in sys.argv))

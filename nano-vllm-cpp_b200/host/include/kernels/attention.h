@@ -1,0 +1,30 @@
+// Attention operators (signatures of include/kernels/attention.h:7-56 of the reference).
+#pragma once
+
+#include "utils/tensor.h"
+
+namespace nano_vllm {
+
+void launch_prefill_attention_dense(const Tensor& query, const Tensor* cu_seqlens_q, const Tensor& key,
+                                    const Tensor& value, const Tensor* cu_seqlens_k, int num_kv_heads, int head_dim,
+                                    float scale, Tensor& output, cudaStream_t stream = nullptr);
+
+void launch_prefill_attention_paged(const Tensor& query, const Tensor* cu_seqlens_q, const Tensor& k_cache,
+                                    const Tensor& v_cache, const Tensor* cu_seqlens_k, const Tensor& block_tables,
+                                    int num_kv_heads, int head_dim, int block_size, float scale, Tensor& output,
+                                    cudaStream_t stream = nullptr);
+
+// No allocator in this signature: split-K scratch comes from the library's built-in array
+// (nvk_decode_attention_paged_static) when the problem fits it, otherwise the call runs unsplit.
+void launch_decode_attention_paged(const Tensor& query, const Tensor& k_cache, const Tensor& v_cache,
+                                   const Tensor& context_lens, const Tensor& block_tables, int num_kv_heads,
+                                   int head_dim, int block_size, float scale, Tensor& output,
+                                   cudaStream_t stream = nullptr);
+
+// Outside the scope of this library: throws std::invalid_argument("unsupported").
+void launch_decode_attention_paged_int8(const Tensor& query, const Tensor& k_cache, const Tensor& v_cache,
+                                        const Tensor& k_scale, const Tensor& v_scale, const Tensor& context_lens,
+                                        const Tensor& block_tables, int num_kv_heads, int head_dim, int block_size,
+                                        float scale, Tensor& output, cudaStream_t stream = nullptr);
+
+}  // namespace nano_vllm

@@ -1,0 +1,17 @@
+// store_kvcache operator (signature of include/kernels/kvcache.h:7-12 of the reference).
+#pragma once
+
+#include "utils/tensor.h"
+
+namespace nano_vllm {
+
+// cache row slot_mapping[t] <- key / value row t; slots < 0 or beyond the cache are skipped.
+void store_kvcache(const Tensor& key, const Tensor& value, Tensor& k_cache, Tensor& v_cache,
+                   const Tensor& slot_mapping, cudaStream_t stream = nullptr);
+
+// int8 KV cache (include/kernels/kvcache.h:17-24 of the reference) is outside the scope of this
+// library: the symbol exists so callers link, and throws std::invalid_argument("unsupported").
+void store_kvcache_int8(const Tensor& key, const Tensor& value, Tensor& k_cache, Tensor& v_cache, Tensor& k_scale,
+                        Tensor& v_scale, const Tensor& slot_mapping, cudaStream_t stream = nullptr);
+
+}  // namespace nano_vllm
