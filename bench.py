@@ -194,10 +194,37 @@ def cpu_baseline(torch, w, budget_s=12.0):
                       f"oracle in {dt:.1f} s; bytes counted at the workload's bf16 element size"}
 
 
+def rank_plan(rank, world, shard):
+    """What one rank works on.  ``batch``: an independent batch per rank (same shape, own seed; weak scaling).
+    ``kv_heads``: tensor-parallel layout of the reference (src/models/transformer.cpp:75-80) -- every rank holds
+    Hkv / world KV heads and their query heads for the SAME sequences, so the step metadata is replicated (same
+    seed) and the total work is fixed (strong scaling).  Neither layout needs a collective inside attention."""
+    if shard == "kv_heads":
+        if CFG["num_kv_heads"] % world != 0:
+            raise ValueError("num_kv_heads must be divisible by the number of GPUs")
+        return {"seed": 2024, "num_heads": CFG["num_heads"] // world, "num_kv_heads": CFG["num_kv_heads"] // world,
+                "scaling": "strong", "parallelism": f"tp{world}: {CFG['num_kv_heads'] // world} KV heads per GPU, replicated metadata, no collective"}
+    return {"seed": 2024 + rank, "num_heads": CFG["num_heads"], "num_kv_heads": CFG["num_kv_heads"], "scaling": "weak",
+            "parallelism": f"{world} independent batches, one per GPU, no collective"}
+
+
+def combine_ranks(torch, dist, world, device, times_ms, sums):
+    """Max over ranks of every timing, sum over ranks of every additive quantity (bytes, launches)."""
+    if world <= 1:
+        return list(times_ms), list(sums)
+    t = torch.tensor(list(times_ms), device=device, dtype=torch.float64)
+    u = torch.tensor(list(sums), device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.all_reduce(u, op=dist.ReduceOp.SUM)
+    return [float(x) for x in t], [float(x) for x in u]
+
+
 def run_ours(args, torch, dist, rank, world, dev):
     nvk = entry.load_package()
     nvk.lib()  # raises if the CUDA library is missing: there is no fallback
-    w = make_workload(torch, dev, seed=2024 + rank)
+    plan = rank_plan(rank, world, args.shard)
+    CFG["num_heads"], CFG["num_kv_heads"] = plan["num_heads"], plan["num_kv_heads"]
+    w = make_workload(torch, dev, seed=plan["seed"])
     ab = algorithmic_bytes(w["context_lens_np"], w["block_tables_np"])
     ws_bytes = nvk.decode_attention_workspace_bytes(CFG["batch"], CFG["num_heads"], CFG["num_kv_heads"],
                                                     CFG["head_dim"], w["block_tables"].shape[1], CFG["block_size"])
@@ -272,29 +299,21 @@ def run_ours(args, torch, dist, rank, world, dev):
         barrier()
         e2e_ms = e0.elapsed_time(e1)
 
-    if world > 1:
-        t = torch.tensor([total_ms, e2e_ms, decode_ms, float(ab["total"]), float(launches)], device=dev,
-                         dtype=torch.float64)
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        total_ms, e2e_ms, decode_ms = float(tmax[0]), float(tmax[1]), float(tmax[2])
-        bytes_all, launches = float(tsum[3]), int(tsum[4])
-    else:
-        bytes_all = float(ab["total"])
+    (total_ms, e2e_ms, decode_ms), (bytes_all, launches) = combine_ranks(
+        torch, dist, world, dev, [total_ms, e2e_ms, decode_ms], [float(ab["total"]), float(launches)])
+    launches = int(launches)
 
     peak, peak_kind = measured_peaks()
     achieved = ab["decode"] / (decode_ms * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": bytes_all * args.steps / (total_ms * 1e-3) / 1e9, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"paged decode attention + store_kvcache, Qwen3-8B shape: batch {CFG['batch']} per GPU, 32/8 heads, "
+        "higher_is_better": True, "scaling": plan["scaling"], "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"paged decode attention + store_kvcache, Qwen3-8B shape: batch {CFG['batch']} per GPU, {CFG['num_heads']}/{CFG['num_kv_heads']} heads per GPU, "
                                "head_dim 128, block_size 256, context U[1024,8192], random-permutation block tables",
                    "bytes_per_step_per_gpu": ab["total"], "kv_pool_blocks": w["pool"],
                    "l2": "inputs (about 4.8 GB of KV per step) exceed the 126 MB L2; no flush needed",
-                   "parallelism": f"{world} independent batches, one per GPU, no collective"},
+                   "parallelism": plan["parallelism"]},
         "e2e": {"value": bytes_all * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches,
@@ -377,6 +396,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue"],
                     help="decode is the benchmark; the others time the remaining kernels of the path (1 GPU)")
+    ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
+                    help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")
     ap.add_argument("--seqs", type=int, default=16, help="prefill workload: number of sequences")
     ap.add_argument("--qmax", type=int, default=4096, help="prefill workload: longest new-token run")
     ap.add_argument("--batch", type=int, default=CFG["batch"],
