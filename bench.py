@@ -394,10 +394,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed"],
                     help="decode is the benchmark; the others time the remaining kernels of the path (1 GPU)")
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
                     help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")
+    ap.add_argument("--layers", type=int, default=36, help="mixed workload: layer caches per step")
     ap.add_argument("--seqs", type=int, default=16, help="prefill workload: number of sequences")
     ap.add_argument("--qmax", type=int, default=4096, help="prefill workload: longest new-token run")
     ap.add_argument("--batch", type=int, default=CFG["batch"],
@@ -431,6 +432,8 @@ def main():
             line = kb.bench_prefill(nvk, torch, dev, steps, args.warmup, args.seqs, min(512, args.qmax), args.qmax)
         elif args.workload == "store":
             line = kb.bench_store(nvk, torch, dev, steps, args.warmup)
+        elif args.workload == "mixed":
+            line = kb.bench_mixed(nvk, torch, dev, min(steps, 10), min(args.warmup, 3), layers=args.layers)
         else:
             line = kb.bench_prologue(nvk, torch, dev, steps, args.warmup)
         print(json.dumps(line), flush=True)

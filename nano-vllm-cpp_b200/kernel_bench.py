@@ -179,3 +179,89 @@ def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
             "roofline": {"bound": "hbm", "kernel": "fused_prologue_kernel", "achieved": ach, "peak": hbm,
                          "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
             "gpu_launches": steps}
+
+
+def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_lo=512, ctx_hi=16384, prefill_seqs=4,
+                prefill_len=2048, mem_fraction=0.80):
+    """Config 4: one continuous-batching step of attention over ``layers`` layer caches -- per layer the store of the
+    prefill tokens, the varlen prefill (no prefix), the store of the decode tokens and the paged decode attention,
+    all on one stream (the reference never fuses prefill and decode into one launch, src/engine/scheduler.cpp:65-67).
+    36 distinct caches of this shape need about 226 GiB, more than one GPU holds, so as many distinct physical
+    caches as fit are allocated and the logical layers are mapped onto them round-robin; every physical cache has
+    its own block-table permutation and each is far larger than L2, so the reuse brings no cache hits."""
+    from . import workloads as wl
+    rng = np.random.default_rng(4040)
+    ctx = rng.integers(ctx_lo, ctx_hi + 1, size=decode_seqs).astype(np.int32)
+    dec_blocks = int(((ctx.astype(np.int64) + BS - 1) // BS).sum())
+    pre_blocks = prefill_seqs * ((prefill_len + BS - 1) // BS)
+    pool = dec_blocks + pre_blocks
+    bytes_per_layer = 2 * pool * BS * HKV * D * 2
+    free, _ = torch.cuda.mem_get_info(dev)
+    phys = int(max(1, min(layers, (free * mem_fraction) // bytes_per_layer)))
+    bf = torch.bfloat16
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4040)
+    caches = []
+    for _ in range(phys):
+        perm = rng.permutation(pool).astype(np.int32)
+        tables = np.zeros((decode_seqs, int(((ctx.max() + BS - 1) // BS))), np.int32)
+        at = 0
+        for i, c in enumerate(ctx):
+            n = (int(c) + BS - 1) // BS
+            tables[i, :n] = perm[at:at + n]
+            at += n
+        last = ctx.astype(np.int64) - 1
+        dslots = (tables[np.arange(decode_seqs), last // BS].astype(np.int64) * BS + last % BS).astype(np.int32)
+        pblocks = perm[at:at + pre_blocks].reshape(prefill_seqs, -1)
+        pos = np.arange(prefill_len)
+        pslots = np.concatenate([pblocks[s, pos // BS].astype(np.int64) * BS + pos % BS for s in range(prefill_seqs)]).astype(np.int32)
+        kc = torch.empty((pool, BS, HKV, D), device=dev, dtype=bf).normal_(generator=gen)
+        vc = torch.empty((pool, BS, HKV, D), device=dev, dtype=bf).normal_(generator=gen)
+        caches.append({"k": kc, "v": vc, "tables": torch.from_numpy(tables).to(dev), "dslots": torch.from_numpy(dslots).to(dev),
+                       "pslots": torch.from_numpy(pslots).to(dev)})
+    total_pq = prefill_seqs * prefill_len
+    cu = torch.arange(0, total_pq + 1, prefill_len, dtype=torch.int32, device=dev)
+    pq = torch.randn((total_pq, HQ, D), generator=gen, device=dev).to(bf)
+    pk = torch.randn((total_pq, HKV, D), generator=gen, device=dev).to(bf)
+    pv = torch.randn((total_pq, HKV, D), generator=gen, device=dev).to(bf)
+    pout = torch.empty_like(pq)
+    dq = torch.randn((decode_seqs, HQ, D), generator=gen, device=dev).to(bf)
+    dk = torch.randn((decode_seqs, HKV, D), generator=gen, device=dev).to(bf)
+    dv = torch.randn((decode_seqs, HKV, D), generator=gen, device=dev).to(bf)
+    dout = torch.empty_like(dq)
+    ctx_dev = torch.from_numpy(ctx).to(dev)
+    scale = 1.0 / math.sqrt(D)
+    max_blocks = caches[0]["tables"].shape[1]
+    ws = torch.empty(max(16, nvk.decode_attention_workspace_bytes(decode_seqs, HQ, HKV, D, max_blocks, BS)), dtype=torch.uint8, device=dev)
+
+    def step():
+        for layer in range(layers):
+            c = caches[layer % phys]
+            nvk.store_kvcache(pk, pv, c["k"], c["v"], c["pslots"])
+            nvk.launch_prefill_attention_dense(pq, cu, pk, pv, cu, HKV, D, scale, pout)
+            nvk.store_kvcache(dk, dv, c["k"], c["v"], c["dslots"])
+            nvk.launch_decode_attention_paged(dq, c["k"], c["v"], ctx_dev, c["tables"], HKV, D, BS, scale, dout, ws)
+
+    mean_ms, med_ms = _time(torch, step, steps, warmup)
+    dec_bytes = int(ctx.astype(np.int64).sum()) * 2 * HKV * D * 2 + 2 * decode_seqs * HQ * D * 2
+    pre_bytes = 2 * total_pq * HQ * D * 2 + 2 * total_pq * HKV * D * 2
+    store_bytes = 2 * (2 * (total_pq + decode_seqs) * HKV * D * 2)
+    bytes_layer = dec_bytes + pre_bytes + store_bytes
+    flops_layer = prefill_seqs * 4 * HQ * D * (prefill_len * (prefill_len + 1) // 2)
+    hbm, tf, kind = _peaks()
+    ideal_ms = layers * (dec_bytes / (hbm * 1e9) + flops_layer / (tf * 1e12)) * 1e3
+    ach = layers * bytes_layer / (mean_ms * 1e-3) / 1e9
+    return {"metric": "mixed_step_attention_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": mean_ms, "median_ms": med_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"mixed continuous-batching step, Qwen3-8B attention shape: {prefill_seqs} prefill sequences x "
+                                   f"{prefill_len} new tokens + {decode_seqs} decode sequences with context U[{ctx_lo},{ctx_hi}], "
+                                   f"{layers} layers per step",
+                       "physical_layer_caches": phys, "bytes_per_layer_cache": bytes_per_layer,
+                       "note": "logical layers are mapped round-robin onto the physical caches that fit in HBM",
+                       "bytes_per_layer": bytes_layer, "prefill_flops_per_layer": flops_layer,
+                       "l2": "each layer cache (GiB) exceeds the 126 MB L2"},
+            "roofline": {"bound": "hbm", "kernel": "decode_split_kernel (dominant; prefill_tc2_kernel second)", "achieved": ach,
+                         "peak": hbm, "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm,
+                         "ideal_ms_per_step": ideal_ms, "frac_of_ideal_time": ideal_ms / mean_ms, "traffic": None},
+            "gpu_launches": steps * layers * 5}
