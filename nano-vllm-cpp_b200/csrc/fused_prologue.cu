@@ -1,18 +1,22 @@
 // Decode prologue for sm_100a: split packed qkv rows, RMSNorm + neox RoPE on the q and k heads,
 // q -> q_out, k / v -> paged cache rows.
 //
-// Replaces fused_split_norm_rope_store_kernel (src/kernels/split_qkv.cu:62-154 of the
-// reference: a 128-thread block per (row, head), one element per thread, a block reduction and a
-// shared-memory exchange per head).  Here one WARP owns one (row, head): each lane holds D/32
-// contiguous elements (one 4/8/16-byte load), the sum of squares is a shuffle reduction and the
-// rotation partner (d +- D/2) lives in lane ^ 16, so there is no shared memory and no barrier.
-// HBM-bound: rows * (Hq + 2 Hkv) * D elements read, the same number written.
+// Replaces fused_split_norm_rope_store_kernel (src/kernels/split_qkv.cu:62-154 of the reference:
+// a 128-thread block per (row, head), one element per thread, a block reduction and a
+// shared-memory exchange per head).  Here one 8-warp block owns one ROW: position, slot, the row
+// of the cos/sin table and the norm weights are fetched once per row instead of once per head, a
+// warp takes every 8th head, each lane holds D/32 contiguous elements of a head (one 4/8/16-byte
+// load), and all of a warp's head vectors are requested before the first one is used.  The sum
+// of squares is a shuffle reduction and the rotation partner (d +- D/2) lives in lane ^ 16, so
+// there is no shared memory and no barrier.  HBM-bound in the limit of many rows (rows * (Hq + 2 Hkv)
+// * D elements read, the same number written); at decode batch sizes it is latency-bound.
 #include "nvk_internal.cuh"
 
 namespace nvk {
 namespace {
 
 constexpr int kWarpsPerBlock = 8;
+constexpr int kHeadsInFlight = 8;   // head vectors a warp keeps in registers at once
 
 template <int V> struct VecOf;
 template <> struct VecOf<2> { using type = uint32_t; };
@@ -29,57 +33,75 @@ fused_prologue_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ pos
                       T* __restrict__ q_out) {
     constexpr int D = V * 32;
     using Vec = typename VecOf<V>::type;
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int heads = hq + 2 * hkv;
-    const int64_t work = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (work >= rows * heads) return;
-    const int64_t row = work / heads;
-    const int head = static_cast<int>(work - row * heads);
-    const bool is_q = head < hq;
-    const bool is_k = !is_q && head < hq + hkv;
+    const int64_t row = blockIdx.x;
+    if (row >= rows) return;
 
-    const T* src = qkv + (row * heads + head) * D + lane * V;
-    union { Vec v; T e[V]; } in, outv;
-    in.v = *reinterpret_cast<const Vec*>(src);
+    const int pos = positions[row];
+    const int64_t slot = slot_mapping[row];
+    const bool rotate = pos >= 0 && pos < max_positions;
+    const bool store_kv = slot >= 0 && slot < cache_rows;
+    const T* src_row = qkv + row * static_cast<int64_t>(heads) * D + lane * V;
 
-    T* dst;
-    if (is_q) {
-        dst = q_out + (row * hq + head) * D;
-    } else {
-        const int64_t slot = slot_mapping[row];
-        if (slot < 0 || slot >= cache_rows) return;   // whole warp leaves together
-        const int kv = is_k ? head - hq : head - hq - hkv;
-        dst = (is_k ? k_cache : v_cache) + (slot * hkv + kv) * D;
-    }
-
-    if (is_q || is_k) {
-        float x[V];
-        float ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < V; ++i) { x[i] = ElemTraits<T>::to_float(in.e[i]); ss += x[i] * x[i]; }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        const float inv_rms = rsqrtf(ss / static_cast<float>(D) + eps);
-        const T* w = (is_q ? q_weight : k_weight) + lane * V;
-#pragma unroll
-        for (int i = 0; i < V; ++i) x[i] = x[i] * inv_rms * ElemTraits<T>::to_float(w[i]);
-        const int pos = positions[row];
-        const bool rotate = pos >= 0 && pos < max_positions;
+    // per-row constants of this lane: cos / sin of its V rotation pairs, q and k norm weights
+    float cs[V], sn[V], wq[V], wk[V];
+    {
         const float* table = cos_sin + static_cast<int64_t>(rotate ? pos : 0) * D + (lane & 15) * V;
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
-            if (rotate) {
-                const float c = table[i], s = table[i + D / 2];
-                x[i] = lane < 16 ? x[i] * c - partner * s : x[i] * c + partner * s;
-            }
+            cs[i] = rotate ? table[i] : 1.0f;
+            sn[i] = rotate ? table[i + D / 2] : 0.0f;
+            wq[i] = ElemTraits<T>::to_float(q_weight[lane * V + i]);
+            wk[i] = ElemTraits<T>::to_float(k_weight[lane * V + i]);
+        }
+    }
+
+    for (int base = warp; base < heads; base += kWarpsPerBlock * kHeadsInFlight) {
+        union Pack { Vec v; T e[V]; };
+        Pack in[kHeadsInFlight];
+#pragma unroll
+        for (int u = 0; u < kHeadsInFlight; ++u) {   // all loads first
+            const int head = base + u * kWarpsPerBlock;
+            if (head < heads) in[u].v = *reinterpret_cast<const Vec*>(src_row + static_cast<int64_t>(head) * D);
         }
 #pragma unroll
-        for (int i = 0; i < V; ++i) outv.e[i] = ElemTraits<T>::from_float(x[i]);
-    } else {
-        outv.v = in.v;   // v heads: plain copy
+        for (int u = 0; u < kHeadsInFlight; ++u) {
+            const int head = base + u * kWarpsPerBlock;
+            if (head >= heads) break;
+            const bool is_q = head < hq;
+            const bool is_k = !is_q && head < hq + hkv;
+            T* dst;
+            if (is_q) {
+                dst = q_out + (row * hq + head) * D;
+            } else {
+                if (!store_kv) continue;   // warp-uniform
+                const int kv = is_k ? head - hq : head - hq - hkv;
+                dst = (is_k ? k_cache : v_cache) + (slot * hkv + kv) * D;
+            }
+            Pack out;
+            if (is_q || is_k) {
+                float x[V];
+                float ss = 0.0f;
+#pragma unroll
+                for (int i = 0; i < V; ++i) { x[i] = ElemTraits<T>::to_float(in[u].e[i]); ss += x[i] * x[i]; }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float inv_rms = rsqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    x[i] = x[i] * inv_rms * (is_q ? wq[i] : wk[i]);
+                    const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
+                    // positions outside the table keep cs = 1, sn = 0: the value passes through un-rotated
+                    const float rot = lane < 16 ? x[i] * cs[i] - partner * sn[i] : x[i] * cs[i] + partner * sn[i];
+                    out.e[i] = ElemTraits<T>::from_float(rotate ? rot : x[i]);
+                }
+            } else {
+                out.v = in[u].v;   // v heads: plain copy
+            }
+            *reinterpret_cast<Vec*>(dst + lane * V) = out.v;
+        }
     }
-    *reinterpret_cast<Vec*>(dst + lane * V) = outv.v;
 }
 
 template <typename T>
@@ -87,8 +109,7 @@ int launch_typed(const void* qkv, const int32_t* positions, const void* qw, cons
                  const float* cos_sin, int64_t max_positions, const int32_t* slot_mapping, void* k_cache,
                  void* v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv, int d, void* q_out,
                  cudaStream_t stream) {
-    const int64_t work = rows * (hq + 2 * hkv);
-    const int64_t blocks = (work + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const int64_t blocks = rows;
     if (blocks > 0x7fffffffLL) return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: too many rows");
     const dim3 grid(static_cast<unsigned>(blocks));
 #define NVK_LAUNCH(V)                                                                                          \
