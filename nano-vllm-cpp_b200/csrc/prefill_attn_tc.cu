@@ -156,20 +156,45 @@ __device__ __forceinline__ void reg_fence32(uint32_t (&r)[32]) {
                       "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]));
 }
 
+// sm_100 packed-pair and three-input float instructions: they halve the instruction count of the softmax
+// passes, which with two resident warps per scheduler are bound by dependent-issue latency, not by lanes.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // Maximum of 32 raw scores (keys key_base .. key_base + 31); MASK hides keys >= lim.
 template <bool MASK>
 __device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], int key_base, int lim) {
     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-        float a = __uint_as_float(r[i]), b = __uint_as_float(r[i + 1]), c = __uint_as_float(r[i + 2]), d = __uint_as_float(r[i + 3]);
-        if (MASK) {
-            if (key_base + i >= lim) a = -INFINITY;
-            if (key_base + i + 1 >= lim) b = -INFINITY;
-            if (key_base + i + 2 >= lim) c = -INFINITY;
-            if (key_base + i + 3 >= lim) d = -INFINITY;
+    for (int i = 0; i < 32; i += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            v[u] = __uint_as_float(r[i + u]);
+            if (MASK && key_base + i + u >= lim) v[u] = -INFINITY;
         }
-        m0 = fmaxf(m0, a); m1 = fmaxf(m1, b); m2 = fmaxf(m2, c); m3 = fmaxf(m3, d);
+        m0 = max3(m0, v[0], v[1]); m1 = max3(m1, v[2], v[3]); m2 = max3(m2, v[4], v[5]); m3 = max3(m3, v[6], v[7]);
     }
     return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
@@ -178,7 +203,8 @@ __device__ __forceinline__ float chunk_max(const uint32_t (&r)[32], int key_base
 template <typename T, bool MASK>
 __device__ __forceinline__ float chunk_probs(const uint32_t (&r)[32], uint32_t (&pk)[16], int key_base, int lim,
                                              float scale_log2, float m_use) {
-    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_use, -m_use);
+    uint64_t acc0 = 0ull, acc1 = 0ull;   // two packed pairs of fp32 partial sums
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
         float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
@@ -189,17 +215,20 @@ __device__ __forceinline__ float chunk_probs(const uint32_t (&r)[32], uint32_t (
             if (key_base + 2 * i + 2 >= lim) s2 = -INFINITY;
             if (key_base + 2 * i + 3 >= lim) s3 = -INFINITY;
         }
-        const float p0 = fast_exp2(fmaf(s0, scale_log2, -m_use)), p1 = fast_exp2(fmaf(s1, scale_log2, -m_use));
-        const float p2 = fast_exp2(fmaf(s2, scale_log2, -m_use)), p3 = fast_exp2(fmaf(s3, scale_log2, -m_use));
-        a0 += p0; a1 += p1; a2 += p2; a3 += p3;
+        float x0, x1, x2, x3;
+        unpack_f32x2(fma_f32x2(pack_f32x2(s0, s1), scale2, neg_m2), x0, x1);
+        unpack_f32x2(fma_f32x2(pack_f32x2(s2, s3), scale2, neg_m2), x2, x3);
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+        acc0 = add_f32x2(acc0, pack_f32x2(p0, p1));
+        acc1 = add_f32x2(acc1, pack_f32x2(p2, p3));
         pk[i] = ElemTraits<T>::pack2(p0, p1);
         pk[i + 1] = ElemTraits<T>::pack2(p2, p3);
     }
+    float a0, a1, a2, a3;
+    unpack_f32x2(acc0, a0, a1);
+    unpack_f32x2(acc1, a2, a3);
     return (a0 + a1) + (a2 + a3);
 }
-
-// UMMA shared-memory descriptor: start address, leading / stride byte offsets (all >> 4), descriptor
-// version 1 (bits 46-47), 128-byte swizzle (layout type 2 in bits 61-63).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     const uint32_t lo = ((addr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
     const uint32_t hi = (sbo_bytes >> 4) | (1u << 14) | (2u << 29);
@@ -880,6 +909,364 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
 }
 
+// =================================================================================================
+// Version 4: as version 2 (one head pair per block, warp specialised, 128-key tiles), but the
+// probabilities go to SHARED memory (canonical K-major 128-byte-swizzled panels, consumed as the A
+// operand of an SS MMA) instead of overwriting the scores in TMEM.  A softmax thread pulls its whole
+// score row into registers first and releases the score columns at once, so S_t(j+1) is computed
+// while softmax_t(j) is still running and a tile's softmax steps follow each other back to back;
+// P.V_t(j) runs under softmax_t(j+1).  K is double buffered, V single buffered, 224 KiB of shared
+// memory and 512 TMEM columns per block.
+// =================================================================================================
+constexpr int kOff4Q = 0, kOff4K = 2 * kTileBytes, kOff4V = 4 * kTileBytes, kOff4P = 5 * kTileBytes, kOff4Bar = 7 * kTileBytes;
+constexpr int kSmemBytes4 = kOff4Bar + 256 + 1024;
+constexpr int kThreads4 = 320;
+
+// One 128-key online-softmax step of a row.  Scores are read once into registers; `on_scores_read` runs as
+// soon as they are (the caller releases the TMEM columns there); probabilities are written to `p_row`
+// (this row of the two swizzled P panels).  Returns false when a bounded wait gave up.
+template <typename T, typename OnRead>
+__device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, unsigned char* p_panels, int row,
+                                                    bool need_mask, int key0, int lim, float scale_log2, bool first,
+                                                    float& m_ref, float& l_run, uint32_t pv_done_bar, uint32_t pv_done_parity,
+                                                    volatile int* abort_flag, OnRead on_scores_read) {
+    uint32_t r0[32], r1[32], r2[32], r3[32];
+    tmem_ld32(t_s, r0);
+    tmem_ld32(t_s + 32, r1);
+    tmem_ld32(t_s + 64, r2);
+    tmem_ld32(t_s + 96, r3);
+    tc_wait_ld();
+    reg_fence32(r0); reg_fence32(r1); reg_fence32(r2); reg_fence32(r3);
+    on_scores_read();
+    float mx;
+    if (need_mask) {
+        mx = fmaxf(fmaxf(chunk_max<true>(r0, key0, lim), chunk_max<true>(r1, key0 + 32, lim)),
+                   fmaxf(chunk_max<true>(r2, key0 + 64, lim), chunk_max<true>(r3, key0 + 96, lim)));
+    } else {
+        mx = fmaxf(fmaxf(chunk_max<false>(r0, 0, 0), chunk_max<false>(r1, 0, 0)),
+                   fmaxf(chunk_max<false>(r2, 0, 0), chunk_max<false>(r3, 0, 0)));
+    }
+    mx *= scale_log2;
+    // P.V of the previous step must be complete before O is rescaled and before its P is overwritten: wait
+    // as late as that allows (with no rescale, after the first 32 exponentials)
+    bool pv_waited = first;
+    if (__any_sync(0xffffffffu, mx > m_ref + kRescaleThreshold)) {
+        if (!pv_waited && !warp_mbar_wait(pv_done_bar, pv_done_parity, abort_flag, 42)) return false;
+        pv_waited = true;
+        const float m_new = fmaxf(m_ref, mx);
+        const float f = (m_new == -INFINITY) ? 1.0f : fast_exp2(m_ref - m_new);
+        if (!first) {
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(t_o + c * 32, r);
+                tc_wait_ld(); reg_fence32(r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+                tmem_st32(t_o + c * 32, r);
+            }
+            tc_wait_st();
+        }
+        l_run *= f;
+        m_ref = m_new;
+    }
+    const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+    uint32_t pk[16];
+    auto store_chunk = [&](int c32) {   // 32 keys = four 16-byte pieces of this row
+        unsigned char* panel = p_panels + (c32 >> 1) * kPanelBytes + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const int cc = (c32 & 1) * 4 + q4;   // 16-byte column inside the 128-byte panel row
+            *reinterpret_cast<uint4*>(panel + ((cc ^ (row & 7)) << 4)) =
+                make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        }
+    };
+    l_run += need_mask ? chunk_probs<T, true>(r0, pk, key0, lim, scale_log2, m_use)
+                       : chunk_probs<T, false>(r0, pk, 0, 0, scale_log2, m_use);
+    if (!pv_waited && !warp_mbar_wait(pv_done_bar, pv_done_parity, abort_flag, 43)) return false;
+    store_chunk(0);
+    l_run += need_mask ? chunk_probs<T, true>(r1, pk, key0 + 32, lim, scale_log2, m_use)
+                       : chunk_probs<T, false>(r1, pk, 0, 0, scale_log2, m_use);
+    store_chunk(1);
+    l_run += need_mask ? chunk_probs<T, true>(r2, pk, key0 + 64, lim, scale_log2, m_use)
+                       : chunk_probs<T, false>(r2, pk, 0, 0, scale_log2, m_use);
+    store_chunk(2);
+    l_run += need_mask ? chunk_probs<T, true>(r3, pk, key0 + 96, lim, scale_log2, m_use)
+                       : chunk_probs<T, false>(r3, pk, 0, 0, scale_log2, m_use);
+    store_chunk(3);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy stores -> visible to the MMA
+    return true;
+}
+
+
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads4, 1)
+prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ int s_info[4];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head0 = 2 * blockIdx.x;
+    const int kvh = head0 * p.num_kv_heads / p.num_heads;
+
+    if (tid == 0) {
+        const int64_t want = static_cast<int64_t>(gridDim.y) - 1 - blockIdx.y;
+        int64_t acc = 0;
+        int found = -1, q0 = 0;
+        if (p.cu_q == nullptr) {
+            if (want * kBM < p.total_q) { found = 0; q0 = static_cast<int>(want * kBM); }
+        } else {
+            for (int64_t s = 0; s < p.num_seqs; ++s) {
+                const int64_t tiles = (static_cast<int64_t>(p.cu_q[s + 1]) - p.cu_q[s] + kBM - 1) / kBM;
+                if (want < acc + tiles) { found = static_cast<int>(s); q0 = static_cast<int>((want - acc) * kBM); break; }
+                acc += tiles;
+            }
+        }
+        s_info[0] = found; s_info[1] = q0;
+        s_abort = 0;
+    }
+    __syncthreads();
+    const int seq = s_info[0];
+    if (seq < 0) return;
+    const int q0 = s_info[1];
+    int64_t qb, kb;
+    int q_len, k_len;
+    if (p.cu_q == nullptr) { qb = 0; kb = 0; q_len = static_cast<int>(p.total_q); k_len = static_cast<int>(p.total_k); }
+    else {
+        qb = p.cu_q[seq]; kb = p.cu_k[seq];
+        q_len = p.cu_q[seq + 1] - static_cast<int>(qb); k_len = p.cu_k[seq + 1] - static_cast<int>(kb);
+    }
+    const int rows_here = min(kBM, q_len - q0);
+    const int shift = k_len - q_len;
+    int k_hi = shift + q0 + rows_here;
+    if (k_hi > k_len) k_hi = k_len;
+    const int num_kt = k_hi > 0 ? (k_hi + kBN - 1) / kBN : 0;
+    const size_t out_stride = static_cast<size_t>(p.num_heads) * kHeadDim;
+
+    if (num_kt == 0) {
+        for (int t = 0; t < 2; ++t) {
+            T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(qb + q0) * p.num_heads + head0 + t) * kHeadDim;
+            for (int i = tid; i < rows_here * (kHeadDim / 8); i += kThreads4) {
+                const int r = i / (kHeadDim / 8), c = i % (kHeadDim / 8);
+                *reinterpret_cast<uint4*>(o0 + r * out_stride + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        return;
+    }
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t sm_q = smem_base + kOff4Q, sm_k = smem_base + kOff4K, sm_v = smem_base + kOff4V, sm_p = smem_base + kOff4P;
+    const uint32_t bars = smem_base + kOff4Bar;
+    const uint32_t bar_q = bars, bar_vfix = bars + 8, bar_vfull = bars + 16, bar_vempty = bars + 24;
+    auto bar_kfull = [&](int s) { return bars + 32 + 8 * s; };
+    auto bar_kempty = [&](int s) { return bars + 48 + 8 * s; };
+    auto bar_sfull = [&](int t) { return bars + 64 + 8 * t; };
+    auto bar_sread = [&](int t) { return bars + 80 + 8 * t; };
+    auto bar_pfull = [&](int t) { return bars + 96 + 8 * t; };
+    auto bar_odone = [&](int t) { return bars + 112 + 8 * t; };
+    auto bar_ofinal = [&](int t) { return bars + 128 + 8 * t; };
+    volatile int* abort_flag = &s_abort;
+
+    if (tid == 0) {
+        mbar_init(bar_q, 1); mbar_init(bar_vfix, 1); mbar_init(bar_vfull, 1); mbar_init(bar_vempty, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_kfull(i), 1); mbar_init(bar_kempty(i), 1);
+            mbar_init(bar_sfull(i), 1); mbar_init(bar_sread(i), 4); mbar_init(bar_pfull(i), 4);
+            mbar_init(bar_odone(i), 1); mbar_init(bar_ofinal(i), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(kTmemCols2) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    const int last_partial = (num_kt * kBN > k_len) ? num_kt - 1 : -1;
+
+    if (warp == 9) {
+        // ------------------------------------------------------------------ TMA producer
+        const int32_t* table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : nullptr;
+        auto key_row = [&](int key0) -> int {
+            if (table) {
+                const int id = table[key0 / p.block_size];
+                if (id < 0 || id >= p.num_cache_blocks) return static_cast<int>(p.key_rows);
+                return id * p.block_size + key0 % p.block_size;
+            }
+            return static_cast<int>(kb) + key0;
+        };
+        auto load_k = [&](int j) -> bool {   // lane 0 only: K_j into slot j & 1
+            const int s = j & 1;
+            if (j >= 2 && !mbar_wait(bar_kempty(s), ((j >> 1) & 1) ^ 1, abort_flag, 11)) return false;
+            const int r = key_row(j * kBN);
+            mbar_expect_tx(bar_kfull(s), kTileBytes);
+            tma_load_3d(sm_k + s * kTileBytes, &tm_k, 0, kvh, r, bar_kfull(s));
+            tma_load_3d(sm_k + s * kTileBytes + kPanelBytes, &tm_k, 64, kvh, r, bar_kfull(s));
+            return true;
+        };
+        bool ok = true;
+        if (lane == 0) {
+            mbar_expect_tx(bar_q, 2 * kTileBytes);
+            for (int t = 0; t < 2; ++t) {
+                tma_load_3d(sm_q + t * kTileBytes, &tm_q, 0, head0 + t, static_cast<int>(qb) + q0, bar_q);
+                tma_load_3d(sm_q + t * kTileBytes + kPanelBytes, &tm_q, 64, head0 + t, static_cast<int>(qb) + q0, bar_q);
+            }
+            ok = load_k(0);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        for (int j = 0; j < num_kt && ok; ++j) {
+            if (lane == 0) {
+                if (j + 1 < num_kt) ok = load_k(j + 1);            // K runs one tile ahead of V
+                if (ok && j >= 1) ok = mbar_wait(bar_vempty, (j - 1) & 1, abort_flag, 12);
+                if (ok) {
+                    const int r = key_row(j * kBN);
+                    mbar_expect_tx(bar_vfull, kTileBytes);
+                    tma_load_3d(sm_v, &tm_v, 0, kvh, r, bar_vfull);
+                    tma_load_3d(sm_v + kPanelBytes, &tm_v, 64, kvh, r, bar_vfull);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (ok && j == last_partial) {
+                ok = warp_mbar_wait(bar_vfull, j & 1, abort_flag, 13);
+                if (ok) {
+                    const int first_bad = k_len - j * kBN;   // in (0, 128)
+                    for (int i = lane; i < (kBN - first_bad) * 16; i += 32) {
+                        const int r = first_bad + i / 16, c16 = i % 16;
+                        *reinterpret_cast<uint4*>(smem_gen + kOff4V + (c16 >> 3) * kPanelBytes + r * 128 + (c16 & 7) * 16) =
+                            make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_vfix);
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            auto issue_s = [&](int t, int j) {
+                const int s = j & 1;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
+                    umma_ss(tmem_base + t * 128, make_smem_desc(sm_q + t * kTileBytes + off, 16, 1024),
+                            make_smem_desc(sm_k + s * kTileBytes + off, 16, 1024), p.idesc_s, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar_sfull(t));
+            };
+            bool ok = mbar_wait(bar_q, 0, abort_flag, 21) && mbar_wait(bar_kfull(0), 0, abort_flag, 22);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0, 0);
+                issue_s(1, 0);
+                tc_commit(bar_kempty(0));
+            }
+            for (int j = 0; j < num_kt && ok; ++j) {
+                if (j + 1 < num_kt) {   // next scores as soon as this step's scores have been read
+                    ok = mbar_wait(bar_kfull((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, 26);
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        ok = mbar_wait(bar_sread(t), j & 1, abort_flag, 27);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_s(t, j + 1);
+                    }
+                    if (ok) tc_commit(bar_kempty((j + 1) & 1));
+                }
+                if (ok) ok = mbar_wait(bar_vfull, j & 1, abort_flag, 23);
+                if (ok && j == last_partial) ok = mbar_wait(bar_vfix, 0, abort_flag, 24);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    ok = mbar_wait(bar_pfull(t), j & 1, abort_flag, 25);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        umma_ss(tmem_base + 256 + t * 128,
+                                make_smem_desc(sm_p + t * kTileBytes + (kk >> 2) * kPanelBytes + (kk & 3) * 32, 16, 1024),
+                                make_smem_desc(sm_v + kk * 2048, kPanelBytes, 1024), p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_odone(t));
+                    if (j == num_kt - 1) tc_commit(bar_ofinal(t));
+                }
+                if (ok) tc_commit(bar_vempty);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax warps (thread = row)
+        const int t = warp >> 2;
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const uint32_t t_s = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + t * 128;
+        const uint32_t t_o = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + 256 + t * 128;
+        const int lim = min(shift + q0 + row + 1, k_len);
+        unsigned char* p_panels = smem_gen + kOff4P + t * kTileBytes;
+        const uint32_t sread = bar_sread(t);
+        float m_ref = -INFINITY, l_run = 0.0f;
+        bool alive = true;
+        for (int j = 0; j < num_kt; ++j) {
+            alive = warp_mbar_wait(bar_sfull(t), j & 1, abort_flag, 31);
+            if (!alive) break;
+            tc_fence_after();
+            const int key0 = j * kBN;
+            const bool need_mask = key0 + kBN > min(shift + q0 + 1, k_len);
+            alive = softmax_row_to_smem<T>(t_s, t_o, p_panels, row, need_mask, key0, lim, p.scale_log2, j == 0, m_ref, l_run,
+                                           bar_odone(t), (j - 1) & 1, abort_flag, [&] {
+                                               tc_fence_before();
+                                               __syncwarp();
+                                               if (lane == 0) mbar_arrive(sread);   // the score columns may be overwritten
+                                           });
+            if (!alive) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pfull(t));
+        }
+        if (alive) alive = warp_mbar_wait(bar_ofinal(t), 0, abort_flag, 32);
+        tc_fence_after();
+        if (alive) {
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            unsigned char* stage = smem_gen + kOff4Q + t * kTileBytes;   // Q_t is dead: every S MMA has completed
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(t_o + c * 32, r);
+                tc_wait_ld(); reg_fence32(r);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint4 v;
+                    v.x = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
+                    v.y = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
+                    v.z = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
+                    v.w = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
+                    const int chunk = c * 4 + q4;
+                    *reinterpret_cast<uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4)) = v;
+                }
+            }
+            __syncwarp();
+            T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(qb + q0) * p.num_heads + head0 + t) * kHeadDim;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int r = wq * 32 + 2 * i + (lane >> 4), chunk = lane & 15;
+                if (r < rows_here) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4));
+                    *reinterpret_cast<uint4*>(o0 + r * out_stride + chunk * 8) = v;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols2) : "memory");
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -918,11 +1305,15 @@ uint32_t make_idesc(bool bf16, bool b_mn_major) {
            (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-// NVK_PREFILL_IMPL=tc1 selects the single-tile kernel for every shape (A/B comparisons).
+// Head-pair kernel used when the GQA group is even: 4 (probabilities through shared memory) unless
+// NVK_PREFILL_IMPL=tc2 asks for the version that keeps them in TMEM; NVK_PREFILL_IMPL=tc1 selects the
+// single-tile kernel for every shape (A/B comparisons).
 int tc_version() {
     static const int v = [] {
         const char* e = std::getenv("NVK_PREFILL_IMPL");
-        return (e != nullptr && e[0] == 't' && e[1] == 'c' && e[2] == '1') ? 1 : 2;
+        if (e != nullptr && e[0] == 't' && e[1] == 'c' && e[2] == '1') return 1;
+        if (e != nullptr && e[0] == 't' && e[1] == 'c' && e[2] == '2') return 2;
+        return 4;
     }();
     return v;
 }
@@ -958,6 +1349,17 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
     const int64_t tiles = (a.total_q + kBM - 1) / kBM + (a.cu_q ? a.num_seqs : 0);
     if (tiles > 65535) return fail(NVK_ERR_UNSUPPORTED, "prefill attention (tcgen05): too many query tiles");
     const int group = a.num_heads / a.num_kv_heads;
+    if (group % 2 == 0 && tc_version() == 4) {   // pairs of query heads that share a KV head, P through shared memory
+        static bool attr4_done[64] = {};
+        if (device >= 0 && device < 64 && !attr4_done[device]) {
+            const cudaError_t e = cudaFuncSetAttribute(prefill_tc4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes4);
+            if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill attention (tcgen05 v4): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            attr4_done[device] = true;
+        }
+        const dim3 grid4(a.num_heads / 2, static_cast<unsigned>(tiles));
+        prefill_tc4_kernel<T><<<grid4, kThreads4, kSmemBytes4, a.stream>>>(tq, tk, tv, p);
+        return check_launch("prefill_tc4_kernel launch");
+    }
     if (group % 2 == 0 && tc_version() == 2) {   // pairs of query heads that share a KV head
         static bool attr2_done[64] = {};
         if (device >= 0 && device < 64 && !attr2_done[device]) {
