@@ -5,7 +5,11 @@
 // src/kernels/flash_attn.cpp:203-300); prefill_attn.cu (mma.sync) remains the path for shapes this
 // kernel does not take.
 //
-// One thread block = 128 query rows of one (sequence, head); 128 threads, thread t owns row t.
+// Three kernels live here: the single-tile kernel described next (taken for odd GQA group sizes), and two
+// head-pair kernels further down ("Version 2": probabilities kept in TMEM; "Version 4": probabilities
+// through shared memory, the default for even group sizes).
+//
+// Single-tile kernel: one thread block = 128 query rows of one (sequence, head); 128 threads, thread t owns row t.
 //   * Q (128 x 128), K tile (128 keys x 128) and V tile live in shared memory as two 128-byte-wide
 //     panels each, written by TMA with the 128-byte swizzle -- exactly the canonical layout the
 //     UMMA shared-memory descriptors expect (Q, K: K-major; V: MN-major, so the row-major V tile

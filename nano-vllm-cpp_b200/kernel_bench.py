@@ -261,7 +261,7 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
                        "note": "logical layers are mapped round-robin onto the physical caches that fit in HBM",
                        "bytes_per_layer": bytes_layer, "prefill_flops_per_layer": flops_layer,
                        "l2": "each layer cache (GiB) exceeds the 126 MB L2"},
-            "roofline": {"bound": "hbm", "kernel": "decode_split_kernel (dominant; prefill_tc2_kernel second)", "achieved": ach,
+            "roofline": {"bound": "hbm", "kernel": "decode_split_kernel (dominant; prefill_tc4_kernel second)", "achieved": ach,
                          "peak": hbm, "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm,
                          "ideal_ms_per_step": ideal_ms, "frac_of_ideal_time": ideal_ms / mean_ms, "traffic": None},
             "gpu_launches": steps * layers * 5}
