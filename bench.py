@@ -394,8 +394,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed"],
-                    help="decode is the benchmark; the others time the remaining kernels of the path (1 GPU)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e"],
+                    help="decode is the benchmark; prefill / store / prologue / mixed time the remaining kernels of the path "
+                         "(1 GPU); e2e reports output tokens per second of the whole decoder, tensor-parallel over --gpus")
+    ap.add_argument("--e2e-layers", type=int, default=36, help="e2e workload: decoder layers (36 = the named model)")
+    ap.add_argument("--e2e-seqs", type=int, default=256, help="e2e workload: number of sequences")
+    ap.add_argument("--e2e-maxlen", type=int, default=1024, help="e2e workload: longest prompt / output")
+    ap.add_argument("--no-graph", action="store_true", help="e2e workload: run decode steps eagerly")
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
                     help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")
     ap.add_argument("--layers", type=int, default=36, help="mixed workload: layer caches per step")
@@ -417,6 +422,31 @@ def main():
             return 0
         torch.cuda.set_device(0)
         print(json.dumps(run_reference(args, torch, torch.device("cuda:0"))), flush=True)
+        return 0
+
+    if args.workload == "e2e":
+        dist = None
+        torch.cuda.set_device(local_rank)
+        if world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+        nvk = entry.load_package()
+        nvk.lib()
+        importlib = __import__("importlib")
+        eb = importlib.import_module(entry.PKG_NAME + ".e2e_bench")
+        em = importlib.import_module(entry.PKG_NAME + ".e2e_model")
+        sampler = ClockSampler(physical_gpu_index(local_rank)) if rank == 0 else None
+        if sampler:
+            sampler.start()
+        line = eb.run_e2e(nvk, torch, dist, rank, world, torch.device(f"cuda:{local_rank}"),
+                          em.DecoderConfig(layers=args.e2e_layers), num_seqs=args.e2e_seqs,
+                          len_lo=min(100, args.e2e_maxlen), len_hi=args.e2e_maxlen, use_graph=not args.no_graph)
+        if sampler:
+            line["clocks"] = sampler.finish()
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
         return 0
 
     if args.workload != "decode":

@@ -1,0 +1,166 @@
+"""End-to-end Qwen3-style decoder used ONLY to measure output tokens per second around the attention path.
+
+What is the product here and what is plumbing: every attention-side operation -- the decode prologue
+(split + q/k RMSNorm + RoPE + cache store), paged decode attention, paged varlen prefill attention -- goes through
+the C ABI of ``libnvk.so``.  Everything else a decoder needs (embedding, the four linears per layer as plain cuBLAS
+GEMMs through ``torch.matmul``, residual RMSNorm, SiLU-gate, greedy sampling, the NCCL all-reduce after o_proj and
+down_proj) is torch plumbing with random-init weights; it mirrors the shapes and the tensor-parallel sharding of the
+reference (QKV / gate-up column-parallel by head, o_proj / down_proj row-parallel followed by an all-reduce:
+src/layers/linear.cpp:306-366; vocabulary-parallel head with a gather for greedy sampling) so that the attention
+calls see exactly the per-rank shapes of a real run: ``Hq/t`` query heads, ``Hkv/t`` KV heads, a private cache.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+
+
+@dataclass
+class DecoderConfig:
+    layers: int = 36
+    hidden: int = 4096
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 12288
+    vocab: int = 151936
+    eps: float = 1e-6
+    rope_theta: float = 1e6
+    block_size: int = 256
+    max_model_len: int = 4096
+    max_num_seqs: int = 512
+    max_num_batched_tokens: int = 16384
+
+
+def rope_table(torch, dev, max_positions, head_dim, theta):
+    """fp32 [max_positions, head_dim] = [cos | sin], inv_freq = theta^(-2i/D) (src/layers/rotary_embedding.cpp:35-47)."""
+    inv = 1.0 / torch.pow(torch.tensor(float(theta), device=dev),
+                          torch.arange(0, head_dim, 2, device=dev, dtype=torch.float32) / head_dim)
+    ang = torch.arange(max_positions, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.cat([torch.cos(ang), torch.sin(ang)], dim=1).contiguous()
+
+
+class Decoder:
+    """One tensor-parallel rank of the decoder."""
+
+    def __init__(self, nvk, torch, dev, cfg: DecoderConfig, rank=0, world=1, dist=None, num_blocks=0, seed=0):
+        if cfg.num_kv_heads % world or cfg.ffn % world or cfg.vocab % world:
+            raise ValueError("heads, ffn and vocab must divide by the tensor-parallel size")
+        self.nvk, self.torch, self.dev, self.cfg = nvk, torch, dev, cfg
+        self.rank, self.world, self.dist = rank, world, dist
+        self.hq, self.hkv = cfg.num_heads // world, cfg.num_kv_heads // world
+        self.ffn, self.vocab = cfg.ffn // world, cfg.vocab // world
+        bf = torch.bfloat16
+        d, hid = cfg.head_dim, cfg.hidden
+        gen = torch.Generator(device=dev)
+
+        def weight(tag, rows, cols, row_lo, row_hi, col_lo=0, col_hi=None, std=0.02):
+            # every rank draws the same full matrix from the same seed and keeps its shard
+            gen.manual_seed(seed * 1000003 + tag)
+            full = torch.randn((rows, cols), generator=gen, device=dev, dtype=torch.float32).mul_(std).to(bf)
+            return full[row_lo:row_hi, col_lo:(cols if col_hi is None else col_hi)].contiguous()
+
+        r = rank
+        self.embed = weight(1, cfg.vocab, hid, 0, cfg.vocab)
+        self.lm_head = weight(2, cfg.vocab, hid, r * self.vocab, (r + 1) * self.vocab)
+        self.final_norm = torch.ones(hid, device=dev, dtype=bf)
+        self.layers = []
+        for l in range(cfg.layers):
+            t = 100 + 10 * l
+            wq = weight(t, cfg.num_heads * d, hid, r * self.hq * d, (r + 1) * self.hq * d)
+            wk = weight(t + 1, cfg.num_kv_heads * d, hid, r * self.hkv * d, (r + 1) * self.hkv * d)
+            wv = weight(t + 2, cfg.num_kv_heads * d, hid, r * self.hkv * d, (r + 1) * self.hkv * d)
+            gate = weight(t + 4, cfg.ffn, hid, r * self.ffn, (r + 1) * self.ffn)
+            up = weight(t + 5, cfg.ffn, hid, r * self.ffn, (r + 1) * self.ffn)
+            self.layers.append({
+                "w_qkv": torch.cat([wq, wk, wv], dim=0).contiguous(),
+                "w_o": weight(t + 3, hid, cfg.num_heads * d, 0, hid, r * self.hq * d, (r + 1) * self.hq * d),
+                "w_gate_up": torch.cat([gate, up], dim=0).contiguous(),
+                "w_down": weight(t + 6, hid, cfg.ffn, 0, hid, r * self.ffn, (r + 1) * self.ffn),
+                "norm_in": torch.ones(hid, device=dev, dtype=bf), "norm_post": torch.ones(hid, device=dev, dtype=bf),
+                "q_norm": torch.ones(d, device=dev, dtype=bf), "k_norm": torch.ones(d, device=dev, dtype=bf),
+            })
+            del wq, wk, wv, gate, up
+        self.cos_sin = rope_table(torch, dev, cfg.max_model_len, d, cfg.rope_theta)
+        self.scale = 1.0 / math.sqrt(d)
+        # [2, layers, blocks, block_size, Hkv/t, D] as in allocate_kv_cache (src/engine/model_runner.cpp:355-472)
+        self.num_blocks = int(num_blocks)
+        self.kv_cache = torch.zeros((2, cfg.layers, self.num_blocks, cfg.block_size, self.hkv, d), device=dev, dtype=bf)
+        self.workspace = None
+
+    # ---- pieces ---------------------------------------------------------------------------------------------
+    def rmsnorm(self, x, w):
+        return self.torch.nn.functional.rms_norm(x, (x.shape[-1],), w, self.cfg.eps)
+
+    def all_reduce(self, x):
+        if self.world > 1:
+            self.dist.all_reduce(x)
+        return x
+
+    def ensure_workspace(self, batch, table_width):
+        need = self.nvk.decode_attention_workspace_bytes(batch, self.hq, self.hkv, self.cfg.head_dim, table_width,
+                                                         self.cfg.block_size)
+        if self.workspace is None or self.workspace.numel() < need:
+            self.workspace = self.torch.empty(max(need, 1), device=self.dev, dtype=self.torch.uint8)
+
+    def forward(self, tokens, positions, slot_mapping, attend):
+        """Hidden states after the last layer.  ``attend(layer_index, q, out)`` runs attention for one layer."""
+        torch, nvk, cfg = self.torch, self.nvk, self.cfg
+        h = self.embed[tokens]
+        n = h.shape[0]
+        q = torch.empty((n, self.hq, cfg.head_dim), device=self.dev, dtype=h.dtype)
+        attn = torch.empty_like(q)
+        for l, w in enumerate(self.layers):
+            x = self.rmsnorm(h, w["norm_in"])
+            qkv = x @ w["w_qkv"].t()
+            nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, slot_mapping,
+                                            self.kv_cache[0, l], self.kv_cache[1, l], self.hq, self.hkv, cfg.head_dim, q)
+            attend(l, q, attn)
+            h = h + self.all_reduce(attn.view(n, -1) @ w["w_o"].t())
+            x = self.rmsnorm(h, w["norm_post"])
+            gu = x @ w["w_gate_up"].t()
+            act = torch.nn.functional.silu(gu[:, :self.ffn]) * gu[:, self.ffn:]
+            h = h + self.all_reduce(act @ w["w_down"].t())
+        return h
+
+    def sample(self, h_rows):
+        """Greedy sampling over the vocabulary shards: local max and arg-max, then one gather."""
+        torch = self.torch
+        logits = (self.rmsnorm(h_rows, self.final_norm) @ self.lm_head.t()).float()
+        val, idx = logits.max(dim=-1)
+        if self.world == 1:
+            return idx
+        pair = torch.stack([val, (idx + self.rank * self.vocab).float()], dim=-1).contiguous()   # ids < 2^24: exact
+        gathered = torch.empty((self.world,) + pair.shape, device=self.dev, dtype=pair.dtype)
+        self.dist.all_gather_into_tensor(gathered, pair)
+        best = gathered[..., 0].argmax(dim=0)
+        return gathered[..., 1].gather(0, best[None, :])[0].long()
+
+    # ---- steps ----------------------------------------------------------------------------------------------
+    def prefill_step(self, arrays):
+        """One prefill step over whole prompts; returns the first sampled token of every sequence."""
+        torch, nvk, cfg, dev = self.torch, self.nvk, self.cfg, self.dev
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory().to(dev, non_blocking=True)  # noqa: E731
+        tokens, positions, slots = up(arrays["tokens"]), up(arrays["positions"]), up(arrays["slot_mapping"])
+        cu_q, cu_k, tables = up(arrays["cu_seqlens_q"]), up(arrays["cu_seqlens_k"]), up(arrays["block_tables"])
+
+        def attend(l, q, out):
+            nvk.launch_prefill_attention_paged(q, cu_q, self.kv_cache[0, l], self.kv_cache[1, l], cu_k, tables, self.hkv,
+                                               cfg.head_dim, cfg.block_size, self.scale, out)
+
+        h = self.forward(tokens, positions, slots, attend)
+        return self.sample(h[up(arrays["last_rows"])])
+
+    def decode_forward(self, tokens, meta):
+        """One decode step on static buffers (capturable): ``meta`` int32 [B, 3 + W] = position, slot, context_len, table."""
+        nvk, cfg = self.nvk, self.cfg
+        positions, slots, ctx = meta[:, 0].contiguous(), meta[:, 1].contiguous(), meta[:, 2].contiguous()
+        tables = meta[:, 3:].contiguous()
+
+        def attend(l, q, out):
+            nvk.launch_decode_attention_paged(q, self.kv_cache[0, l], self.kv_cache[1, l], ctx, tables, self.hkv,
+                                              cfg.head_dim, cfg.block_size, self.scale, out, self.workspace)
+
+        return self.sample(self.forward(tokens, positions, slots, attend))
