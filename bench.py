@@ -449,6 +449,32 @@ def main():
             dist.destroy_process_group()
         return 0
 
+    if args.workload == "mixed" and world > 1:
+        # config 4 with all 36 layer caches resident: KV-head shards, one per GPU, no collective inside attention
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+        nvk = entry.load_package()
+        nvk.lib()
+        kb = __import__("importlib").import_module(entry.PKG_NAME + ".kernel_bench")
+        dev = torch.device(f"cuda:{local_rank}")
+        if CFG["num_kv_heads"] % world:
+            raise SystemExit("--gpus must divide the number of KV heads")
+        dist.barrier()
+        line = kb.bench_mixed(nvk, torch, dev, min(args.steps, 10), min(args.warmup, 3), layers=args.layers,
+                              hq=CFG["num_heads"] // world, hkv=CFG["num_kv_heads"] // world)
+        t = torch.tensor([line["ms_per_step"]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            ms = float(t.item())
+            line["value"] = line["value"] * line["ms_per_step"] / ms * world     # bytes of all shards / slowest rank
+            line["roofline"]["note"] = "roofline figures are rank 0's shard"
+            line.update({"ms_per_step": ms, "n_gpus": world, "scaling": "strong"})
+            line["config"]["parallelism"] = f"tp{world}: {CFG['num_kv_heads'] // world} KV heads per GPU, replicated metadata"
+            print(json.dumps(line), flush=True)
+        dist.destroy_process_group()
+        return 0
+
     if args.workload != "decode":
         if rank != 0:
             return 0

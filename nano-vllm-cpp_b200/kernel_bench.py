@@ -182,7 +182,7 @@ def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
 
 
 def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_lo=512, ctx_hi=16384, prefill_seqs=4,
-                prefill_len=2048, mem_fraction=0.80):
+                prefill_len=2048, mem_fraction=0.80, hq=HQ, hkv=HKV):
     """Config 4: one continuous-batching step of attention over ``layers`` layer caches -- per layer the store of the
     prefill tokens, the varlen prefill (no prefix), the store of the decode tokens and the paged decode attention,
     all on one stream (the reference never fuses prefill and decode into one launch, src/engine/scheduler.cpp:65-67).
@@ -195,7 +195,7 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
     dec_blocks = int(((ctx.astype(np.int64) + BS - 1) // BS).sum())
     pre_blocks = prefill_seqs * ((prefill_len + BS - 1) // BS)
     pool = dec_blocks + pre_blocks
-    bytes_per_layer = 2 * pool * BS * HKV * D * 2
+    bytes_per_layer = 2 * pool * BS * hkv * D * 2
     free, _ = torch.cuda.mem_get_info(dev)
     phys = int(max(1, min(layers, (free * mem_fraction) // bytes_per_layer)))
     bf = torch.bfloat16
@@ -215,39 +215,39 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
         pblocks = perm[at:at + pre_blocks].reshape(prefill_seqs, -1)
         pos = np.arange(prefill_len)
         pslots = np.concatenate([pblocks[s, pos // BS].astype(np.int64) * BS + pos % BS for s in range(prefill_seqs)]).astype(np.int32)
-        kc = torch.empty((pool, BS, HKV, D), device=dev, dtype=bf).normal_(generator=gen)
-        vc = torch.empty((pool, BS, HKV, D), device=dev, dtype=bf).normal_(generator=gen)
+        kc = torch.empty((pool, BS, hkv, D), device=dev, dtype=bf).normal_(generator=gen)
+        vc = torch.empty((pool, BS, hkv, D), device=dev, dtype=bf).normal_(generator=gen)
         caches.append({"k": kc, "v": vc, "tables": torch.from_numpy(tables).to(dev), "dslots": torch.from_numpy(dslots).to(dev),
                        "pslots": torch.from_numpy(pslots).to(dev)})
     total_pq = prefill_seqs * prefill_len
     cu = torch.arange(0, total_pq + 1, prefill_len, dtype=torch.int32, device=dev)
-    pq = torch.randn((total_pq, HQ, D), generator=gen, device=dev).to(bf)
-    pk = torch.randn((total_pq, HKV, D), generator=gen, device=dev).to(bf)
-    pv = torch.randn((total_pq, HKV, D), generator=gen, device=dev).to(bf)
+    pq = torch.randn((total_pq, hq, D), generator=gen, device=dev).to(bf)
+    pk = torch.randn((total_pq, hkv, D), generator=gen, device=dev).to(bf)
+    pv = torch.randn((total_pq, hkv, D), generator=gen, device=dev).to(bf)
     pout = torch.empty_like(pq)
-    dq = torch.randn((decode_seqs, HQ, D), generator=gen, device=dev).to(bf)
-    dk = torch.randn((decode_seqs, HKV, D), generator=gen, device=dev).to(bf)
-    dv = torch.randn((decode_seqs, HKV, D), generator=gen, device=dev).to(bf)
+    dq = torch.randn((decode_seqs, hq, D), generator=gen, device=dev).to(bf)
+    dk = torch.randn((decode_seqs, hkv, D), generator=gen, device=dev).to(bf)
+    dv = torch.randn((decode_seqs, hkv, D), generator=gen, device=dev).to(bf)
     dout = torch.empty_like(dq)
     ctx_dev = torch.from_numpy(ctx).to(dev)
     scale = 1.0 / math.sqrt(D)
     max_blocks = caches[0]["tables"].shape[1]
-    ws = torch.empty(max(16, nvk.decode_attention_workspace_bytes(decode_seqs, HQ, HKV, D, max_blocks, BS)), dtype=torch.uint8, device=dev)
+    ws = torch.empty(max(16, nvk.decode_attention_workspace_bytes(decode_seqs, hq, hkv, D, max_blocks, BS)), dtype=torch.uint8, device=dev)
 
     def step():
         for layer in range(layers):
             c = caches[layer % phys]
             nvk.store_kvcache(pk, pv, c["k"], c["v"], c["pslots"])
-            nvk.launch_prefill_attention_dense(pq, cu, pk, pv, cu, HKV, D, scale, pout)
+            nvk.launch_prefill_attention_dense(pq, cu, pk, pv, cu, hkv, D, scale, pout)
             nvk.store_kvcache(dk, dv, c["k"], c["v"], c["dslots"])
-            nvk.launch_decode_attention_paged(dq, c["k"], c["v"], ctx_dev, c["tables"], HKV, D, BS, scale, dout, ws)
+            nvk.launch_decode_attention_paged(dq, c["k"], c["v"], ctx_dev, c["tables"], hkv, D, BS, scale, dout, ws)
 
     mean_ms, med_ms = _time(torch, step, steps, warmup)
-    dec_bytes = int(ctx.astype(np.int64).sum()) * 2 * HKV * D * 2 + 2 * decode_seqs * HQ * D * 2
-    pre_bytes = 2 * total_pq * HQ * D * 2 + 2 * total_pq * HKV * D * 2
-    store_bytes = 2 * (2 * (total_pq + decode_seqs) * HKV * D * 2)
+    dec_bytes = int(ctx.astype(np.int64).sum()) * 2 * hkv * D * 2 + 2 * decode_seqs * hq * D * 2
+    pre_bytes = 2 * total_pq * hq * D * 2 + 2 * total_pq * hkv * D * 2
+    store_bytes = 2 * (2 * (total_pq + decode_seqs) * hkv * D * 2)
     bytes_layer = dec_bytes + pre_bytes + store_bytes
-    flops_layer = prefill_seqs * 4 * HQ * D * (prefill_len * (prefill_len + 1) // 2)
+    flops_layer = prefill_seqs * 4 * hq * D * (prefill_len * (prefill_len + 1) // 2)
     hbm, tf, kind = _peaks()
     ideal_ms = layers * (dec_bytes / (hbm * 1e9) + flops_layer / (tf * 1e12)) * 1e3
     ach = layers * bytes_layer / (mean_ms * 1e-3) / 1e9
