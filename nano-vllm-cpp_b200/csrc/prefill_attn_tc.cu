@@ -33,8 +33,10 @@
 #include <cuda.h>
 
 #include <cmath>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
+#include <utility>
 
 namespace nvk {
 namespace {
@@ -122,6 +124,33 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
+// SS MMA whose descriptors are a base descriptor plus a compile-time offset of the 14-bit start-address field
+// (units of 16 bytes).  The adds sit inside the volatile asm, so the compiler cannot precompute (and then keep in
+// registers, or spill) one descriptor pair per MMA of an unrolled loop: the issuing thread stays small.
+template <int A_OFF16, int B_OFF16>
+__device__ __forceinline__ void umma_ss_off(uint32_t d_tmem, uint64_t a_base, uint64_t b_base, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "add.u64 da, %1, %5;\n\t"
+        "add.u64 db, %2, %6;\n\t"
+        "setp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}\n"
+        :: "r"(d_tmem), "l"(a_base), "l"(b_base), "r"(idesc), "r"(acc), "n"(A_OFF16), "n"(B_OFF16) : "memory");
+}
+constexpr int kmajor_off16(int step) { return ((step / 4) * kPanelBytes + (step % 4) * 32) / 16; }
+// The 8 K-steps of S = Q K^T (both operands K-major: two 64-element panels, 32 bytes per step inside a panel).
+template <int... KS>
+__device__ __forceinline__ void umma_scores(std::integer_sequence<int, KS...>, uint32_t d_tmem, uint64_t q_base, uint64_t k_base,
+                                            uint32_t idesc) {
+    (umma_ss_off<kmajor_off16(KS), kmajor_off16(KS)>(d_tmem, q_base, k_base, idesc, KS > 0 ? 1u : 0u), ...);
+}
+// The 8 K-steps of O += P V (P K-major as above, V MN-major: 2048 bytes per 16 keys).
+template <int... KK>
+__device__ __forceinline__ void umma_pv(std::integer_sequence<int, KK...>, uint32_t d_tmem, uint64_t p_base, uint64_t v_base,
+                                        uint32_t idesc, uint32_t acc_first) {
+    (umma_ss_off<kmajor_off16(KK), KK * 2048 / 16>(d_tmem, p_base, v_base, idesc, KK > 0 ? 1u : acc_first), ...);
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -934,6 +963,11 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
                                                     bool need_mask, int key0, int lim, float scale_log2, bool first,
                                                     float& m_ref, float& l_run, uint32_t pv_done_bar, uint32_t pv_done_parity,
                                                     volatile int* abort_flag, OnRead on_scores_read) {
+#if defined(NVK_TC4_EXP) && NVK_TC4_EXP >= 3
+    on_scores_read();
+    if (!first && !warp_mbar_wait(pv_done_bar, pv_done_parity, abort_flag, 42)) return false;
+    return true;
+#endif
     uint32_t r0[32], r1[32], r2[32], r3[32];
     tmem_ld32(t_s, r0);
     tmem_ld32(t_s + 32, r1);
@@ -1271,6 +1305,417 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
 }
 
+// =================================================================================================
+// Version 5: version 4 made persistent.  One block per SM takes (query tile, head pair) items from a
+// ticket counter, heaviest query tiles first, and keeps TMEM, barriers and the three warp roles alive
+// across items: while the softmax warps write one item's output (staged in the P buffer, which the
+// last P.V has finished with), the producer has already fetched the next item's Q and first K tiles and
+// the issuer has its first score MMAs in flight.  A block launched per item pays the fill and drain of
+// the chain load -> S -> softmax -> P.V -> store (about 1.5 rounds) every time; here only the first
+// and last item of a block do.  All barrier phases are counted cumulatively over items.
+// =================================================================================================
+constexpr int kTicketSlots = 64;
+#ifndef NVK_TC5_REGS
+#define NVK_TC5_REGS 1
+#define NVK_TC5_REGS_LOW 56
+#define NVK_TC5_REGS_HIGH 224
+#endif
+constexpr int kThreads5 = NVK_TC5_REGS ? 384 : 320;   // three warpgroups (register reallocation works on whole warpgroups)
+__device__ unsigned int g_prefill_ticket[kTicketSlots];
+__device__ unsigned int g_prefill_done[kTicketSlots];
+
+struct Tc5Params {
+    TcParams base;
+    int pairs;            // head pairs
+    int tiles;            // upper bound of query tiles over all sequences
+    unsigned int total;   // pairs * tiles
+    int slot;             // ticket counter of this launch
+};
+
+struct Tc5Item {          // one (query tile, head pair), published by the producer warp
+    int kind;             // 1 = work, 0 = no more work
+    int seq, q0, pair;
+};
+
+// Geometry of an item, derived identically by every role from (seq, q0).
+struct Tc5Geom {
+    int64_t qb, kb;
+    int q_len, k_len, rows_here, shift, num_kt, last_partial;
+};
+__device__ __forceinline__ Tc5Geom tc5_geometry(const TcParams& p, int seq, int q0) {
+    Tc5Geom g;
+    if (p.cu_q == nullptr) { g.qb = 0; g.kb = 0; g.q_len = static_cast<int>(p.total_q); g.k_len = static_cast<int>(p.total_k); }
+    else {
+        g.qb = p.cu_q[seq]; g.kb = p.cu_k[seq];
+        g.q_len = p.cu_q[seq + 1] - static_cast<int>(g.qb); g.k_len = p.cu_k[seq + 1] - static_cast<int>(g.kb);
+    }
+    g.rows_here = min(kBM, g.q_len - q0);
+    g.shift = g.k_len - g.q_len;
+    int k_hi = g.shift + q0 + g.rows_here;
+    if (k_hi > g.k_len) k_hi = g.k_len;
+    g.num_kt = k_hi > 0 ? (k_hi + kBN - 1) / kBN : 0;
+    g.last_partial = (g.num_kt * kBN > g.k_len) ? g.num_kt - 1 : -1;
+    return g;
+}
+
+// Query tile number `want` (0 = first tile of the first sequence) -> (seq, q0); false when past the end.
+__device__ __forceinline__ bool tc5_locate(const TcParams& p, int64_t want, int& seq, int& q0) {
+    if (p.cu_q == nullptr) {
+        if (want * kBM >= p.total_q) return false;
+        seq = 0; q0 = static_cast<int>(want * kBM);
+        return true;
+    }
+    int64_t acc = 0;
+    for (int64_t s = 0; s < p.num_seqs; ++s) {
+        const int64_t tiles = (static_cast<int64_t>(p.cu_q[s + 1]) - p.cu_q[s] + kBM - 1) / kBM;
+        if (want < acc + tiles) { seq = static_cast<int>(s); q0 = static_cast<int>((want - acc) * kBM); return true; }
+        acc += tiles;
+    }
+    return false;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads5, 1)
+prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const Tc5Params pp) {
+    const TcParams& p = pp.base;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+    __shared__ Tc5Item s_ring[4];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned long long dbg_t0 = 0;
+    if (p.dbg_clk != nullptr && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(dbg_t0));
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t sm_q = smem_base + kOff4Q, sm_k = smem_base + kOff4K, sm_v = smem_base + kOff4V, sm_p = smem_base + kOff4P;
+    const uint32_t bars = smem_base + kOff4Bar;
+    const uint32_t bar_qfull = bars, bar_vfix = bars + 8, bar_vfull = bars + 16, bar_vempty = bars + 24, bar_qempty = bars + 144;
+    auto bar_kfull = [&](int s) { return bars + 32 + 8 * s; };
+    auto bar_kempty = [&](int s) { return bars + 48 + 8 * s; };
+    auto bar_sfull = [&](int t) { return bars + 64 + 8 * t; };
+    auto bar_sread = [&](int t) { return bars + 80 + 8 * t; };
+    auto bar_pfull = [&](int t) { return bars + 96 + 8 * t; };
+    auto bar_odone = [&](int t) { return bars + 112 + 8 * t; };
+    auto bar_ofinal = [&](int t) { return bars + 128 + 8 * t; };
+    auto bar_item = [&](int s) { return bars + 152 + 8 * s; };   // ring entry s published
+    volatile int* abort_flag = &s_abort;
+
+    if (tid == 0) {
+        s_abort = 0;
+        mbar_init(bar_qfull, 1); mbar_init(bar_qempty, 1); mbar_init(bar_vfix, 1); mbar_init(bar_vfull, 1); mbar_init(bar_vempty, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_kfull(i), 1); mbar_init(bar_kempty(i), 1);
+            mbar_init(bar_sfull(i), 1); mbar_init(bar_sread(i), 4); mbar_init(bar_pfull(i), 4);
+            mbar_init(bar_odone(i), 1); mbar_init(bar_ofinal(i), 1);
+        }
+        for (int i = 0; i < 4; ++i) mbar_init(bar_item(i), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(kTmemCols2) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    const size_t out_stride = static_cast<size_t>(p.num_heads) * kHeadDim;
+
+    // Three warpgroups: 0 and 1 are the softmax warps of tile 0 and 1, 2 holds the issuer, the producer and two idle
+    // warps.  The block starts with 168 registers per thread (the cap of 384 threads); the third warpgroup hands
+    // most of its registers back and the softmax warpgroups grow to 224, which holds a whole 128-key score row, its
+    // probabilities and the step's state without spilling.
+
+    if (warp >= 8) {
+#if NVK_TC5_REGS
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(NVK_TC5_REGS_LOW));
+#endif
+    if (warp == 9) {
+        // ------------------------------------------------------------------ ticket taker + TMA producer
+        int n = 0;            // items published so far (all of them carry work)
+        int gk = 0, gv = 0;   // K / V tiles loaded so far, over all items
+        bool ok = true;
+        // Next item that carries work (whole warp; lane 0 takes the tickets).  Tiles past the last sequence are
+        // skipped, tiles whose rows see no key are zero-filled right here and never published.
+        auto take_item = [&](int& kind, int& seq, int& q0, int& pair, Tc5Geom& g) {
+            while (true) {
+                kind = 0; seq = 0; q0 = 0; pair = 0;
+                if (lane == 0) {
+                    while (true) {
+                        const unsigned int ticket = atomicAdd(&g_prefill_ticket[pp.slot], 1u);
+                        if (ticket >= pp.total) break;
+                        pair = static_cast<int>(ticket % static_cast<unsigned int>(pp.pairs));
+                        const int64_t want = static_cast<int64_t>(pp.tiles) - 1 - static_cast<int64_t>(ticket / static_cast<unsigned int>(pp.pairs));
+                        if (tc5_locate(p, want, seq, q0)) { kind = 1; break; }
+                    }
+                }
+                kind = __shfl_sync(0xffffffffu, kind, 0);
+                seq = __shfl_sync(0xffffffffu, seq, 0);
+                q0 = __shfl_sync(0xffffffffu, q0, 0);
+                pair = __shfl_sync(0xffffffffu, pair, 0);
+                if (!kind) return;
+                g = tc5_geometry(p, seq, q0);
+                if (g.num_kt > 0) return;
+                for (int t = 0; t < 2; ++t) {
+                    T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(g.qb + q0) * p.num_heads + 2 * pair + t) * kHeadDim;
+                    for (int i = lane; i < g.rows_here * (kHeadDim / 8); i += 32) {
+                        const int r = i / (kHeadDim / 8), c = i % (kHeadDim / 8);
+                        *reinterpret_cast<uint4*>(o0 + r * out_stride + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
+        };
+        int kind = 0, seq = 0, q0 = 0, pair = 0;
+        Tc5Geom g{};
+        int nkind = 0, nseq = 0, nq0 = 0, npair = 0;
+        Tc5Geom ng{};
+        take_item(nkind, nseq, nq0, npair, ng);
+        while (ok) {
+            kind = nkind; seq = nseq; q0 = nq0; pair = npair; g = ng;
+            if (lane == 0) {
+                Tc5Item it;
+                it.kind = kind; it.seq = seq; it.q0 = q0; it.pair = pair;
+                s_ring[n & 3] = it;
+                mbar_arrive(bar_item(n & 3));   // release: the entry is visible to whoever waits on the barrier
+            }
+            if (!kind) break;
+            const int head0 = 2 * pair;
+            const int kvh = head0 * p.num_kv_heads / p.num_heads;
+            const int32_t* table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : nullptr;
+            auto key_row = [&](int key0) -> int {
+                if (table) {
+                    const int id = table[key0 / p.block_size];
+                    if (id < 0 || id >= p.num_cache_blocks) return static_cast<int>(p.key_rows);
+                    return id * p.block_size + key0 % p.block_size;
+                }
+                return static_cast<int>(g.kb) + key0;
+            };
+            auto load_k = [&](int j) -> bool {   // lane 0 only
+                const int c = gk + j, s = c & 1;
+                if (c >= 2 && !mbar_wait(bar_kempty(s), ((c >> 1) & 1) ^ 1, abort_flag, 11)) return false;
+                const int r = key_row(j * kBN);
+                mbar_expect_tx(bar_kfull(s), kTileBytes);
+                tma_load_3d(sm_k + s * kTileBytes, &tm_k, 0, kvh, r, bar_kfull(s));
+                tma_load_3d(sm_k + s * kTileBytes + kPanelBytes, &tm_k, 64, kvh, r, bar_kfull(s));
+                return true;
+            };
+            if (lane == 0) {
+                if (n >= 1) ok = mbar_wait(bar_qempty, (n - 1) & 1, abort_flag, 14);   // previous item's score MMAs are done with Q
+                if (ok) {
+                    mbar_expect_tx(bar_qfull, 2 * kTileBytes);
+                    for (int t = 0; t < 2; ++t) {
+                        tma_load_3d(sm_q + t * kTileBytes, &tm_q, 0, head0 + t, static_cast<int>(g.qb) + q0, bar_qfull);
+                        tma_load_3d(sm_q + t * kTileBytes + kPanelBytes, &tm_q, 64, head0 + t, static_cast<int>(g.qb) + q0, bar_qfull);
+                    }
+                    ok = load_k(0);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            // the next ticket, its sequence look-up and geometry are fetched now, under this item's rounds
+            if (ok) take_item(nkind, nseq, nq0, npair, ng);
+            for (int j = 0; j < g.num_kt && ok; ++j) {
+                const int cv = gv + j;
+                if (lane == 0) {
+                    if (j + 1 < g.num_kt) ok = load_k(j + 1);            // K runs one tile ahead of V
+                    if (ok && cv >= 1) ok = mbar_wait(bar_vempty, (cv - 1) & 1, abort_flag, 12);
+                    if (ok) {
+                        const int r = key_row(j * kBN);
+                        mbar_expect_tx(bar_vfull, kTileBytes);
+                        tma_load_3d(sm_v, &tm_v, 0, kvh, r, bar_vfull);
+                        tma_load_3d(sm_v + kPanelBytes, &tm_v, 64, kvh, r, bar_vfull);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (ok && j == g.last_partial) {
+                    // rows of V past the sequence may hold anything (0 * NaN = NaN): zero them once landed
+                    ok = warp_mbar_wait(bar_vfull, cv & 1, abort_flag, 13);
+                    if (ok) {
+                        const int first_bad = g.k_len - j * kBN;   // in (0, 128)
+                        for (int i = lane; i < (kBN - first_bad) * 16; i += 32) {
+                            const int r = first_bad + i / 16, c16 = i % 16;
+                            *reinterpret_cast<uint4*>(smem_gen + kOff4V + (c16 >> 3) * kPanelBytes + r * 128 + (c16 & 7) * 16) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_vfix);
+                    }
+                }
+            }
+            gk += g.num_kt; gv += g.num_kt; ++n;
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int n = 0, G = 0, gk = 0, gv = 0, nf = 0;   // items, rounds, K tiles, V tiles, partial-tile fixes so far
+            bool ok = true;
+            // One base descriptor per operand buffer; a tile-internal offset only moves the 14-bit start-address
+            // field (units of 16 bytes, never carrying out of it), so each MMA's descriptors are one add away and
+            // the issuer needs few registers.
+            const uint64_t dq[2] = {make_smem_desc(sm_q, 16, 1024), make_smem_desc(sm_q + kTileBytes, 16, 1024)};
+            const uint64_t dk[2] = {make_smem_desc(sm_k, 16, 1024), make_smem_desc(sm_k + kTileBytes, 16, 1024)};
+            const uint64_t dp[2] = {make_smem_desc(sm_p, 16, 1024), make_smem_desc(sm_p + kTileBytes, 16, 1024)};
+            const uint64_t dv = make_smem_desc(sm_v, kPanelBytes, 1024);
+            while (ok) {
+                ok = mbar_wait(bar_item(n & 3), (n >> 2) & 1, abort_flag, 28);
+                if (!ok) break;
+                const Tc5Item it = s_ring[n & 3];
+                if (it.kind == 0) break;
+                const Tc5Geom g = tc5_geometry(p, it.seq, it.q0);
+                auto issue_s = [&](int t, int j) {
+                    const int s = (gk + j) & 1;
+                    umma_scores(std::make_integer_sequence<int, 8>{}, tmem_base + t * 128, dq[t], dk[s], p.idesc_s);
+                    tc_commit(bar_sfull(t));
+                };
+                // scores of the item's first key tile: Q and K(0) landed, the previous round's scores were read
+                ok = mbar_wait(bar_qfull, n & 1, abort_flag, 21) && mbar_wait(bar_kfull(gk & 1), (gk >> 1) & 1, abort_flag, 22);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (G >= 1) ok = mbar_wait(bar_sread(t), (G - 1) & 1, abort_flag, 29);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(t, 0);
+                }
+                if (!ok) break;
+                tc_commit(bar_kempty(gk & 1));
+                if (g.num_kt == 1) tc_commit(bar_qempty);   // every score MMA of the item has been issued
+                for (int j = 0; j < g.num_kt && ok; ++j) {
+                    if (j + 1 < g.num_kt) {   // next scores as soon as this step's scores have been read
+                        const int c = gk + j + 1;
+                        ok = mbar_wait(bar_kfull(c & 1), (c >> 1) & 1, abort_flag, 26);
+                        for (int t = 0; t < 2 && ok; ++t) {
+                            ok = mbar_wait(bar_sread(t), (G + j) & 1, abort_flag, 27);
+                            if (!ok) break;
+                            tc_fence_after();
+                            issue_s(t, j + 1);
+                        }
+                        if (!ok) break;
+                        tc_commit(bar_kempty(c & 1));
+                        if (j + 2 == g.num_kt) tc_commit(bar_qempty);
+                    }
+                    ok = mbar_wait(bar_vfull, (gv + j) & 1, abort_flag, 23);
+                    if (ok && j == g.last_partial) ok = mbar_wait(bar_vfix, nf & 1, abort_flag, 24);
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        // p_full of an item's first round also says that the previous item's output has left TMEM
+                        ok = mbar_wait(bar_pfull(t), (G + j) & 1, abort_flag, 25);
+                        if (!ok) break;
+                        tc_fence_after();
+                        umma_pv(std::make_integer_sequence<int, 8>{}, tmem_base + 256 + t * 128, dp[t], dv, p.idesc_pv, j > 0 ? 1u : 0u);
+                        tc_commit(bar_odone(t));
+                        if (j == g.num_kt - 1) tc_commit(bar_ofinal(t));
+                    }
+                    if (ok) tc_commit(bar_vempty);
+                }
+                G += g.num_kt; gk += g.num_kt; gv += g.num_kt; ++n;
+                if (g.last_partial >= 0) ++nf;
+            }
+        }
+    }
+    } else {
+#if NVK_TC5_REGS
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(NVK_TC5_REGS_HIGH));
+#endif
+        // ------------------------------------------------------------------ softmax warps (thread = row)
+        const int t = warp >> 2;
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const uint32_t t_s = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + t * 128;
+        const uint32_t t_o = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + 256 + t * 128;
+        unsigned char* p_panels = smem_gen + kOff4P + t * kTileBytes;
+        const uint32_t sread = bar_sread(t);
+        int n = 0, G = 0;
+        bool alive = true;
+        while (alive) {
+            alive = warp_mbar_wait(bar_item(n & 3), (n >> 2) & 1, abort_flag, 33);
+            if (!alive) break;
+            const Tc5Item it = s_ring[n & 3];
+            if (it.kind == 0) break;
+            const Tc5Geom g = tc5_geometry(p, it.seq, it.q0);
+            const int q0 = it.q0;
+            const int lim = min(g.shift + q0 + row + 1, g.k_len);
+            float m_ref = -INFINITY, l_run = 0.0f;
+            for (int j = 0; j < g.num_kt; ++j) {
+                alive = warp_mbar_wait(bar_sfull(t), (G + j) & 1, abort_flag, 31);
+                if (!alive) break;
+                tc_fence_after();
+                const int key0 = j * kBN;
+                const bool need_mask = key0 + kBN > min(g.shift + q0 + 1, g.k_len);
+                alive = softmax_row_to_smem<T>(t_s, t_o, p_panels, row, need_mask, key0, lim, p.scale_log2, j == 0, m_ref, l_run,
+                                               bar_odone(t), (G + j - 1) & 1, abort_flag, [&] {
+                                                   tc_fence_before();
+                                                   __syncwarp();
+                                                   if (lane == 0) mbar_arrive(sread);   // the score columns may be overwritten
+                                               });
+                if (!alive) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pfull(t));
+            }
+            if (alive) alive = warp_mbar_wait(bar_ofinal(t), n & 1, abort_flag, 32);
+            if (!alive) break;
+            tc_fence_after();
+            {
+                // The last P.V is complete, so the P buffer is free: stage this warp's 32 output rows there (16-byte
+                // chunks XOR-swizzled by row) and write them out as whole 256-byte rows.  The next item's Q is
+                // already being loaded into the Q buffer meanwhile.
+                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                unsigned char* stage = p_panels;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(t_o + c * 32, r);
+                    tc_wait_ld(); reg_fence32(r);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 v;
+                        v.x = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
+                        v.y = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
+                        v.z = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
+                        v.w = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
+                        const int chunk = c * 4 + q4;
+                        *reinterpret_cast<uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4)) = v;
+                    }
+                }
+                // O has left TMEM: the arrive on p_full in the next item's first round tells the issuer so
+                __syncwarp();
+                T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(g.qb + q0) * p.num_heads + 2 * it.pair + t) * kHeadDim;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int r = wq * 32 + 2 * i + (lane >> 4), chunk = lane & 15;
+                    if (r < g.rows_here) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4));
+                        *reinterpret_cast<uint4*>(o0 + r * out_stride + chunk * 8) = v;
+                    }
+                }
+                __syncwarp();   // the staging rows are read before the next item's probabilities overwrite them
+            }
+            G += g.num_kt; ++n;
+        }
+        if (p.dbg_clk != nullptr && tid == 0) {
+            unsigned long long t1;
+            unsigned int smid;
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
+            asm volatile("mov.u32 %0, %%smid;\n" : "=r"(smid));
+            p.dbg_clk[blockIdx.x * 4 + 0] = smid; p.dbg_clk[blockIdx.x * 4 + 1] = n;
+            p.dbg_clk[blockIdx.x * 4 + 2] = static_cast<long long>(dbg_t0); p.dbg_clk[blockIdx.x * 4 + 3] = static_cast<long long>(t1);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols2) : "memory");
+    }
+    if (tid == 0) {   // the last block to finish re-arms the ticket counter for the next launch that uses this slot
+        __threadfence();
+        if (atomicAdd(&g_prefill_done[pp.slot], 1u) == gridDim.x - 1) {
+            g_prefill_ticket[pp.slot] = 0u;
+            g_prefill_done[pp.slot] = 0u;
+            __threadfence();
+        }
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1309,15 +1754,15 @@ uint32_t make_idesc(bool bf16, bool b_mn_major) {
            (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-// Head-pair kernel used when the GQA group is even: 4 (probabilities through shared memory) unless
-// NVK_PREFILL_IMPL=tc2 asks for the version that keeps them in TMEM; NVK_PREFILL_IMPL=tc1 selects the
-// single-tile kernel for every shape (A/B comparisons).
+// Head-pair kernel used when the GQA group is even: 5 (persistent, probabilities through shared memory) unless
+// NVK_PREFILL_IMPL=tc4 asks for the one-block-per-item form of the same kernel or NVK_PREFILL_IMPL=tc2 for the
+// version that keeps the probabilities in TMEM; NVK_PREFILL_IMPL=tc1 selects the single-tile kernel for every
+// shape (A/B comparisons).
 int tc_version() {
     static const int v = [] {
         const char* e = std::getenv("NVK_PREFILL_IMPL");
-        if (e != nullptr && e[0] == 't' && e[1] == 'c' && e[2] == '1') return 1;
-        if (e != nullptr && e[0] == 't' && e[1] == 'c' && e[2] == '2') return 2;
-        return 4;
+        if (e != nullptr && e[0] == 't' && e[1] == 'c' && (e[2] == '1' || e[2] == '2' || e[2] == '4')) return e[2] - '0';
+        return 5;
     }();
     return v;
 }
@@ -1353,6 +1798,29 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
     const int64_t tiles = (a.total_q + kBM - 1) / kBM + (a.cu_q ? a.num_seqs : 0);
     if (tiles > 65535) return fail(NVK_ERR_UNSUPPORTED, "prefill attention (tcgen05): too many query tiles");
     const int group = a.num_heads / a.num_kv_heads;
+    if (group % 2 == 0 && tc_version() == 5) {   // persistent blocks, one per SM, items from a ticket counter
+        static bool attr5_done[64] = {};
+        static int sm_count[64] = {};
+        static std::atomic<unsigned int> launch_seq{0};
+        if (device >= 0 && device < 64 && !attr5_done[device]) {
+            const cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes4);
+            if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill attention (tcgen05 v5): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            if (cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count[device] <= 0)
+                return fail(NVK_ERR_CUDA, "prefill attention (tcgen05 v5): cannot read the SM count");
+            attr5_done[device] = true;
+        }
+        Tc5Params pp{};
+        pp.base = p;
+        pp.pairs = a.num_heads / 2;
+        pp.tiles = static_cast<int>(tiles);
+        pp.total = static_cast<unsigned int>(pp.pairs) * static_cast<unsigned int>(tiles);
+        // Launches that may run at the same time on one device need different counters; 64 of them rotate.
+        pp.slot = static_cast<int>(launch_seq.fetch_add(1u) % kTicketSlots);
+        const int sms = (device >= 0 && device < 64) ? sm_count[device] : 1;
+        const unsigned int blocks = pp.total < static_cast<unsigned int>(sms) ? pp.total : static_cast<unsigned int>(sms);
+        prefill_tc5_kernel<T><<<blocks, kThreads5, kSmemBytes4, a.stream>>>(tq, tk, tv, pp);
+        return check_launch("prefill_tc5_kernel launch");
+    }
     if (group % 2 == 0 && tc_version() == 4) {   // pairs of query heads that share a KV head, P through shared memory
         static bool attr4_done[64] = {};
         if (device >= 0 && device < 64 && !attr4_done[device]) {
