@@ -1315,6 +1315,10 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // and last item of a block do.  All barrier phases are counted cumulatively over items.
 // =================================================================================================
 constexpr int kTicketSlots = 64;
+#ifndef NVK_TC5_ISSUERS
+#define NVK_TC5_ISSUERS 2
+#endif
+constexpr int kIssuers5 = NVK_TC5_ISSUERS;   // issuing warps: 1, or 2 (one per query tile)
 #ifndef NVK_TC5_REGS
 #define NVK_TC5_REGS 1
 #define NVK_TC5_REGS_LOW 56
@@ -1404,9 +1408,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
     if (tid == 0) {
         s_abort = 0;
-        mbar_init(bar_qfull, 1); mbar_init(bar_qempty, 1); mbar_init(bar_vfix, 1); mbar_init(bar_vfull, 1); mbar_init(bar_vempty, 1);
+        mbar_init(bar_qfull, 1); mbar_init(bar_qempty, kIssuers5); mbar_init(bar_vfix, 1); mbar_init(bar_vfull, 1); mbar_init(bar_vempty, kIssuers5);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_kfull(i), 1); mbar_init(bar_kempty(i), 1);
+            mbar_init(bar_kfull(i), 1); mbar_init(bar_kempty(i), kIssuers5);
             mbar_init(bar_sfull(i), 1); mbar_init(bar_sread(i), 4); mbar_init(bar_pfull(i), 4);
             mbar_init(bar_odone(i), 1); mbar_init(bar_ofinal(i), 1);
         }
@@ -1547,9 +1551,12 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             gk += g.num_kt; gv += g.num_kt; ++n;
         }
-    } else if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 8 || warp == 8 + 2 * (kIssuers5 - 1)) {
+        // ------------------------------------------------------------------ MMA issuer(s): with two, warp 8 drives
+        // tile 0 and warp 10 tile 1 (one thread sustains about one MMA per 100 clocks here, the tensor pipe one per 64)
         if (lane == 0) {
+            const int t_lo = (kIssuers5 == 2 && warp != 8) ? 1 : 0;
+            const int t_hi = (kIssuers5 == 2 && warp == 8) ? 1 : 2;
             int n = 0, G = 0, gk = 0, gv = 0, nf = 0;   // items, rounds, K tiles, V tiles, partial-tile fixes so far
             bool ok = true;
             // One base descriptor per operand buffer; a tile-internal offset only moves the 14-bit start-address
@@ -1572,20 +1579,20 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                 };
                 // scores of the item's first key tile: Q and K(0) landed, the previous round's scores were read
                 ok = mbar_wait(bar_qfull, n & 1, abort_flag, 21) && mbar_wait(bar_kfull(gk & 1), (gk >> 1) & 1, abort_flag, 22);
-                for (int t = 0; t < 2 && ok; ++t) {
+                for (int t = t_lo; t < t_hi && ok; ++t) {
                     if (G >= 1) ok = mbar_wait(bar_sread(t), (G - 1) & 1, abort_flag, 29);
                     if (!ok) break;
                     tc_fence_after();
                     issue_s(t, 0);
                 }
                 if (!ok) break;
-                tc_commit(bar_kempty(gk & 1));
+                tc_commit(bar_kempty(gk & 1));              // (every issuer arrives)
                 if (g.num_kt == 1) tc_commit(bar_qempty);   // every score MMA of the item has been issued
                 for (int j = 0; j < g.num_kt && ok; ++j) {
                     if (j + 1 < g.num_kt) {   // next scores as soon as this step's scores have been read
                         const int c = gk + j + 1;
                         ok = mbar_wait(bar_kfull(c & 1), (c >> 1) & 1, abort_flag, 26);
-                        for (int t = 0; t < 2 && ok; ++t) {
+                        for (int t = t_lo; t < t_hi && ok; ++t) {
                             ok = mbar_wait(bar_sread(t), (G + j) & 1, abort_flag, 27);
                             if (!ok) break;
                             tc_fence_after();
@@ -1597,7 +1604,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                     }
                     ok = mbar_wait(bar_vfull, (gv + j) & 1, abort_flag, 23);
                     if (ok && j == g.last_partial) ok = mbar_wait(bar_vfix, nf & 1, abort_flag, 24);
-                    for (int t = 0; t < 2 && ok; ++t) {
+                    for (int t = t_lo; t < t_hi && ok; ++t) {
                         // p_full of an item's first round also says that the previous item's output has left TMEM
                         ok = mbar_wait(bar_pfull(t), (G + j) & 1, abort_flag, 25);
                         if (!ok) break;
