@@ -963,11 +963,6 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
                                                     bool need_mask, int key0, int lim, float scale_log2, bool first,
                                                     float& m_ref, float& l_run, uint32_t pv_done_bar, uint32_t pv_done_parity,
                                                     volatile int* abort_flag, OnRead on_scores_read) {
-#if defined(NVK_TC4_EXP) && NVK_TC4_EXP >= 3
-    on_scores_read();
-    if (!first && !warp_mbar_wait(pv_done_bar, pv_done_parity, abort_flag, 42)) return false;
-    return true;
-#endif
     uint32_t r0[32], r1[32], r2[32], r3[32];
     tmem_ld32(t_s, r0);
     tmem_ld32(t_s + 32, r1);
@@ -976,18 +971,35 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
     tc_wait_ld();
     reg_fence32(r0); reg_fence32(r1); reg_fence32(r2); reg_fence32(r3);
     on_scores_read();
-    float mx;
-    if (need_mask) {
-        mx = fmaxf(fmaxf(chunk_max<true>(r0, key0, lim), chunk_max<true>(r1, key0 + 32, lim)),
-                   fmaxf(chunk_max<true>(r2, key0 + 64, lim), chunk_max<true>(r3, key0 + 96, lim)));
-    } else {
-        mx = fmaxf(fmaxf(chunk_max<false>(r0, 0, 0), chunk_max<false>(r1, 0, 0)),
-                   fmaxf(chunk_max<false>(r2, 0, 0), chunk_max<false>(r3, 0, 0)));
-    }
-    mx *= scale_log2;
+    uint32_t pk[16];
+    auto store_chunk = [&](int c32) {   // 32 keys = four 16-byte pieces of this row
+        unsigned char* panel = p_panels + (c32 >> 1) * kPanelBytes + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const int cc = (c32 & 1) * 4 + q4;   // 16-byte column inside the 128-byte panel row
+            *reinterpret_cast<uint4*>(panel + ((cc ^ (row & 7)) << 4)) =
+                make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        }
+    };
+    auto probs = [&](const uint32_t (&r)[32], int c32, float m_use) -> float {
+        return need_mask ? chunk_probs<T, true>(r, pk, key0 + 32 * c32, lim, scale_log2, m_use)
+                         : chunk_probs<T, false>(r, pk, 0, 0, scale_log2, m_use);
+    };
+    auto row_max = [&]() -> float {
+        float mx;
+        if (need_mask) {
+            mx = fmaxf(fmaxf(chunk_max<true>(r0, key0, lim), chunk_max<true>(r1, key0 + 32, lim)),
+                       fmaxf(chunk_max<true>(r2, key0 + 64, lim), chunk_max<true>(r3, key0 + 96, lim)));
+        } else {
+            mx = fmaxf(fmaxf(chunk_max<false>(r0, 0, 0), chunk_max<false>(r1, 0, 0)),
+                       fmaxf(chunk_max<false>(r2, 0, 0), chunk_max<false>(r3, 0, 0)));
+        }
+        return mx * scale_log2;
+    };
     // P.V of the previous step must be complete before O is rescaled and before its P is overwritten: wait
-    // as late as that allows (with no rescale, after the first 32 exponentials)
+    // as late as that allows (with no rescale, after the first 32 exponentials).
     bool pv_waited = first;
+    const float mx = row_max();
     if (__any_sync(0xffffffffu, mx > m_ref + kRescaleThreshold)) {
         if (!pv_waited && !warp_mbar_wait(pv_done_bar, pv_done_parity, abort_flag, 42)) return false;
         pv_waited = true;
@@ -1010,28 +1022,14 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
         m_ref = m_new;
     }
     const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-    uint32_t pk[16];
-    auto store_chunk = [&](int c32) {   // 32 keys = four 16-byte pieces of this row
-        unsigned char* panel = p_panels + (c32 >> 1) * kPanelBytes + row * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-            const int cc = (c32 & 1) * 4 + q4;   // 16-byte column inside the 128-byte panel row
-            *reinterpret_cast<uint4*>(panel + ((cc ^ (row & 7)) << 4)) =
-                make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-        }
-    };
-    l_run += need_mask ? chunk_probs<T, true>(r0, pk, key0, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(r0, pk, 0, 0, scale_log2, m_use);
+    l_run += probs(r0, 0, m_use);
     if (!pv_waited && !warp_mbar_wait(pv_done_bar, pv_done_parity, abort_flag, 43)) return false;
     store_chunk(0);
-    l_run += need_mask ? chunk_probs<T, true>(r1, pk, key0 + 32, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(r1, pk, 0, 0, scale_log2, m_use);
+    l_run += probs(r1, 1, m_use);
     store_chunk(1);
-    l_run += need_mask ? chunk_probs<T, true>(r2, pk, key0 + 64, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(r2, pk, 0, 0, scale_log2, m_use);
+    l_run += probs(r2, 2, m_use);
     store_chunk(2);
-    l_run += need_mask ? chunk_probs<T, true>(r3, pk, key0 + 96, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(r3, pk, 0, 0, scale_log2, m_use);
+    l_run += probs(r3, 3, m_use);
     store_chunk(3);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy stores -> visible to the MMA
     return true;
