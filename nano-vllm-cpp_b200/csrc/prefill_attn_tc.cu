@@ -971,19 +971,19 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
     tc_wait_ld();
     reg_fence32(r0); reg_fence32(r1); reg_fence32(r2); reg_fence32(r3);
     on_scores_read();
-    uint32_t pk[16];
-    auto store_chunk = [&](int c32) {   // 32 keys = four 16-byte pieces of this row
+    uint32_t pk[16], pk2[16];
+    auto store_chunk = [&](int c32, const uint32_t (&v)[16]) {   // 32 keys = four 16-byte pieces of this row
         unsigned char* panel = p_panels + (c32 >> 1) * kPanelBytes + row * 128;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
             const int cc = (c32 & 1) * 4 + q4;   // 16-byte column inside the 128-byte panel row
             *reinterpret_cast<uint4*>(panel + ((cc ^ (row & 7)) << 4)) =
-                make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+                make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
         }
     };
-    auto probs = [&](const uint32_t (&r)[32], int c32, float m_use) -> float {
-        return need_mask ? chunk_probs<T, true>(r, pk, key0 + 32 * c32, lim, scale_log2, m_use)
-                         : chunk_probs<T, false>(r, pk, 0, 0, scale_log2, m_use);
+    auto probs = [&](const uint32_t (&r)[32], uint32_t (&v)[16], int c32, float m_use) -> float {
+        return need_mask ? chunk_probs<T, true>(r, v, key0 + 32 * c32, lim, scale_log2, m_use)
+                         : chunk_probs<T, false>(r, v, 0, 0, scale_log2, m_use);
     };
     auto row_max = [&]() -> float {
         float mx;
@@ -997,7 +997,7 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
         return mx * scale_log2;
     };
     // P.V of the previous step must be complete before O is rescaled and before its P is overwritten: wait
-    // as late as that allows (with no rescale, after the first 32 exponentials).
+    // as late as that allows (with no rescale, after the first 64 exponentials).
     bool pv_waited = first;
     const float mx = row_max();
     if (__any_sync(0xffffffffu, mx > m_ref + kRescaleThreshold)) {
@@ -1022,15 +1022,16 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
         m_ref = m_new;
     }
     const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-    l_run += probs(r0, 0, m_use);
+    // the first 64 probabilities wait in registers: by then the previous P.V has all but always completed
+    l_run += probs(r0, pk, 0, m_use);
+    l_run += probs(r1, pk2, 1, m_use);
     if (!pv_waited && !warp_mbar_wait(pv_done_bar, pv_done_parity, abort_flag, 43)) return false;
-    store_chunk(0);
-    l_run += probs(r1, 1, m_use);
-    store_chunk(1);
-    l_run += probs(r2, 2, m_use);
-    store_chunk(2);
-    l_run += probs(r3, 3, m_use);
-    store_chunk(3);
+    store_chunk(0, pk);
+    store_chunk(1, pk2);
+    l_run += probs(r2, pk, 2, m_use);
+    store_chunk(2, pk);
+    l_run += probs(r3, pk2, 3, m_use);
+    store_chunk(3, pk2);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy stores -> visible to the MMA
     return true;
 }
