@@ -6,8 +6,8 @@
 // kernel does not take.
 //
 // Three kernels live here: the single-tile kernel described next (taken for odd GQA group sizes), and two
-// head-pair kernels further down ("Version 2": probabilities kept in TMEM; "Version 4": probabilities
-// through shared memory, the default for even group sizes).
+// head-pair kernels further down ("Version 4": one block per item, probabilities through shared memory;
+// "Version 5": the same made persistent, the default for even group sizes).
 //
 // Single-tile kernel: one thread block = 128 query rows of one (sequence, head); 128 threads, thread t owns row t.
 //   * Q (128 x 128), K tile (128 keys x 128) and V tile live in shared memory as two 128-byte-wide
@@ -592,359 +592,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
-// =================================================================================================
-// Version 2: warp-specialised, two query tiles per block (the two query heads of a pair that share
-// one KV head, same 128 query rows), K / V tiles double buffered and loaded ONCE for both tiles.
-//
-//   warps 0-3  softmax of tile 0 (thread = row)        warp 8  MMA issuer (one elected thread)
-//   warps 4-7  softmax of tile 1                       warp 9  TMA producer (+ V tail fix-up)
-//
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases S_t[0,64).
-// Per tile the chain is S_t(j) -> softmax_t(j) -> PV_t(j) -> S_t(j+1) (aliasing + in-order MMAs);
-// the issuer interleaves the two chains -- PV_0(j), S_0(j+1), PV_1(j), S_1(j+1), ... -- so one
-// tile's MMAs run while the other tile is in its softmax.  K / V traffic from L2 per FLOP is half
-// that of version 1 and every tile is requested a full round ahead.
-// =================================================================================================
-constexpr int kThreads2 = 320;
-constexpr int kOff2Q = 0, kOff2K = 2 * kTileBytes, kOff2V = 4 * kTileBytes, kOff2Bar = 6 * kTileBytes;
-constexpr int kSmemBytes2 = kOff2Bar + 256 + 1024;
-constexpr int kTmemCols2 = 512;
+constexpr int kTmemCols2 = 512;   // head-pair kernels: S0 S1 O0 O1
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 
-// Online-softmax step of one thread's row for key tile j: reads S from TMEM, rescales O if the running
-// maximum grew by more than the threshold, writes P (16-bit pairs) over S.
-template <typename T>
-__device__ __forceinline__ void softmax_row_step(uint32_t t_s, uint32_t t_o, bool need_mask, int key0, int lim,
-                                                 float scale_log2, bool first, float& m_ref, float& l_run) {
-    uint32_t ra[32], rb[32];
-    float mx;
-    tmem_ld32(t_s, ra);
-    tc_wait_ld(); reg_fence32(ra);
-    tmem_ld32(t_s + 32, rb);
-    if (need_mask) {
-        mx = chunk_max<true>(ra, key0, lim);
-        tc_wait_ld(); reg_fence32(rb);
-        tmem_ld32(t_s + 64, ra);
-        mx = fmaxf(mx, chunk_max<true>(rb, key0 + 32, lim));
-        tc_wait_ld(); reg_fence32(ra);
-        tmem_ld32(t_s + 96, rb);
-        mx = fmaxf(mx, chunk_max<true>(ra, key0 + 64, lim));
-        tc_wait_ld(); reg_fence32(rb);
-        mx = fmaxf(mx, chunk_max<true>(rb, key0 + 96, lim));
-    } else {
-        mx = chunk_max<false>(ra, 0, 0);
-        tc_wait_ld(); reg_fence32(rb);
-        tmem_ld32(t_s + 64, ra);
-        mx = fmaxf(mx, chunk_max<false>(rb, 0, 0));
-        tc_wait_ld(); reg_fence32(ra);
-        tmem_ld32(t_s + 96, rb);
-        mx = fmaxf(mx, chunk_max<false>(ra, 0, 0));
-        tc_wait_ld(); reg_fence32(rb);
-        mx = fmaxf(mx, chunk_max<false>(rb, 0, 0));
-    }
-    tmem_ld32(t_s, ra);   // pass 2 starts re-reading while the maximum is settled
-    mx *= scale_log2;
-    if (__any_sync(0xffffffffu, mx > m_ref + kRescaleThreshold)) {
-        const float m_new = fmaxf(m_ref, mx);
-        const float f = (m_new == -INFINITY) ? 1.0f : fast_exp2(m_ref - m_new);
-        if (!first) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(t_o + c * 32, r);
-                tc_wait_ld(); reg_fence32(r);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-                tmem_st32(t_o + c * 32, r);
-            }
-        }
-        l_run *= f;
-        m_ref = m_new;
-    }
-    const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-    uint32_t pk[16];
-    tc_wait_ld(); reg_fence32(ra);
-    tmem_ld32(t_s + 32, rb);
-    l_run += need_mask ? chunk_probs<T, true>(ra, pk, key0, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(ra, pk, 0, 0, scale_log2, m_use);
-    tc_wait_ld(); reg_fence32(rb);
-    tmem_st16(t_s, pk);
-    tmem_ld32(t_s + 64, ra);
-    l_run += need_mask ? chunk_probs<T, true>(rb, pk, key0 + 32, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(rb, pk, 0, 0, scale_log2, m_use);
-    tc_wait_ld(); reg_fence32(ra);
-    tmem_st16(t_s + 16, pk);
-    tmem_ld32(t_s + 96, rb);
-    l_run += need_mask ? chunk_probs<T, true>(ra, pk, key0 + 64, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(ra, pk, 0, 0, scale_log2, m_use);
-    tc_wait_ld(); reg_fence32(rb);
-    tmem_st16(t_s + 32, pk);
-    l_run += need_mask ? chunk_probs<T, true>(rb, pk, key0 + 96, lim, scale_log2, m_use)
-                       : chunk_probs<T, false>(rb, pk, 0, 0, scale_log2, m_use);
-    tmem_st16(t_s + 48, pk);
-    tc_wait_st();
-}
-
-template <typename T>
-__global__ void __launch_bounds__(kThreads2, 1)
-prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ int s_info[4];
-    __shared__ uint32_t s_tmem_base;
-    __shared__ int s_abort;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int head0 = 2 * blockIdx.x;                       // tile t works on head0 + t
-    const int kvh = head0 * p.num_kv_heads / p.num_heads;   // both heads of the pair share it
-
-    if (tid == 0) {
-        const int64_t want = static_cast<int64_t>(gridDim.y) - 1 - blockIdx.y;
-        int64_t acc = 0;
-        int found = -1, q0 = 0;
-        if (p.cu_q == nullptr) {
-            if (want * kBM < p.total_q) { found = 0; q0 = static_cast<int>(want * kBM); }
-        } else {
-            for (int64_t s = 0; s < p.num_seqs; ++s) {
-                const int64_t tiles = (static_cast<int64_t>(p.cu_q[s + 1]) - p.cu_q[s] + kBM - 1) / kBM;
-                if (want < acc + tiles) { found = static_cast<int>(s); q0 = static_cast<int>((want - acc) * kBM); break; }
-                acc += tiles;
-            }
-        }
-        s_info[0] = found; s_info[1] = q0;
-        s_abort = 0;
-    }
-    __syncthreads();
-    const int seq = s_info[0];
-    if (seq < 0) return;
-    const int q0 = s_info[1];
-    int64_t qb, kb;
-    int q_len, k_len;
-    if (p.cu_q == nullptr) { qb = 0; kb = 0; q_len = static_cast<int>(p.total_q); k_len = static_cast<int>(p.total_k); }
-    else {
-        qb = p.cu_q[seq]; kb = p.cu_k[seq];
-        q_len = p.cu_q[seq + 1] - static_cast<int>(qb); k_len = p.cu_k[seq + 1] - static_cast<int>(kb);
-    }
-    const int rows_here = min(kBM, q_len - q0);
-    const int shift = k_len - q_len;
-    int k_hi = shift + q0 + rows_here;
-    if (k_hi > k_len) k_hi = k_len;
-    const int num_kt = k_hi > 0 ? (k_hi + kBN - 1) / kBN : 0;
-    const size_t out_stride = static_cast<size_t>(p.num_heads) * kHeadDim;
-
-    if (num_kt == 0) {   // no visible key for any row: zero rows for both heads
-        for (int t = 0; t < 2; ++t) {
-            T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(qb + q0) * p.num_heads + head0 + t) * kHeadDim;
-            for (int i = tid; i < rows_here * (kHeadDim / 8); i += kThreads2) {
-                const int r = i / (kHeadDim / 8), c = i % (kHeadDim / 8);
-                *reinterpret_cast<uint4*>(o0 + r * out_stride + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
-        return;
-    }
-
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sm_q = smem_base + kOff2Q, sm_k = smem_base + kOff2K, sm_v = smem_base + kOff2V;
-    const uint32_t bars = smem_base + kOff2Bar;
-    const uint32_t bar_q = bars, bar_vfix = bars + 8;
-    auto bar_kfull = [&](int s) { return bars + 16 + 8 * s; };
-    auto bar_vfull = [&](int s) { return bars + 32 + 8 * s; };
-    auto bar_kempty = [&](int s) { return bars + 48 + 8 * s; };
-    auto bar_vempty = [&](int s) { return bars + 64 + 8 * s; };
-    auto bar_sfull = [&](int t) { return bars + 80 + 8 * t; };
-    auto bar_pfull = [&](int t) { return bars + 96 + 8 * t; };
-    auto bar_odone = [&](int t) { return bars + 112 + 8 * t; };
-    volatile int* abort_flag = &s_abort;
-
-    if (tid == 0) {
-        mbar_init(bar_q, 1); mbar_init(bar_vfix, 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_kfull(i), 1); mbar_init(bar_vfull(i), 1); mbar_init(bar_kempty(i), 1); mbar_init(bar_vempty(i), 1);
-            mbar_init(bar_sfull(i), 1); mbar_init(bar_pfull(i), 4); mbar_init(bar_odone(i), 1);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    __syncwarp();
-    if (warp == 8) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(kTmemCols2) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = s_tmem_base;
-    const int last_partial = (k_len % kBN != 0 && num_kt * kBN > k_len) ? num_kt - 1 : -1;   // tile whose V tail needs zeroing
-
-    if (warp == 9) {
-        // ------------------------------------------------------------------ TMA producer
-        const int32_t* table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : nullptr;
-        auto key_row = [&](int key0) -> int {
-            if (table) {
-                const int id = table[key0 / p.block_size];
-                if (id < 0 || id >= p.num_cache_blocks) return static_cast<int>(p.key_rows);
-                return id * p.block_size + key0 % p.block_size;
-            }
-            return static_cast<int>(kb) + key0;
-        };
-        if (lane == 0) {
-            mbar_expect_tx(bar_q, 2 * kTileBytes);
-            for (int t = 0; t < 2; ++t) {
-                tma_load_3d(sm_q + t * kTileBytes, &tm_q, 0, head0 + t, static_cast<int>(qb) + q0, bar_q);
-                tma_load_3d(sm_q + t * kTileBytes + kPanelBytes, &tm_q, 64, head0 + t, static_cast<int>(qb) + q0, bar_q);
-            }
-        }
-        bool ok = true;
-        for (int j = 0; j < num_kt && ok; ++j) {
-            const int s = j & 1;
-            const uint32_t use_parity = (j >> 1) & 1;
-            if (lane == 0) {
-                const int r = key_row(j * kBN);
-                if (j >= 2) ok = mbar_wait(bar_kempty(s), use_parity ^ 1, abort_flag, 11);
-                if (ok) {
-                    mbar_expect_tx(bar_kfull(s), kTileBytes);
-                    tma_load_3d(sm_k + s * kTileBytes, &tm_k, 0, kvh, r, bar_kfull(s));
-                    tma_load_3d(sm_k + s * kTileBytes + kPanelBytes, &tm_k, 64, kvh, r, bar_kfull(s));
-                }
-                if (ok && j >= 2) ok = mbar_wait(bar_vempty(s), use_parity ^ 1, abort_flag, 12);
-                if (ok) {
-                    mbar_expect_tx(bar_vfull(s), kTileBytes);
-                    tma_load_3d(sm_v + s * kTileBytes, &tm_v, 0, kvh, r, bar_vfull(s));
-                    tma_load_3d(sm_v + s * kTileBytes + kPanelBytes, &tm_v, 64, kvh, r, bar_vfull(s));
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (ok && j == last_partial) {
-                // rows of V past the sequence may hold anything (0 * NaN = NaN): zero them once landed
-                ok = warp_mbar_wait(bar_vfull(s), use_parity, abort_flag, 13);
-                if (ok) {
-                    const int first_bad = k_len - j * kBN;   // in (0, 128)
-                    for (int i = lane; i < (kBN - first_bad) * 16; i += 32) {
-                        const int r = first_bad + i / 16, c16 = i % 16;
-                        *reinterpret_cast<uint4*>(smem_gen + kOff2V + s * kTileBytes + (c16 >> 3) * kPanelBytes + r * 128 +
-                                                  (c16 & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_vfix);
-                }
-            }
-        }
-    } else if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            auto issue_s = [&](int t, int s) {
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
-                    umma_ss(tmem_base + t * 128, make_smem_desc(sm_q + t * kTileBytes + off, 16, 1024),
-                            make_smem_desc(sm_k + s * kTileBytes + off, 16, 1024), p.idesc_s, ks > 0 ? 1u : 0u);
-                }
-                tc_commit(bar_sfull(t));
-            };
-            bool ok = mbar_wait(bar_q, 0, abort_flag, 21) && mbar_wait(bar_kfull(0), 0, abort_flag, 22);
-            if (ok) {
-                tc_fence_after();
-                issue_s(0, 0);
-                issue_s(1, 0);
-                tc_commit(bar_kempty(0));
-            }
-            for (int j = 0; j < num_kt && ok; ++j) {
-                const int s = j & 1;
-                ok = mbar_wait(bar_vfull(s), (j >> 1) & 1, abort_flag, 23);
-                if (ok && j == last_partial) ok = mbar_wait(bar_vfix, 0, abort_flag, 24);
-                const bool more = j + 1 < num_kt;
-                const int s1 = (j + 1) & 1;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    ok = mbar_wait(bar_pfull(t), j & 1, abort_flag, 25);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8,
-                                make_smem_desc(sm_v + s * kTileBytes + kk * 2048, kPanelBytes, 1024), p.idesc_pv,
-                                (j > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    tc_commit(bar_odone(t));
-                    if (t == 1) tc_commit(bar_vempty(s));
-                    if (more) {
-                        if (t == 0) ok = mbar_wait(bar_kfull(s1), ((j + 1) >> 1) & 1, abort_flag, 26);
-                        if (!ok) break;
-                        issue_s(t, s1);
-                        if (t == 1) tc_commit(bar_kempty(s1));
-                    }
-                }
-            }
-        }
-    } else {
-        // ------------------------------------------------------------------ softmax warps (thread = row)
-        const int t = warp >> 2;                    // tile
-        const int wq = warp & 3;                    // TMEM lane quarter
-        const int row = wq * 32 + lane;
-        const uint32_t t_s = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + t * 128;
-        const uint32_t t_o = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + 256 + t * 128;
-        const int lim = min(shift + q0 + row + 1, k_len);
-        float m_ref = -INFINITY, l_run = 0.0f;
-        bool alive = true;
-        for (int j = 0; j < num_kt; ++j) {
-            alive = warp_mbar_wait(bar_sfull(t), j & 1, abort_flag, 31);
-            if (!alive) break;
-            tc_fence_after();
-            const int key0 = j * kBN;
-            const bool need_mask = key0 + kBN > min(shift + q0 + 1, k_len);
-            softmax_row_step<T>(t_s, t_o, need_mask, key0, lim, p.scale_log2, j == 0, m_ref, l_run);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_pfull(t));
-        }
-        if (alive) alive = warp_mbar_wait(bar_odone(t), (num_kt - 1) & 1, abort_flag, 32);
-        tc_fence_after();
-        if (alive) {
-            // all MMAs of this tile are complete: its Q buffer is free and becomes the output stage
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            unsigned char* stage = smem_gen + kOff2Q + t * kTileBytes;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(t_o + c * 32, r);
-                tc_wait_ld(); reg_fence32(r);
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint4 v;
-                    v.x = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
-                    v.y = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
-                    v.z = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
-                    v.w = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
-                    const int chunk = c * 4 + q4;
-                    *reinterpret_cast<uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4)) = v;
-                }
-            }
-            __syncwarp();
-            // each warp copies out its own 32 rows: two full 256-byte rows per instruction
-            T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(qb + q0) * p.num_heads + head0 + t) * kHeadDim;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int r = wq * 32 + 2 * i + (lane >> 4), chunk = lane & 15;
-                if (r < rows_here) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4));
-                    *reinterpret_cast<uint4*>(o0 + r * out_stride + chunk * 8) = v;
-                }
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 8) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols2) : "memory");
-    }
-}
-
 // =================================================================================================
-// Version 4: as version 2 (one head pair per block, warp specialised, 128-key tiles), but the
-// probabilities go to SHARED memory (canonical K-major 128-byte-swizzled panels, consumed as the A
+// Version 4: one head pair per block (the two query heads of a pair that share a KV head: K and V tiles are
+// loaded once for both), warp specialised (8 softmax warps, thread = row; one MMA-issuer warp; one TMA-producer
+// warp), 128-key tiles.  The probabilities go to SHARED memory (canonical K-major 128-byte-swizzled panels, consumed as the A
 // operand of an SS MMA) instead of overwriting the scores in TMEM.  A softmax thread pulls its whole
 // score row into registers first and releases the score columns at once, so S_t(j+1) is computed
 // while softmax_t(j) is still running and a tile's softmax steps follow each other back to back;
@@ -1760,14 +1417,13 @@ uint32_t make_idesc(bool bf16, bool b_mn_major) {
            (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-// Head-pair kernel used when the GQA group is even: 5 (persistent, probabilities through shared memory) unless
-// NVK_PREFILL_IMPL=tc4 asks for the one-block-per-item form of the same kernel or NVK_PREFILL_IMPL=tc2 for the
-// version that keeps the probabilities in TMEM; NVK_PREFILL_IMPL=tc1 selects the single-tile kernel for every
-// shape (A/B comparisons).
+// Head-pair kernel used when the GQA group is even: the persistent one ("Version 5") unless NVK_PREFILL_IMPL=tc4
+// asks for its one-block-per-item form; NVK_PREFILL_IMPL=tc1 selects the single-tile kernel for every shape
+// (A/B comparisons; tests/test_gpu_parity.py runs the parity cases once under each setting).
 int tc_version() {
     static const int v = [] {
         const char* e = std::getenv("NVK_PREFILL_IMPL");
-        if (e != nullptr && e[0] == 't' && e[1] == 'c' && (e[2] == '1' || e[2] == '2' || e[2] == '4')) return e[2] - '0';
+        if (e != nullptr && e[0] == 't' && e[1] == 'c' && (e[2] == '1' || e[2] == '4')) return e[2] - '0';
         return 5;
     }();
     return v;
@@ -1837,17 +1493,6 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
         const dim3 grid4(a.num_heads / 2, static_cast<unsigned>(tiles));
         prefill_tc4_kernel<T><<<grid4, kThreads4, kSmemBytes4, a.stream>>>(tq, tk, tv, p);
         return check_launch("prefill_tc4_kernel launch");
-    }
-    if (group % 2 == 0 && tc_version() == 2) {   // pairs of query heads that share a KV head
-        static bool attr2_done[64] = {};
-        if (device >= 0 && device < 64 && !attr2_done[device]) {
-            const cudaError_t e = cudaFuncSetAttribute(prefill_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
-            if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill attention (tcgen05 v2): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            attr2_done[device] = true;
-        }
-        const dim3 grid2(a.num_heads / 2, static_cast<unsigned>(tiles));
-        prefill_tc2_kernel<T><<<grid2, kThreads2, kSmemBytes2, a.stream>>>(tq, tk, tv, p);
-        return check_launch("prefill_tc2_kernel launch");
     }
     const dim3 grid(a.num_heads, static_cast<unsigned>(tiles));
     prefill_tc_kernel<T><<<grid, kThreads, kSmemBytes, a.stream>>>(tq, tk, tv, p);

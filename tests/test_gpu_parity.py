@@ -362,3 +362,18 @@ def test_fused_split_norm_rope_store_matches_oracle(num_q_heads, num_kv_heads, h
         tol = np.maximum(np.abs(ref), 1e-3) * 2.0 ** -7
         assert (np.abs(got - ref) <= tol).all()
         assert (got == ref).mean() > 0.98
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("impl", ["tc4", "tc1"])
+def test_prefill_parity_under_the_other_tensor_core_kernels(impl):
+    """The library picks its prefill kernel once per process (NVK_PREFILL_IMPL): re-run this file's prefill cases in
+    a child process under each alternative, so the one-block-per-item and the single-tile kernels stay covered."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, NVK_PREFILL_IMPL=impl)
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-m", "gpu", "-x", "-k",
+                          "prefill and not under_the_other"], env=env, capture_output=True, text=True, timeout=600,
+                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
