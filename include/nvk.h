@@ -107,6 +107,29 @@ int nvk_decode_attention_paged(const void* query, const void* k_cache, const voi
                                size_t workspace_bytes, void* stream);
 
 /*
+ * int8 KV cache.  Replaces nano_vllm::store_kvcache_int8 (include/kernels/kvcache.h:14-24; kernel
+ * src/kernels/kvcache.cu:222-296) and nano_vllm::launch_decode_attention_paged_int8
+ * (include/kernels/attention.h:43-56; kernel src/kernels/attention.cu:746-842).
+ *   key, value        [num_tokens, num_kv_heads, head_dim], dtype F16 / BF16 / F32
+ *   k_cache, v_cache  int8 [cache_rows, num_kv_heads, head_dim]  (cache_rows = num_cache_blocks * block_size)
+ *   k_scale, v_scale  fp16 [cache_rows, num_kv_heads]: scale = max(absmax / 127, 1e-10) of the head vector,
+ *                     quantised value = clamp(rint(x * 127 / max(absmax, 1e-10)), -127, 127)
+ * The store skips tokens whose slot is < 0 or >= cache_rows and writes caches and scales bit-identical to the
+ * reference's.  The decode entry point has the semantics of nvk_decode_attention_paged with
+ * k = int8 * k_scale, v = int8 * v_scale; workspace as there (same nvk_decode_attention_workspace_bytes).
+ * F16 / BF16 queries with head_dim 128 take the tensor-core path, other shapes and F32 the general one.
+ */
+int nvk_store_kvcache_int8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale,
+                           void* v_scale, const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads,
+                           int head_dim, int64_t cache_rows, int dtype, void* stream);
+int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, const void* v_cache,
+                                    const void* k_scale, const void* v_scale, const int32_t* context_lens,
+                                    const int32_t* block_tables, int64_t batch, int64_t max_blocks,
+                                    int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim,
+                                    int block_size, float scale, void* output, int dtype, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
+/*
  * Same computation as nvk_decode_attention_paged for callers that cannot provide a workspace and
  * must not allocate device memory.  (No counterpart in the reference: its decode entry point simply
  * has no scratch.)  Typical callers: a wrapper with the reference's launch_decode_attention_paged

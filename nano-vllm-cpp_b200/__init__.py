@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "nvk_abi_version", "nvk_last_error", "nvk_store_kvcache", "nvk_fused_split_norm_rope_store",
     "nvk_decode_attention_workspace_bytes", "nvk_decode_attention_paged",
     "nvk_prefill_attention_varlen", "nvk_decode_attention_paged_static",
+    "nvk_store_kvcache_int8", "nvk_decode_attention_paged_int8",
 )
 
 _lib = None
@@ -180,6 +181,51 @@ def launch_decode_attention_paged_static(query, k_cache, v_cache, context_lens, 
         ctypes.c_int(block_size), ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)),
         _stream()))
     launch_count += 2
+
+
+def store_kvcache_int8(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping) -> None:
+    """``store_kvcache_int8`` (include/kernels/kvcache.h:14-24): quantising scatter into int8 caches + fp16 scales."""
+    global launch_count
+    import torch
+    for n, t in (("key", key), ("value", value), ("k_cache", k_cache), ("v_cache", v_cache), ("k_scale", k_scale),
+                 ("v_scale", v_scale), ("slot_mapping", slot_mapping)):
+        _require_cuda(n, t)
+    if k_cache.dtype != torch.int8 or v_cache.dtype != torch.int8:
+        raise ValueError("store_kvcache_int8 requires int8 caches")
+    if k_scale.dtype != torch.float16 or v_scale.dtype != torch.float16:
+        raise ValueError("store_kvcache_int8 requires float16 scales")
+    if key.dim() != 3:
+        raise ValueError("key must be rank-3 for int8 store")
+    if slot_mapping.dtype.itemsize != 4:
+        raise ValueError("slot_mapping must be int32")
+    hkv, d = key.shape[1], key.shape[2]
+    _check(lib().nvk_store_kvcache_int8(
+        _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(slot_mapping),
+        ctypes.c_int64(slot_mapping.numel()), ctypes.c_int(hkv), ctypes.c_int(d),
+        ctypes.c_int64(k_cache.numel() // (hkv * d)), ctypes.c_int(_dtype_code(key)), _stream()))
+    launch_count += 1
+
+
+def launch_decode_attention_paged_int8(query, k_cache, v_cache, k_scale, v_scale, context_lens, block_tables,
+                                       num_kv_heads, head_dim, block_size, scale, output, workspace=None) -> None:
+    """``launch_decode_attention_paged_int8`` (include/kernels/attention.h:43-56), with the optional split-K workspace
+    of :func:`launch_decode_attention_paged`."""
+    global launch_count
+    for n, t in (("query", query), ("k_cache", k_cache), ("v_cache", v_cache), ("k_scale", k_scale), ("v_scale", v_scale),
+                 ("context_lens", context_lens), ("block_tables", block_tables), ("output", output)):
+        _require_cuda(n, t)
+    if context_lens.dtype.itemsize != 4 or block_tables.dtype.itemsize != 4:
+        raise ValueError("context_lens and block_tables must be int32")
+    batch, num_heads = query.shape[0], query.shape[1]
+    num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
+    _check(lib().nvk_decode_attention_paged_int8(
+        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(context_lens), _ptr(block_tables),
+        ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
+        ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim), ctypes.c_int(block_size),
+        ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)), _ptr(workspace),
+        ctypes.c_size_t(workspace.numel() * workspace.element_size() if workspace is not None else 0), _stream()))
+    ws_need = decode_attention_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, block_tables.shape[1], block_size)
+    launch_count += 2 if (workspace is not None and ws_need > 0) else 1
 
 
 def _prefill(query, key, value, k_cache, v_cache, cu_q, cu_k, block_tables, num_kv_heads, head_dim,

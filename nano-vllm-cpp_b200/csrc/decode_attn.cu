@@ -24,6 +24,8 @@
 
 #include <cmath>
 
+#include <cuda_fp16.h>
+
 namespace nvk {
 namespace {
 
@@ -262,6 +264,268 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p,
     *reinterpret_cast<uint2*>(dst) = packed;
 }
 
+// ---------------------------------------------------------------------------------------------
+// int8 KV cache (src/kernels/attention.cu:746-842 of the reference: decode_paged_attention_int8_kernel).
+//
+// Same block / split / merge structure as decode_split_kernel; what streams from HBM is half as wide:
+// per token and KV head 128 int8 of K, 128 of V and two fp16 scales.  Each warp's cp.async ring carries
+// the int8 tiles (16 tokens x 128 B for K, the same for V); once a tile has landed every lane widens the
+// 16-byte pieces it copied itself to fp16 (x ^ 0x80 glued under the exponent of 1024.0, minus 1152.0:
+// exact, 5 instructions per 4 elements) into one fp16 tile per warp, laid out exactly like the 16-bit
+// kernel's tiles, so ldmatrix and the MMAs are unchanged (run as f16 whatever the query type: the query
+// is converted once, probabilities are <= 1).  The scales never touch the tiles: k_scale multiplies the
+// score of its key after the first MMA, v_scale multiplies the probability of its key before the second
+// (the row sum uses the unscaled probability).  Scales are fetched two tiles ahead into registers by
+// lanes 0-15 (K) and 16-31 (V).
+// ---------------------------------------------------------------------------------------------
+constexpr int kRowBytesI8 = kHeadDim;                      // one head row of int8 K or V
+constexpr int kTileBytesI8 = kTileTokens * kRowBytesI8;    // 2 KiB
+constexpr int kStageBytesI8 = 2 * kTileBytesI8;            // K + V
+constexpr int kWarpBytesI8 = kStages * kStageBytesI8 + kStageBytes;   // ring + one widened K / V tile pair
+constexpr int kSmemBytesI8 = kWarps * kWarpBytesI8;        // 80 KiB -> two blocks per SM
+
+// 16 int8 (one 16-byte piece) -> 16 fp16 (two 16-byte pieces)
+__device__ __forceinline__ void widen_i8x16(const uint4& in, uint4& lo, uint4& hi) {
+    const uint32_t w[4] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u, in.z ^ 0x80808080u, in.w ^ 0x80808080u};
+    uint32_t h[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t a = __byte_perm(w[i], 0x64646464u, 0x4140);   // {1024 + b0, 1024 + b1}
+        const uint32_t b = __byte_perm(w[i], 0x64646464u, 0x4342);   // {1024 + b2, 1024 + b3}
+        asm("sub.f16x2 %0, %1, %2;\n" : "=r"(h[2 * i]) : "r"(a), "r"(0x64806480u));      // - 1152 = - (1024 + 128)
+        asm("sub.f16x2 %0, %1, %2;\n" : "=r"(h[2 * i + 1]) : "r"(b), "r"(0x64806480u));
+    }
+    lo = make_uint4(h[0], h[1], h[2], h[3]);
+    hi = make_uint4(h[4], h[5], h[6], h[7]);
+}
+
+struct DecodeInt8Params {
+    DecodeParams base;
+    const __half* k_scale; const __half* v_scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const DecodeInt8Params pp) {
+    const DecodeParams& p = pp.base;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_blocks[kMaxChunkBlocks];
+
+    const int kvh = blockIdx.x;
+    const int split = blockIdx.y;
+    const int64_t b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = p.group;
+
+    const int ctx = p.context_lens[b];
+    const int t0 = split * p.chunk_tokens;
+    T* out = static_cast<T*>(p.out);
+    if (ctx <= 0) {
+        if (split == 0) {
+            for (int i = tid; i < G * kHeadDim; i += kThreads)
+                out[(b * p.num_heads + kvh * G) * kHeadDim + i] = ElemTraits<T>::from_float(0.0f);
+        }
+        return;
+    }
+    if (t0 >= ctx) return;
+    const int t1 = min(ctx, t0 + p.chunk_tokens);
+    const int live_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
+
+    const int blk0 = t0 / p.block_size;
+    const int nblk = (t1 - 1) / p.block_size - blk0 + 1;
+    for (int i = tid; i < nblk; i += kThreads) {
+        const int id = p.block_tables[b * p.max_blocks + blk0 + i];
+        s_blocks[i] = (id >= 0 && id < p.num_cache_blocks) ? id : -1;
+    }
+    __syncthreads();
+
+    // Query fragments as f16: rows g < G of the 16-row A tile, rows 8..15 are zero.
+    uint32_t qa[8][2];
+    {
+        const T* qrow = static_cast<const T*>(p.q) + (b * p.num_heads + kvh * G + (g < G ? g : 0)) * kHeadDim;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                const int d = ks * 16 + hlf * 8 + 2 * t;
+                const float x0 = ElemTraits<T>::to_float(qrow[d]), x1 = ElemTraits<T>::to_float(qrow[d + 1]);
+                qa[ks][hlf] = g < G ? ElemTraits<__half>::pack2(x0, x1) : 0u;
+            }
+        }
+    }
+
+    unsigned char* ring = smem + warp * kWarpBytesI8;
+    const uint32_t ring_u32 = smem_u32(ring);
+    unsigned char* wide = ring + kStages * kStageBytesI8;          // widened K tile, then widened V tile
+    const uint32_t wide_u32 = smem_u32(wide);
+    const int num_tiles = (t1 - t0 + kTileTokens - 1) / kTileTokens;
+    const int my_tiles = num_tiles > warp ? (num_tiles - warp + kWarps - 1) / kWarps : 0;
+    const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kRowBytesI8;   // bytes between tokens
+    const unsigned char* kc = static_cast<const unsigned char*>(p.k_cache) + static_cast<size_t>(kvh) * kRowBytesI8;
+    const unsigned char* vc = static_cast<const unsigned char*>(p.v_cache) + static_cast<size_t>(kvh) * kRowBytesI8;
+
+    // Lane's pieces of a tile: 16-byte column c of rows r = 4 * i + (lane >> 3), i = 0..3 (K and V alike).
+    const int c = lane & 7, rq = lane >> 3;
+
+    auto issue = [&](int j) {
+        if (j < my_tiles) {
+            const int tok0 = t0 + (warp + j * kWarps) * kTileTokens;
+            const int blk = tok0 / p.block_size;
+            const int phys = s_blocks[blk - blk0];
+            const int off = tok0 - blk * p.block_size;
+            const size_t base = (static_cast<size_t>(phys < 0 ? 0 : phys) * p.block_size + off) * row_stride + c * 16;
+            const uint32_t stage = ring_u32 + (j % kStages) * kStageBytesI8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = 4 * i + rq;
+                const int bytes = (phys >= 0 && tok0 + r < t1) ? 16 : 0;
+                const size_t src = base + (bytes ? r * row_stride : 0);
+                const uint32_t dst = stage + r * kRowBytesI8 + c * 16;
+                cp_async16(dst, kc + src, bytes);
+                cp_async16(dst + kTileBytesI8, vc + src, bytes);
+            }
+        }
+        cp_async_commit();
+    };
+    // Scale of this lane's token of tile j: lanes 0-15 K, lanes 16-31 V (0 outside the chunk or the cache).
+    auto fetch_scale = [&](int j) -> float {
+        if (j >= my_tiles) return 0.0f;
+        const int tok = t0 + (warp + j * kWarps) * kTileTokens + (lane & 15);
+        const int blk = tok / p.block_size;
+        if (tok >= t1) return 0.0f;
+        const int phys = s_blocks[blk - blk0];
+        if (phys < 0) return 0.0f;
+        const size_t row = static_cast<size_t>(phys) * p.block_size + (tok - blk * p.block_size);
+        const __half* src = (lane < 16 ? pp.k_scale : pp.v_scale) + row * p.num_kv_heads + kvh;
+        return __half2float(*src);
+    };
+
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float m_run = -INFINITY, l_run = 0.0f;
+
+    issue(0);
+    issue(1);
+    float sc_cur = fetch_scale(0), sc_next = fetch_scale(1);
+
+    const int k_row = ((lane >> 4) << 3) + (lane & 7);
+    const int k_sel = (lane >> 3) & 1;
+    const int v_row = (((lane >> 3) >> 1) << 3) + (lane & 7);
+    const int v_sel = (lane >> 3) & 1;
+
+    for (int j = 0; j < my_tiles; ++j) {
+        issue(j + kStages - 1);
+        const float sc_after = fetch_scale(j + 2);
+        cp_async_wait<kStages - 1>();
+        // widen the pieces this lane copied (its own cp.async groups are complete: no cross-lane wait needed)
+        {
+            const unsigned char* stage = ring + (j % kStages) * kStageBytesI8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = 4 * i + rq;
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv) {
+                    const uint4 in = *reinterpret_cast<const uint4*>(stage + kv * kTileBytesI8 + r * kRowBytesI8 + c * 16);
+                    uint4 lo, hi;
+                    widen_i8x16(in, lo, hi);
+                    unsigned char* dst = wide + kv * kTileBytes + r * kRowBytes;
+                    *reinterpret_cast<uint4*>(dst + (((2 * c) ^ (r & 7)) << 4)) = lo;
+                    *reinterpret_cast<uint4*>(dst + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
+                }
+            }
+        }
+        __syncwarp();
+        const int tok0 = t0 + (warp + j * kWarps) * kTileTokens;
+
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t b0, b1, b2, b3;
+            const int chunk = 2 * ks + k_sel;
+            ldmatrix_x4(b0, b1, b2, b3, wide_u32 + k_row * kRowBytes + ((chunk ^ (k_row & 7)) << 4));
+            mma_16816<__half>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+            mma_16816<__half>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        }
+        // scores of head g: tokens tok0 + {2t, 2t+1, 8+2t, 9+2t}; each carries its key's K scale
+        const float ks0 = __shfl_sync(0xffffffffu, sc_cur, 2 * t), ks1 = __shfl_sync(0xffffffffu, sc_cur, 2 * t + 1);
+        const float ks2 = __shfl_sync(0xffffffffu, sc_cur, 8 + 2 * t), ks3 = __shfl_sync(0xffffffffu, sc_cur, 9 + 2 * t);
+        const float vs0 = __shfl_sync(0xffffffffu, sc_cur, 16 + 2 * t), vs1 = __shfl_sync(0xffffffffu, sc_cur, 17 + 2 * t);
+        const float vs2 = __shfl_sync(0xffffffffu, sc_cur, 24 + 2 * t), vs3 = __shfl_sync(0xffffffffu, sc_cur, 25 + 2 * t);
+        float sc[4];
+        sc[0] = s0[0] * ks0 * p.scale_log2; sc[1] = s0[1] * ks1 * p.scale_log2;
+        sc[2] = s1[0] * ks2 * p.scale_log2; sc[3] = s1[1] * ks3 * p.scale_log2;
+        const int tk = tok0 + 2 * t;
+        if (tk >= t1) sc[0] = -INFINITY;
+        if (tk + 1 >= t1) sc[1] = -INFINITY;
+        if (tk + 8 >= t1) sc[2] = -INFINITY;
+        if (tk + 9 >= t1) sc[3] = -INFINITY;
+        float m_tile = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
+        m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
+        const float m_new = fmaxf(m_run, m_tile);   // finite: token tok0 is always valid
+        const float corr = fast_exp2(m_run - m_new);
+        const float p0 = fast_exp2(sc[0] - m_new), p1 = fast_exp2(sc[1] - m_new);
+        const float p2 = fast_exp2(sc[2] - m_new), p3 = fast_exp2(sc[3] - m_new);
+        l_run = l_run * corr + ((p0 + p1) + (p2 + p3));
+        m_run = m_new;
+        const uint32_t pb0 = ElemTraits<__half>::pack2(p0 * vs0, p1 * vs1);
+        const uint32_t pb1 = ElemTraits<__half>::pack2(p2 * vs2, p3 * vs3);
+        const float c0 = __shfl_sync(0xffffffffu, corr, 8 * t);
+        const float c1 = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            uint32_t a0, a1, a2, a3;
+            const int chunk = 2 * mt + v_sel;
+            ldmatrix_x4_trans(a0, a1, a2, a3, wide_u32 + kTileBytes + v_row * kRowBytes + ((chunk ^ (v_row & 7)) << 4));
+            o[mt][0] *= c0; o[mt][1] *= c1; o[mt][2] *= c0; o[mt][3] *= c1;
+            mma_16816<__half>(o[mt], a0, a1, a2, a3, pb0, pb1);
+        }
+        __syncwarp();   // the widened tile is rewritten in the next iteration
+        sc_cur = sc_next;
+        sc_next = sc_after;
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every ring is idle from here on: reuse the shared memory for the cross-warp merge
+
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+    float* sm_o = reinterpret_cast<float*>(smem);                    // [warp][head][128]
+    float* sm_m = sm_o + kWarps * kMaxGroup * kHeadDim;              // [warp][head]
+    float* sm_l = sm_m + kWarps * kMaxGroup;
+    if (t == 0) { sm_m[warp * kMaxGroup + g] = m_run; sm_l[warp * kMaxGroup + g] = l_run; }
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+        const int d = mt * 16 + g;
+        float* dst = sm_o + (warp * kMaxGroup + 2 * t) * kHeadDim + d;
+        dst[0] = o[mt][0]; dst[kHeadDim] = o[mt][1]; dst[8] = o[mt][2]; dst[kHeadDim + 8] = o[mt][3];
+    }
+    __syncthreads();
+
+    const int d = tid;
+    for (int h = 0; h < G; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, sm_m[w * kMaxGroup + h]);
+        float acc = 0.0f, lsum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float f = fast_exp2(sm_m[w * kMaxGroup + h] - mx);
+            acc += f * sm_o[(w * kMaxGroup + h) * kHeadDim + d];
+            lsum += f * sm_l[w * kMaxGroup + h];
+        }
+        const float val = acc / lsum;
+        const int64_t head = b * p.num_heads + kvh * G + h;
+        if (live_splits == 1) {
+            out[head * kHeadDim + d] = ElemTraits<T>::from_float(val);
+        } else {
+            p.ws_o[(head * p.num_splits + split) * kHeadDim + d] = val;
+            if (d == 0) p.ws_lse[head * p.num_splits + split] = mx + log2f(lsum);
+        }
+    }
+}
+
 // Split policy from host-known sizes only.  Returns chunk length in tokens (multiple of block_size).
 int choose_chunk_tokens(int64_t batch, int num_kv_heads, int64_t max_blocks, int block_size, bool have_workspace) {
     const int64_t max_tokens = max_blocks * block_size;
@@ -323,6 +587,53 @@ int launch_typed(const DecodeArgs& a) {
     return rc;
 }
 
+template <typename T>
+int launch_int8_typed(const DecodeInt8Args& x) {
+    const DecodeArgs& a = x.base;
+    static bool attr_done[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 0 && device < 64 && !attr_done[device]) {
+        const cudaError_t e = cudaFuncSetAttribute(decode_split_int8_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesI8);
+        if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "decode attention (int8): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_done[device] = true;
+    }
+    DecodeInt8Params pp{};
+    DecodeParams& p = pp.base;
+    pp.k_scale = static_cast<const __half*>(x.k_scale); pp.v_scale = static_cast<const __half*>(x.v_scale);
+    p.q = a.q; p.k_cache = a.k_cache; p.v_cache = a.v_cache;
+    p.context_lens = a.context_lens; p.block_tables = a.block_tables; p.out = a.out;
+    p.max_blocks = a.max_blocks; p.num_cache_blocks = a.num_cache_blocks;
+    p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.group = a.num_heads / a.num_kv_heads;
+    p.block_size = a.block_size;
+    p.scale_log2 = a.scale * kLog2e;
+    const size_t need = decode_mma_workspace_bytes(a.batch, a.num_heads, a.num_kv_heads, a.head_dim, a.max_blocks, a.block_size);
+    const bool have_ws = a.workspace != nullptr && a.workspace_bytes >= need && aligned_to(a.workspace, 16);
+    p.chunk_tokens = choose_chunk_tokens(a.batch, a.num_kv_heads, a.max_blocks, a.block_size, have_ws);
+    if (p.chunk_tokens / a.block_size > kMaxChunkBlocks) {
+        if (!have_ws) return fail(NVK_ERR_UNSUPPORTED, "decode attention (int8): max_blocks %lld needs a workspace", (long long)a.max_blocks);
+        p.chunk_tokens = kMaxChunkBlocks * a.block_size;
+    }
+    const int64_t max_tokens = a.max_blocks * a.block_size;
+    p.num_splits = static_cast<int>((max_tokens + p.chunk_tokens - 1) / p.chunk_tokens);
+    if (p.num_splits > 1) {
+        p.ws_lse = static_cast<float*>(a.workspace);
+        const size_t lse_bytes = (static_cast<size_t>(a.batch) * a.num_heads * p.num_splits * sizeof(float) + 15) / 16 * 16;
+        p.ws_o = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + lse_bytes);
+    }
+    if (a.batch > 65535 || p.num_splits > 65535) return fail(NVK_ERR_UNSUPPORTED, "decode attention (int8): batch or split count exceeds grid limits");
+    const dim3 grid(a.num_kv_heads, p.num_splits, static_cast<unsigned>(a.batch));
+    decode_split_int8_kernel<T><<<grid, kThreads, kSmemBytesI8, a.stream>>>(pp);
+    int rc = check_launch("decode_split_int8_kernel launch");
+    if (rc != NVK_OK) return rc;
+    if (p.num_splits > 1) {
+        const int64_t rows = a.batch * a.num_heads;
+        decode_merge_kernel<T><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, a.stream>>>(p, rows);
+        rc = check_launch("decode_merge_kernel launch");
+    }
+    return rc;
+}
+
 }  // namespace
 
 bool decode_mma_supported(const DecodeArgs& a) {
@@ -346,6 +657,23 @@ size_t decode_mma_workspace_bytes(int64_t batch, int num_heads, int num_kv_heads
     const size_t rows = static_cast<size_t>(batch) * num_heads * splits;
     const size_t lse_bytes = (rows * sizeof(float) + 15) / 16 * 16;
     return lse_bytes + rows * static_cast<size_t>(head_dim) * sizeof(float);
+}
+
+bool decode_int8_mma_supported(const DecodeInt8Args& x) {
+    const DecodeArgs& a = x.base;
+    if (a.dtype != NVK_F16 && a.dtype != NVK_BF16) return false;
+    if (a.head_dim != kHeadDim) return false;
+    if (a.num_kv_heads <= 0 || a.num_heads % a.num_kv_heads != 0) return false;
+    if (a.num_heads / a.num_kv_heads > kMaxGroup) return false;
+    if (a.block_size < kTileTokens || a.block_size % kTileTokens != 0) return false;
+    if (!aligned_to(a.q, 2) || !aligned_to(a.k_cache, 16) || !aligned_to(a.v_cache, 16) || !aligned_to(a.out, 8)) return false;
+    if (!aligned_to(x.k_scale, 2) || !aligned_to(x.v_scale, 2)) return false;
+    if (a.workspace == nullptr && a.max_blocks > kMaxChunkBlocks) return false;
+    return true;
+}
+
+int launch_decode_int8_mma(const DecodeInt8Args& x) {
+    return x.base.dtype == NVK_BF16 ? launch_int8_typed<__nv_bfloat16>(x) : launch_int8_typed<__half>(x);
 }
 
 int launch_decode_mma(const DecodeArgs& a) {

@@ -1,0 +1,196 @@
+// int8 paged KV cache for sm_100a: quantising store and the general decode path.
+//
+// Replaces store_kvcache_int8_kernel (src/kernels/kvcache.cu:222-296 of the reference: one 32-thread block per
+// (token, KV head), lane-strided element loops) and, for shapes the tensor-core kernel in decode_attn.cu does not
+// take, decode_paged_attention_int8_kernel (src/kernels/attention.cu:746-842).
+//
+// Format (the reference's): K and V as int8 [cache_rows, Hkv, D]; one fp16 scale per (cache row, KV head) in
+// k_scale / v_scale [cache_rows, Hkv]; scale = max(absmax / 127, 1e-10), q = clamp(rint(x * 127 / max(absmax, 1e-10)), +-127).
+// The store is HBM-bound (reads 2 * tokens * Hkv * D elements, writes half as many bytes plus the scales): one warp
+// per (token, KV head), every lane holds D / 32 contiguous elements of K and of V (one 4/8/16-byte load each), the
+// absolute maximum is a shuffle reduction, the quantised bytes leave as one packed store per lane.  The arithmetic is
+// the reference's operation for operation (IEEE division, round-to-nearest-even conversion), so caches and scales are
+// bit-identical to the reference's.
+#include "nvk_internal.cuh"
+
+#include <cuda_fp16.h>
+
+namespace nvk {
+namespace {
+
+constexpr int kStoreWarps = 8;
+
+template <int V> struct PackOf;
+template <> struct PackOf<2> { using in16 = uint32_t; using in32 = uint2; using out = uint16_t; };
+template <> struct PackOf<4> { using in16 = uint2; using in32 = uint4; using out = uint32_t; };
+template <> struct PackOf<8> { using in16 = uint4; using in32 = uint4; using out = uint2; };
+
+template <typename T, int V>
+__device__ __forceinline__ void load_elems(const T* src, float (&x)[V]) {
+    if constexpr (sizeof(T) == 2) {
+        union { typename PackOf<V>::in16 v; T e[V]; } u;
+        u.v = *reinterpret_cast<const typename PackOf<V>::in16*>(src);
+#pragma unroll
+        for (int i = 0; i < V; ++i) x[i] = ElemTraits<T>::to_float(u.e[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) x[i] = src[i];
+    }
+}
+
+template <int V>
+__device__ __forceinline__ void quantise_and_store(const float (&x)[V], int8_t* dst, __half* scale_dst, int lane) {
+    float absmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) absmax = fmaxf(absmax, fabsf(x[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, o));
+    const float sc = fmaxf(__fdiv_rn(absmax, 127.0f), 1e-10f);
+    const float inv_sc = __fdiv_rn(127.0f, fmaxf(absmax, 1e-10f));
+    union { typename PackOf<V>::out v; int8_t e[V]; } q;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        int v = __float2int_rn(__fmul_rn(x[i], inv_sc));
+        v = max(-127, min(127, v));
+        q.e[i] = static_cast<int8_t>(v);
+    }
+    *reinterpret_cast<typename PackOf<V>::out*>(dst + lane * V) = q.v;
+    if (lane == 0) *scale_dst = __float2half(sc);
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kStoreWarps * 32)
+store_int8_kernel(const T* __restrict__ key, const T* __restrict__ value, int8_t* __restrict__ k_cache,
+                  int8_t* __restrict__ v_cache, __half* __restrict__ k_scale, __half* __restrict__ v_scale,
+                  const int32_t* __restrict__ slot_mapping, int64_t num_tokens, int num_kv_heads, int64_t cache_rows) {
+    constexpr int D = V * 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t work = static_cast<int64_t>(blockIdx.x) * kStoreWarps + (threadIdx.x >> 5);   // (token, head)
+    if (work >= num_tokens * num_kv_heads) return;
+    const int64_t token = work / num_kv_heads;
+    const int head = static_cast<int>(work % num_kv_heads);
+    const int64_t slot = slot_mapping[token];
+    if (slot < 0 || slot >= cache_rows) return;
+    float kx[V], vx[V];
+    load_elems<T, V>(key + work * D + lane * V, kx);
+    load_elems<T, V>(value + work * D + lane * V, vx);
+    const int64_t dst_row = slot * num_kv_heads + head;
+    quantise_and_store<V>(kx, k_cache + dst_row * D, k_scale + dst_row, lane);
+    quantise_and_store<V>(vx, v_cache + dst_row * D, v_scale + dst_row, lane);
+}
+
+// General decode path: one warp per (sequence, query head), lane owns D / 32 contiguous elements; serial online
+// softmax over the keys as in the reference.  Used for fp32 queries and head dims other than 128.
+template <typename T, int V>
+__global__ void __launch_bounds__(128)
+decode_int8_rowwise_kernel(const T* __restrict__ query, const int8_t* __restrict__ k_cache, const int8_t* __restrict__ v_cache,
+                           const __half* __restrict__ k_scale, const __half* __restrict__ v_scale,
+                           const int32_t* __restrict__ context_lens, const int32_t* __restrict__ block_tables,
+                           int64_t batch, int64_t max_blocks, int64_t num_cache_blocks, int num_heads, int num_kv_heads,
+                           int block_size, float scale, T* __restrict__ output) {
+    constexpr int D = V * 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t work = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    if (work >= batch * num_heads) return;
+    const int64_t seq = work / num_heads;
+    const int head = static_cast<int>(work % num_heads);
+    const int kv_head = head * num_kv_heads / num_heads;
+    float q[V], acc[V];
+    load_elems<T, V>(query + work * D + lane * V, q);
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.0f;
+    const int64_t k_len = context_lens[seq];
+    float running_max = -INFINITY, running_sum = 0.0f;
+    const int32_t* table = block_tables + seq * max_blocks;
+    for (int64_t k = 0; k < k_len; ++k) {
+        const int64_t block = table[k / block_size];
+        const bool inside = block >= 0 && block < num_cache_blocks;   // ids outside the cache read as zeros
+        const int64_t row = inside ? (block * block_size + k % block_size) * num_kv_heads + kv_head : 0;
+        const float ks = inside ? __half2float(k_scale[row]) : 0.0f, vs = inside ? __half2float(v_scale[row]) : 0.0f;
+        union { typename PackOf<V>::out v; int8_t e[V]; } kq, vq;
+        kq.v = *reinterpret_cast<const typename PackOf<V>::out*>(k_cache + row * D + lane * V);
+        vq.v = *reinterpret_cast<const typename PackOf<V>::out*>(v_cache + row * D + lane * V);
+        float partial = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) partial += q[i] * (static_cast<float>(kq.e[i]) * ks);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, o);
+        const float qk = partial * scale;
+        const float old_max = running_max;
+        running_max = fmaxf(running_max, qk);
+        const float correction = expf(old_max - running_max);
+        const float e = expf(qk - running_max);
+        running_sum = running_sum * correction + e;
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = acc[i] * correction + e * (static_cast<float>(vq.e[i]) * vs);
+    }
+    const float inv = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
+    T* dst = output + work * D + lane * V;
+#pragma unroll
+    for (int i = 0; i < V; ++i) dst[i] = ElemTraits<T>::from_float(acc[i] * inv);
+}
+
+template <typename T>
+int launch_store_typed(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                       const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,
+                       cudaStream_t stream) {
+    const int64_t work = num_tokens * num_kv_heads;
+    const int64_t blocks = (work + kStoreWarps - 1) / kStoreWarps;
+    if (blocks > 0x7fffffffLL) return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: too many tokens");
+#define NVK_LAUNCH(V)                                                                                              \
+    store_int8_kernel<T, V><<<static_cast<unsigned>(blocks), kStoreWarps * 32, 0, stream>>>(                        \
+        static_cast<const T*>(key), static_cast<const T*>(value), static_cast<int8_t*>(k_cache),                   \
+        static_cast<int8_t*>(v_cache), static_cast<__half*>(k_scale), static_cast<__half*>(v_scale), slot_mapping, \
+        num_tokens, num_kv_heads, cache_rows)
+    switch (head_dim) {
+        case 64: NVK_LAUNCH(2); break;
+        case 128: NVK_LAUNCH(4); break;
+        case 256: NVK_LAUNCH(8); break;
+        default: return fail(NVK_ERR_UNSUPPORTED, "store_kvcache_int8: head_dim must be 64, 128 or 256 (got %d)", head_dim);
+    }
+#undef NVK_LAUNCH
+    return check_launch("store_kvcache_int8 kernel launch");
+}
+
+template <typename T>
+int launch_rowwise_typed(const DecodeInt8Args& a) {
+    const int64_t work = a.base.batch * a.base.num_heads;
+    const int64_t blocks = (work + 3) / 4;
+    if (blocks > 0x7fffffffLL) return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (int8): too many rows");
+#define NVK_LAUNCH(V)                                                                                                        \
+    decode_int8_rowwise_kernel<T, V><<<static_cast<unsigned>(blocks), 128, 0, a.base.stream>>>(                               \
+        static_cast<const T*>(a.base.q), static_cast<const int8_t*>(a.base.k_cache), static_cast<const int8_t*>(a.base.v_cache), \
+        static_cast<const __half*>(a.k_scale), static_cast<const __half*>(a.v_scale), a.base.context_lens, a.base.block_tables, \
+        a.base.batch, a.base.max_blocks, a.base.num_cache_blocks, a.base.num_heads, a.base.num_kv_heads, a.base.block_size,   \
+        a.base.scale, static_cast<T*>(a.base.out))
+    switch (a.base.head_dim) {
+        case 64: NVK_LAUNCH(2); break;
+        case 128: NVK_LAUNCH(4); break;
+        case 256: NVK_LAUNCH(8); break;
+        default: return fail(NVK_ERR_UNSUPPORTED, "decode attention (int8): head_dim must be 64, 128 or 256 (got %d)", a.base.head_dim);
+    }
+#undef NVK_LAUNCH
+    return check_launch("decode_int8_rowwise_kernel launch");
+}
+
+}  // namespace
+
+int launch_store_int8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                      const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,
+                      int dtype, cudaStream_t stream) {
+    switch (dtype) {
+        case NVK_BF16: return launch_store_typed<__nv_bfloat16>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
+        case NVK_F16: return launch_store_typed<__half>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
+        default: return launch_store_typed<float>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
+    }
+}
+
+int launch_rowwise_decode_int8(const DecodeInt8Args& a) {
+    switch (a.base.dtype) {
+        case NVK_BF16: return launch_rowwise_typed<__nv_bfloat16>(a);
+        case NVK_F16: return launch_rowwise_typed<__half>(a);
+        default: return launch_rowwise_typed<float>(a);
+    }
+}
+
+}  // namespace nvk

@@ -115,6 +115,55 @@ int nvk_decode_attention_paged(const void* query, const void* k_cache, const voi
     return launch_rowwise_decode(a);
 }
 
+int nvk_store_kvcache_int8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale,
+                           void* v_scale, const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads,
+                           int head_dim, int64_t cache_rows, int dtype, void* stream) {
+    if (!key || !value || !k_cache || !v_cache || !k_scale || !v_scale || !slot_mapping)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: every tensor must be defined");
+    if (!is_compute_dtype(dtype)) return fail(NVK_ERR_INVALID_ARGUMENT, "unsupported input dtype for store_kvcache_int8");
+    if (num_kv_heads <= 0 || head_dim <= 0 || cache_rows <= 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: dimensions must be positive");
+    if (num_tokens <= 0) return NVK_OK;   // the reference returns without a launch (kvcache.cu:327)
+    const size_t in_align = static_cast<size_t>(head_dim / 32) * (dtype == NVK_F32 ? 4 : 2);
+    if (!aligned_to(key, in_align > 16 ? 16 : in_align) || !aligned_to(value, in_align > 16 ? 16 : in_align) ||
+        !aligned_to(k_cache, 8) || !aligned_to(v_cache, 8) || !aligned_to(k_scale, 2) || !aligned_to(v_scale, 2))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: misaligned tensor");
+    return launch_store_int8(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads,
+                             head_dim, cache_rows, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, const void* v_cache, const void* k_scale,
+                                    const void* v_scale, const int32_t* context_lens, const int32_t* block_tables,
+                                    int64_t batch, int64_t max_blocks, int64_t num_cache_blocks, int num_heads,
+                                    int num_kv_heads, int head_dim, int block_size, float scale, void* output, int dtype,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+    if (!query || !k_cache || !v_cache || !k_scale || !v_scale || !context_lens || !block_tables || !output)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (int8) requires KV cache, scales, context_lens, and block_tables");
+    if (!is_compute_dtype(dtype)) return fail(NVK_ERR_INVALID_ARGUMENT, "unsupported query dtype for decode_attention_paged_int8");
+    if (batch < 0 || max_blocks <= 0 || num_cache_blocks <= 0 || num_heads <= 0 || num_kv_heads <= 0 ||
+        head_dim <= 0 || block_size <= 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "attention dimensions must be positive");
+    if (num_heads % num_kv_heads != 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
+    if (batch == 0) return NVK_OK;
+    DecodeInt8Args a{{query, k_cache, v_cache, context_lens, block_tables, output, batch, max_blocks, num_cache_blocks,
+                      num_heads, num_kv_heads, head_dim, block_size, scale, dtype, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream)},
+                     k_scale, v_scale};
+    if (decode_int8_mma_supported(a)) {
+        if (workspace != nullptr) {
+            const size_t need = decode_mma_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size);
+            if (workspace_bytes < need)
+                return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (int8): workspace of %zu bytes given, %zu needed",
+                            workspace_bytes, need);
+            if (!aligned_to(workspace, 16))
+                return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (int8): workspace must be 16-byte aligned");
+        }
+        return launch_decode_int8_mma(a);
+    }
+    return launch_rowwise_decode_int8(a);
+}
+
 int nvk_prefill_attention_varlen(const void* query, const void* key, const void* value, const void* k_cache,
                                  const void* v_cache, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
                                  const int32_t* block_tables, int64_t num_seqs, int64_t total_q, int64_t total_k,

@@ -198,6 +198,96 @@ void oracle_decode_attention_paged(const float* query, const float* k_cache, con
     }
 }
 
+/* ---- int8 KV cache --------------------------------------------------------------------- */
+
+/* src/kernels/kvcache.cu:222-296 (store_kvcache_int8_kernel): per (token, KV head) the absolute maximum of the head
+ * vector gives scale = max(absmax / 127, 1e-10) (stored as fp16) and q = clamp(rint(x * (127 / max(absmax, 1e-10)))). */
+void oracle_store_kvcache_int8(const float* key, const float* value, int8_t* k_cache, int8_t* v_cache,
+                               float* k_scale, float* v_scale, const int32_t* slot_mapping,
+                               int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows) {
+    for (int64_t token = 0; token < num_tokens; ++token) {
+        const int64_t slot = slot_mapping[token];
+        if (slot < 0 || slot >= cache_rows) continue;
+        for (int h = 0; h < num_kv_heads; ++h) {
+            for (int which = 0; which < 2; ++which) {
+                const float* src = (which ? value : key) + (token * num_kv_heads + h) * head_dim;
+                int8_t* dst = (which ? v_cache : k_cache) + (slot * num_kv_heads + h) * head_dim;
+                float absmax = 0.0f;
+                for (int d = 0; d < head_dim; ++d) {
+                    const float a = fabsf(src[d]);
+                    if (a > absmax) absmax = a;
+                }
+                float sc = absmax / 127.0f;
+                sc = fmaxf(sc, 1e-10f);
+                const float inv_sc = 127.0f / fmaxf(absmax, 1e-10f);
+                for (int d = 0; d < head_dim; ++d) {
+                    int q = (int)nearbyintf(src[d] * inv_sc);   /* __float2int_rn */
+                    if (q > 127) q = 127;
+                    if (q < -127) q = -127;
+                    dst[d] = (int8_t)q;
+                }
+                (which ? v_scale : k_scale)[slot * num_kv_heads + h] = oracle_round_fp16(sc);   /* __float2half */
+            }
+        }
+    }
+}
+
+/* src/kernels/attention.cu:746-842 (decode_paged_attention_int8_kernel): as the decode kernel above with
+ * k = int8 * k_scale and v = int8 * v_scale (scales per cache row and KV head, fp16 widened to float). */
+void oracle_decode_attention_paged_int8(const float* query, const int8_t* k_cache, const int8_t* v_cache,
+                                        const float* k_scale, const float* v_scale,
+                                        const int32_t* context_lens, const int32_t* block_tables,
+                                        int64_t batch, int64_t max_blocks, int num_heads, int num_kv_heads,
+                                        int head_dim, int block_size, float scale, float* output, int num_threads) {
+    const int64_t total = batch * num_heads;
+    (void)num_threads;
+#ifdef _OPENMP
+#pragma omp parallel for schedule(dynamic, 1) num_threads(num_threads > 0 ? num_threads : 1)
+#endif
+    for (int64_t work = 0; work < total; ++work) {
+        const int64_t seq = work / num_heads;
+        const int head = (int)(work % num_heads);
+        const int kv_head = kv_head_for_query_head(head, num_heads, num_kv_heads);
+        const float* q = query + (seq * num_heads + head) * head_dim;
+        float* out = output + (seq * num_heads + head) * head_dim;
+        const int64_t k_len = context_lens[seq];
+        if (k_len <= 0) {
+            for (int d = 0; d < head_dim; ++d) out[d] = 0.0f;
+            continue;
+        }
+        float running_max = -INFINITY;
+        float running_sum = 0.0f;
+        float* v_acc = (float*)calloc((size_t)head_dim, sizeof(float));
+        float* k_row = (float*)malloc((size_t)head_dim * sizeof(float));
+        const int32_t* table = block_tables + seq * max_blocks;
+        for (int64_t k_index = 0; k_index < k_len; ++k_index) {
+            const int64_t block_id = table[k_index / block_size];
+            const int64_t cache_row = block_id * block_size + k_index % block_size;
+            const float ks = k_scale[cache_row * num_kv_heads + kv_head];
+            const float vs = v_scale[cache_row * num_kv_heads + kv_head];
+            const int8_t* k_ptr = k_cache + (cache_row * num_kv_heads + kv_head) * head_dim;
+            const int8_t* v_ptr = v_cache + (cache_row * num_kv_heads + kv_head) * head_dim;
+            for (int d = 0; d < head_dim; ++d) k_row[d] = (float)k_ptr[d] * ks;
+            const float qk = warp_strided_dot(q, k_row, head_dim) * scale;
+            const float old_max = running_max;
+            running_max = fmaxf(running_max, qk);
+            const float correction = expf(old_max - running_max);
+            const float exp_qk = expf(qk - running_max);
+            running_sum = running_sum * correction + exp_qk;
+            for (int d = 0; d < head_dim; ++d) {
+                const float v_val = (float)v_ptr[d] * vs;
+                v_acc[d] = v_acc[d] * correction + exp_qk * v_val;
+            }
+        }
+        {
+            const float inv = (running_sum > 0.0f) ? (1.0f / running_sum) : 0.0f;
+            for (int d = 0; d < head_dim; ++d) out[d] = v_acc[d] * inv;
+        }
+        free(k_row);
+        free(v_acc);
+    }
+}
+
 /* ---- prefill ----------------------------------------------------------------------------- */
 
 /* One query row against keys addressed by `row_of_key`; shared by dense and paged prefill. */

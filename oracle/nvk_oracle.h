@@ -36,6 +36,20 @@ void oracle_decode_attention_paged(const float* query, const float* k_cache, con
                                    int num_kv_heads, int head_dim, int block_size, float scale,
                                    float* output, int num_threads);
 
+/* src/kernels/kvcache.cu:222-296 (store_kvcache_int8_kernel).  key / value are [tokens, Hkv, D] floats already
+ * representable in the model dtype; caches are int8 [cache_rows, Hkv, D]; scales are [cache_rows, Hkv], returned as
+ * floats that hold the fp16-rounded value the reference stores. */
+void oracle_store_kvcache_int8(const float* key, const float* value, int8_t* k_cache, int8_t* v_cache,
+                               float* k_scale, float* v_scale, const int32_t* slot_mapping,
+                               int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows);
+
+/* src/kernels/attention.cu:746-842 (decode_paged_attention_int8_kernel). */
+void oracle_decode_attention_paged_int8(const float* query, const int8_t* k_cache, const int8_t* v_cache,
+                                        const float* k_scale, const float* v_scale,
+                                        const int32_t* context_lens, const int32_t* block_tables,
+                                        int64_t batch, int64_t max_blocks, int num_heads, int num_kv_heads,
+                                        int head_dim, int block_size, float scale, float* output, int num_threads);
+
 /* src/kernels/attention.cu:114-202 (prefill_dense_attention_kernel) with
  * locate_prefill_sequence (:27-54).  cu_seqlens_* may both be NULL: one sequence. */
 void oracle_prefill_attention_dense(const float* query, const float* key, const float* value,

@@ -84,6 +84,42 @@ int nvkref_decode_attention_paged(const void* query, const void* k_cache, const 
     });
 }
 
+/* int8 KV cache: caches are int8 (dtype code 5), scales fp16 (code 0), both per the reference's headers
+ * (include/kernels/kvcache.h:14-24, include/kernels/attention.h:43-56). */
+int nvkref_store_kvcache_int8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale,
+                              void* v_scale, const void* slot_mapping, int64_t num_tokens, int num_kv_heads,
+                              int head_dim, int64_t num_cache_blocks, int block_size, int dtype, void* stream) {
+    return guarded([&] {
+        auto k = borrow(key, {num_tokens, num_kv_heads, head_dim}, dtype);
+        auto v = borrow(value, {num_tokens, num_kv_heads, head_dim}, dtype);
+        auto kc = borrow(k_cache, {num_cache_blocks, block_size, num_kv_heads, head_dim}, 5);
+        auto vc = borrow(v_cache, {num_cache_blocks, block_size, num_kv_heads, head_dim}, 5);
+        auto ks = borrow(k_scale, {num_cache_blocks, block_size, num_kv_heads}, 0);
+        auto vs = borrow(v_scale, {num_cache_blocks, block_size, num_kv_heads}, 0);
+        auto sm = borrow(slot_mapping, {num_tokens}, 3);
+        nano_vllm::store_kvcache_int8(k, v, kc, vc, ks, vs, sm, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int nvkref_decode_attention_paged_int8(const void* query, const void* k_cache, const void* v_cache,
+                                       const void* k_scale, const void* v_scale, const void* context_lens,
+                                       const void* block_tables, int64_t batch, int64_t max_blocks,
+                                       int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim,
+                                       int block_size, float scale, void* output, int dtype, void* stream) {
+    return guarded([&] {
+        auto q = borrow(query, {batch, num_heads, head_dim}, dtype);
+        auto o = borrow(output, {batch, num_heads, head_dim}, dtype);
+        auto kc = borrow(k_cache, {num_cache_blocks, block_size, num_kv_heads, head_dim}, 5);
+        auto vc = borrow(v_cache, {num_cache_blocks, block_size, num_kv_heads, head_dim}, 5);
+        auto ks = borrow(k_scale, {num_cache_blocks, block_size, num_kv_heads}, 0);
+        auto vs = borrow(v_scale, {num_cache_blocks, block_size, num_kv_heads}, 0);
+        auto cl = borrow(context_lens, {batch}, 3);
+        auto bt = borrow(block_tables, {batch, max_blocks}, 3);
+        nano_vllm::launch_decode_attention_paged_int8(q, kc, vc, ks, vs, cl, bt, num_kv_heads, head_dim,
+                                                      block_size, scale, o, static_cast<cudaStream_t>(stream));
+    });
+}
+
 int nvkref_prefill_attention_dense(const void* query, const void* key, const void* value,
                                    const void* cu_seqlens_q, const void* cu_seqlens_k,
                                    int64_t num_seqs, int64_t total_q, int64_t total_k,
