@@ -39,6 +39,9 @@ CASES = {
     "store_bf16": ("store", "bf16", dict(tokens=37, row_elems=2 * 128, cache_rows=128, seed=505)),
     "prologue_bf16": ("prologue", "bf16", dict(rows=19, num_q_heads=8, num_kv_heads=2, head_dim=128, cache_rows=256,
                                                max_positions=300, seed=506)),
+    # int8 KV cache: every row of a bf16 cache goes through the reference's quantising store, then its int8 decode
+    "int8_kv_bf16": ("int8", "bf16", dict(batch=4, num_heads=8, num_kv_heads=2, head_dim=128, block_size=16,
+                                          ctx_lo=1, ctx_hi=90, seed=507)),
 }
 
 
@@ -53,7 +56,7 @@ def make_inputs(name):
     """Seeded inputs of a case as numpy arrays (float32 holding values representable in the case's dtype)."""
     kind, dtype, kw = CASES[name]
     wl = workloads()
-    if kind == "decode":
+    if kind in ("decode", "int8"):
         return wl.make_decode_workload(**kw)
     if kind == "prefill":
         return wl.make_prefill_workload(**kw)
@@ -143,6 +146,30 @@ def main(out_dir):
                                                     kw["num_kv_heads"], kw["head_dim"], kw["block_size"],
                                                     ctypes.c_float(w["scale"]), P(o), code, None))
             out["out"] = bits(o)
+        elif kind == "int8":
+            hkv, d, bs = kw["num_kv_heads"], kw["head_dim"], kw["block_size"]
+            blocks = w["k_cache"].shape[0]
+            rows = blocks * bs
+            key, value = D(w["k_cache"].reshape(rows, hkv, d), tt), D(w["v_cache"].reshape(rows, hkv, d), tt)
+            kc = torch.zeros((blocks, bs, hkv, d), dtype=torch.int8, device=dev)
+            vc = torch.zeros_like(kc)
+            ks = torch.zeros((blocks, bs, hkv), dtype=torch.float16, device=dev)
+            vs = torch.zeros_like(ks)
+            slots = torch.arange(rows, dtype=torch.int32, device=dev)
+            keep.extend([kc, vc, ks, vs, slots])
+            check(ref.nvkref_store_kvcache_int8(P(key), P(value), P(kc), P(vc), P(ks), P(vs), P(slots), ctypes.c_int64(rows), hkv, d,
+                                                ctypes.c_int64(blocks), bs, code, None))
+            q = D(w["q"], tt)
+            o = torch.empty_like(q)
+            ctx, bt = D(w["context_lens"]), D(w["block_tables"])
+            check(ref.nvkref_decode_attention_paged_int8(P(q), P(kc), P(vc), P(ks), P(vs), P(ctx), P(bt), ctypes.c_int64(kw["batch"]),
+                                                         ctypes.c_int64(bt.shape[1]), ctypes.c_int64(blocks), kw["num_heads"], hkv, d, bs,
+                                                         ctypes.c_float(w["scale"]), P(o), code, None))
+            out["k_cache"] = kc.cpu().numpy().reshape(rows, hkv, d)
+            out["v_cache"] = vc.cpu().numpy().reshape(rows, hkv, d)
+            out["k_scale"] = ks.float().cpu().numpy().reshape(rows, hkv)      # fp16 values, widened exactly
+            out["v_scale"] = vs.float().cpu().numpy().reshape(rows, hkv)
+            out["out"] = bits(o)
         elif kind == "prefill":
             q = D(w["q"], tt)
             o = torch.empty_like(q)
@@ -185,4 +212,7 @@ def main(out_dir):
 
 
 if __name__ == "__main__":
+    # python tests/golden/make_golden.py [output_dir] [case ...]: with case names, only those fixtures are (re)written
+    if len(sys.argv) > 2:
+        CASES = {k: v for k, v in CASES.items() if k in sys.argv[2:]}
     main(sys.argv[1] if len(sys.argv) > 1 else HERE)

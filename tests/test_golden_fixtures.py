@@ -141,3 +141,49 @@ def test_gpu_store_and_prologue_match_reference_fixtures():
     for got, ref in ((to_np(q_out), fx["q_out"]), (to_np(kc), fx["k_cache"])):
         assert _bf16_ulp_close(got, ref)
         assert (got == ref).mean() > 0.97
+
+
+# ------------------------------------------------------------------------------------------ int8 KV cache
+
+def _int8_case():
+    kw, w, fx = _case("int8_kv_bf16")
+    rows = w["k_cache"].shape[0] * kw["block_size"]
+    shape = (rows, kw["num_kv_heads"], kw["head_dim"])
+    return kw, w, fx, rows, shape
+
+
+def test_oracle_int8_store_is_bit_exact_with_reference_kernel():
+    kw, w, fx, rows, shape = _int8_case()
+    kc = np.zeros(shape, np.int8); vc = np.zeros(shape, np.int8)
+    ks = np.zeros(shape[:2], np.float32); vs = np.zeros(shape[:2], np.float32)
+    oracle.store_kvcache_int8(w["k_cache"].reshape(shape), w["v_cache"].reshape(shape), kc, vc, ks, vs,
+                              np.arange(rows, dtype=np.int32))
+    assert np.array_equal(kc, fx["k_cache"]) and np.array_equal(vc, fx["v_cache"])
+    assert np.array_equal(ks, fx["k_scale"]) and np.array_equal(vs, fx["v_scale"])
+
+
+def test_oracle_int8_decode_matches_reference_kernel():
+    kw, w, fx, rows, shape = _int8_case()
+    out = oracle.decode_attention_paged_int8(w["q"], fx["k_cache"], fx["v_cache"], fx["k_scale"], fx["v_scale"], w["context_lens"],
+                                             w["block_tables"], kw["num_kv_heads"], kw["head_dim"], kw["block_size"], w["scale"])
+    assert _bf16_ulp_close(oracle.round_bf16(out), fx["out"])
+
+
+@pytest.mark.gpu
+def test_library_int8_store_and_decode_match_reference_kernels():
+    import torch
+    kw, w, fx, rows, shape = _int8_case()
+    bf = torch.bfloat16
+    lib = nvk()
+    kc = torch.zeros(shape, dtype=torch.int8, device="cuda"); vc = torch.zeros_like(kc)
+    ks = torch.zeros(shape[:2], dtype=torch.float16, device="cuda"); vs = torch.zeros_like(ks)
+    lib.store_kvcache_int8(to_dev(w["k_cache"].reshape(shape), bf), to_dev(w["v_cache"].reshape(shape), bf), kc, vc, ks, vs,
+                           torch.arange(rows, dtype=torch.int32, device="cuda"))
+    q = to_dev(w["q"], bf)
+    out = torch.empty_like(q)
+    lib.launch_decode_attention_paged_int8(q, kc, vc, ks, vs, to_dev(w["context_lens"]), to_dev(w["block_tables"]), kw["num_kv_heads"],
+                                           kw["head_dim"], kw["block_size"], w["scale"], out)
+    torch.cuda.synchronize()
+    assert np.array_equal(kc.cpu().numpy(), fx["k_cache"]) and np.array_equal(vc.cpu().numpy(), fx["v_cache"])
+    assert np.array_equal(ks.float().cpu().numpy(), fx["k_scale"]) and np.array_equal(vs.float().cpu().numpy(), fx["v_scale"])
+    assert_attention_close(to_np(out), fx["out"])
