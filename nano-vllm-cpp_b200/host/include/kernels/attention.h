@@ -21,7 +21,7 @@ void launch_decode_attention_paged(const Tensor& query, const Tensor& k_cache, c
                                    int head_dim, int block_size, float scale, Tensor& output,
                                    cudaStream_t stream = nullptr);
 
-// Outside the scope of this library: throws std::invalid_argument("unsupported").
+// Decode attention over an int8 cache with fp16 scales (include/kernels/attention.h:43-56 of the reference).
 void launch_decode_attention_paged_int8(const Tensor& query, const Tensor& k_cache, const Tensor& v_cache,
                                         const Tensor& k_scale, const Tensor& v_scale, const Tensor& context_lens,
                                         const Tensor& block_tables, int num_kv_heads, int head_dim, int block_size,

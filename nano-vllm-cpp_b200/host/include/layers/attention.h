@@ -12,7 +12,8 @@ public:
     Attention(int num_heads, int num_kv_heads, int head_dim, int block_size);
 
     void set_kv_cache(const Tensor& k_cache, const Tensor& v_cache);
-    // int8 caches are outside the scope of this library: throws std::invalid_argument("unsupported").
+    // int8 caches [blocks, block_size, Hkv, D] with fp16 scales [blocks, block_size, Hkv]: new K/V are quantised on
+    // store, decode reads them through launch_decode_attention_paged_int8, prefill attends over the dense K/V.
     void set_kv_cache_int8(const Tensor& k_cache, const Tensor& v_cache, const Tensor& k_scale, const Tensor& v_scale);
 
     // Prefill or decode according to get_context(); stores key/value first when a cache and a
@@ -29,7 +30,7 @@ public:
     const Tensor& v_cache() const { return v_cache_; }
     Tensor& k_scale() { return k_scale_; }
     Tensor& v_scale() { return v_scale_; }
-    bool is_int8() const { return false; }
+    bool is_int8() const { return is_int8_; }
 
 private:
     int num_heads_ = 0;
@@ -41,6 +42,7 @@ private:
     Tensor v_cache_;
     Tensor k_scale_;
     Tensor v_scale_;
+    bool is_int8_ = false;
 };
 
 }  // namespace nano_vllm

@@ -53,10 +53,23 @@ void Attention::set_kv_cache(const Tensor& k_cache, const Tensor& v_cache) {
     if (k_cache.sizes() != v_cache.sizes()) throw std::invalid_argument("k_cache and v_cache must have the same shape");
     k_cache_ = k_cache;
     v_cache_ = v_cache;
+    is_int8_ = false;
 }
 
-void Attention::set_kv_cache_int8(const Tensor&, const Tensor&, const Tensor&, const Tensor&) {
-    throw std::invalid_argument("unsupported: int8 KV cache");
+void Attention::set_kv_cache_int8(const Tensor& k_cache, const Tensor& v_cache, const Tensor& k_scale, const Tensor& v_scale) {
+    require_cuda_contiguous("k_cache", k_cache);
+    require_cuda_contiguous("v_cache", v_cache);
+    require_cuda_contiguous("k_scale", k_scale);
+    require_cuda_contiguous("v_scale", v_scale);
+    if (k_cache.dtype() != ScalarType::kInt8 || v_cache.dtype() != ScalarType::kInt8)
+        throw std::invalid_argument("int8 KV cache tensors must be int8");
+    if (k_scale.dtype() != ScalarType::kFloat16 || v_scale.dtype() != ScalarType::kFloat16)
+        throw std::invalid_argument("int8 KV cache scales must be float16");
+    k_cache_ = k_cache;
+    v_cache_ = v_cache;
+    k_scale_ = k_scale;
+    v_scale_ = v_scale;
+    is_int8_ = true;
 }
 
 Tensor Attention::forward(const Tensor& query, const Tensor& key, const Tensor& value, DeviceAllocator& allocator,
@@ -84,7 +97,11 @@ Tensor Attention::forward(const Tensor& query, const Tensor& key, const Tensor& 
 
     // new K/V go into the cache first: both prefill-with-prefix and decode read them back from it
     if (k_cache_.defined() && ctx.slot_mapping.defined()) {
-        store_kvcache(key, value, k_cache_, v_cache_, ctx.slot_mapping, stream);
+        if (is_int8_) {
+            store_kvcache_int8(key, value, k_cache_, v_cache_, k_scale_, v_scale_, ctx.slot_mapping, stream);
+        } else {
+            store_kvcache(key, value, k_cache_, v_cache_, ctx.slot_mapping, stream);
+        }
     }
 
     Tensor output = Tensor::empty(query.sizes(), query.dtype(), query.device(), allocator);
@@ -92,7 +109,7 @@ Tensor Attention::forward(const Tensor& query, const Tensor& key, const Tensor& 
     if (ctx.is_prefill) {
         const Tensor* cu_q = ctx.cu_seqlens_q.defined() ? &ctx.cu_seqlens_q : nullptr;
         const Tensor* cu_k = ctx.cu_seqlens_k.defined() ? &ctx.cu_seqlens_k : nullptr;
-        if (paged) {
+        if (paged && !is_int8_) {   // an int8 cache is only read by decode: prefill attends over the dense K / V it was given
             if (cu_k == nullptr) throw std::invalid_argument("prefill attention with block_tables requires cu_seqlens_k");
             launch_prefill_attention_paged(query, cu_q, k_cache_, v_cache_, cu_k, ctx.block_tables, num_kv_heads_,
                                            head_dim_, block_size_, scale_, output, stream);
@@ -103,6 +120,11 @@ Tensor Attention::forward(const Tensor& query, const Tensor& key, const Tensor& 
     }
     if (!paged || !ctx.context_lens.defined())
         throw std::invalid_argument("decode attention requires KV cache, context_lens, and block_tables");
+    if (is_int8_) {
+        launch_decode_attention_paged_int8(query, k_cache_, v_cache_, k_scale_, v_scale_, ctx.context_lens, ctx.block_tables,
+                                           num_kv_heads_, head_dim_, block_size_, scale_, output, stream);
+        return output;
+    }
     flash_attn_decode_kvcache(query, k_cache_, v_cache_, ctx.context_lens, ctx.block_tables, num_kv_heads_, head_dim_,
                               block_size_, scale_, output, allocator, stream);
     return output;
@@ -114,6 +136,11 @@ Tensor Attention::forward_decode_flash_only(const Tensor& query, DeviceAllocator
         throw std::invalid_argument("forward_decode_flash_only requires KV cache, context_lens, and block_tables");
     require_cuda_contiguous("query", query);
     Tensor output = Tensor::empty(query.sizes(), query.dtype(), query.device(), allocator);
+    if (is_int8_) {
+        launch_decode_attention_paged_int8(query, k_cache_, v_cache_, k_scale_, v_scale_, ctx.context_lens, ctx.block_tables,
+                                           num_kv_heads_, head_dim_, block_size_, scale_, output, stream);
+        return output;
+    }
     flash_attn_decode_kvcache(query, k_cache_, v_cache_, ctx.context_lens, ctx.block_tables, num_kv_heads_, head_dim_,
                               block_size_, scale_, output, allocator, stream);
     return output;

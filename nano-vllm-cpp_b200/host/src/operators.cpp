@@ -125,8 +125,38 @@ void store_kvcache(const Tensor& key, const Tensor& value, Tensor& k_cache, Tens
                                           code(slot_mapping.dtype()), tokens, k.cols, k_rows, code(key.dtype()), stream));
 }
 
-void store_kvcache_int8(const Tensor&, const Tensor&, Tensor&, Tensor&, Tensor&, Tensor&, const Tensor&, cudaStream_t) {
-    throw std::invalid_argument("unsupported: int8 KV cache");
+void store_kvcache_int8(const Tensor& key, const Tensor& value, Tensor& k_cache, Tensor& v_cache, Tensor& k_scale,
+                        Tensor& v_scale, const Tensor& slot_mapping, cudaStream_t stream) {
+    ensure_cuda_tensor("key", key);
+    ensure_cuda_tensor("value", value);
+    ensure_cuda_tensor("k_cache", k_cache);
+    ensure_cuda_tensor("v_cache", v_cache);
+    ensure_cuda_tensor("k_scale", k_scale);
+    ensure_cuda_tensor("v_scale", v_scale);
+    ensure_cuda_tensor("slot_mapping", slot_mapping);
+    validate_supported_dtype("key", key.dtype());
+    ensure_same_dtype("key", key, "value", value);
+    if (k_cache.dtype() != ScalarType::kInt8 || v_cache.dtype() != ScalarType::kInt8)
+        throw std::invalid_argument("store_kvcache_int8 requires int8 caches");
+    if (k_scale.dtype() != ScalarType::kFloat16 || v_scale.dtype() != ScalarType::kFloat16)
+        throw std::invalid_argument("store_kvcache_int8 requires float16 scales");
+    if (slot_mapping.dtype() != ScalarType::kInt32) throw std::invalid_argument("slot_mapping must be int32 for the int8 store");
+    const int64_t tokens = static_cast<int64_t>(slot_mapping.numel());
+    if (tokens <= 0) return;   // the reference returns without a launch
+    if (key.dim() != 3) throw std::invalid_argument("key must be rank-3 for int8 store");
+    ensure_same_shape("key", key, "value", value);
+    if (key.sizes()[0] != tokens) throw std::invalid_argument("key rows must match slot_mapping");
+    const int heads = static_cast<int>(key.sizes()[1]);
+    const int head_dim = static_cast<int>(key.sizes()[2]);
+    const int64_t row = static_cast<int64_t>(heads) * head_dim;
+    const int64_t rows = cache_rows_from_tensor("k_cache", k_cache, row);
+    if (cache_rows_from_tensor("v_cache", v_cache, row) != rows)
+        throw std::invalid_argument("k_cache and v_cache must contain the same number of slots");
+    if (static_cast<int64_t>(k_scale.numel()) != rows * heads || static_cast<int64_t>(v_scale.numel()) != rows * heads)
+        throw std::invalid_argument("k_scale and v_scale must hold one value per cache row and KV head");
+    throw_on_nvk_status(nvk_store_kvcache_int8(key.data(), value.data(), k_cache.data(), v_cache.data(), k_scale.data(),
+                                               v_scale.data(), static_cast<const int32_t*>(slot_mapping.data()), tokens, heads,
+                                               head_dim, rows, code(key.dtype()), stream));
 }
 
 // ---- fused decode prologue ---------------------------------------------------------------------------
@@ -209,9 +239,43 @@ void flash_attn_decode_kvcache(const Tensor& query, const Tensor& k_cache, const
                   &allocator, stream);
 }
 
-void launch_decode_attention_paged_int8(const Tensor&, const Tensor&, const Tensor&, const Tensor&, const Tensor&,
-                                        const Tensor&, const Tensor&, int, int, int, float, Tensor&, cudaStream_t) {
-    throw std::invalid_argument("unsupported: int8 KV cache");
+void launch_decode_attention_paged_int8(const Tensor& query, const Tensor& k_cache, const Tensor& v_cache,
+                                        const Tensor& k_scale, const Tensor& v_scale, const Tensor& context_lens,
+                                        const Tensor& block_tables, int num_kv_heads, int head_dim, int block_size,
+                                        float scale, Tensor& output, cudaStream_t stream) {
+    check_qo(query, output);
+    validate_supported_dtype("query", query.dtype());
+    ensure_cuda_tensor("k_cache", k_cache);
+    ensure_cuda_tensor("v_cache", v_cache);
+    ensure_cuda_tensor("k_scale", k_scale);
+    ensure_cuda_tensor("v_scale", v_scale);
+    ensure_cuda_tensor("context_lens", context_lens);
+    ensure_cuda_tensor("block_tables", block_tables);
+    if (k_cache.dtype() != ScalarType::kInt8 || v_cache.dtype() != ScalarType::kInt8)
+        throw std::invalid_argument("int8 decode attention requires int8 caches");
+    if (k_scale.dtype() != ScalarType::kFloat16 || v_scale.dtype() != ScalarType::kFloat16)
+        throw std::invalid_argument("int8 decode attention requires float16 scales");
+    if (context_lens.dtype() != ScalarType::kInt32 || block_tables.dtype() != ScalarType::kInt32)
+        throw std::invalid_argument("context_lens and block_tables must be int32");
+    if (block_tables.dim() != 2 || block_tables.sizes()[0] != query.sizes()[0])
+        throw std::invalid_argument("block_tables must be [batch, max_blocks]");
+    if (static_cast<int64_t>(context_lens.numel()) != query.sizes()[0])
+        throw std::invalid_argument("context_lens must hold one entry per sequence");
+    if (query.sizes()[2] != head_dim) throw std::invalid_argument("query head_dim does not match head_dim");
+    const int64_t batch = query.sizes()[0];
+    const int heads = static_cast<int>(query.sizes()[1]);
+    const int64_t max_blocks = block_tables.sizes()[1];
+    const int64_t per_block = static_cast<int64_t>(block_size) * num_kv_heads * head_dim;
+    if (per_block <= 0 || static_cast<int64_t>(k_cache.numel()) % per_block != 0 || k_cache.numel() != v_cache.numel())
+        throw std::invalid_argument("int8 caches do not hold a whole number of blocks");
+    const int64_t blocks = static_cast<int64_t>(k_cache.numel()) / per_block;
+    if (static_cast<int64_t>(k_scale.numel()) != blocks * block_size * num_kv_heads || k_scale.numel() != v_scale.numel())
+        throw std::invalid_argument("k_scale and v_scale must hold one value per cache row and KV head");
+    // no allocator in this signature (as in the reference): the call runs without split-K scratch
+    throw_on_nvk_status(nvk_decode_attention_paged_int8(
+        query.data(), k_cache.data(), v_cache.data(), k_scale.data(), v_scale.data(),
+        static_cast<const int32_t*>(context_lens.data()), static_cast<const int32_t*>(block_tables.data()), batch, max_blocks,
+        blocks, heads, num_kv_heads, head_dim, block_size, scale, output.data(), code(query.dtype()), nullptr, 0, stream));
 }
 
 // ---- prefill ------------------------------------------------------------------------------------------

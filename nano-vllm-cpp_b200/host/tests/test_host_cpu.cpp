@@ -225,8 +225,10 @@ TEST_CASE(operators_reject_bad_operands_before_any_cuda_call) {
     CHECK_THROWS(Attention(0, 1, 4, 256), std::invalid_argument);
     Attention attention(1, 1, 4, 3);
     CHECK_THROWS(attention.set_kv_cache(cache, cache), std::invalid_argument);                  // cache not on CUDA
-    CHECK_THROWS(attention.set_kv_cache_int8(cache, cache, cache, cache), std::invalid_argument);
+    CHECK_THROWS(attention.set_kv_cache_int8(cache, cache, cache, cache), std::invalid_argument);       // not on CUDA
+    CHECK_THROWS(attention.set_kv_cache_int8(dev_cache, dev_cache, dev_cache, dev_cache), std::invalid_argument);   // not int8
     CHECK_THROWS(store_kvcache_int8(key, key, cache, cache, cache, cache, slots), std::invalid_argument);
+    CHECK_THROWS(store_kvcache_int8(dev_key, dev_key, dev_cache, dev_cache, dev_cache, dev_cache, dev_slots), std::invalid_argument);
 }
 
 int main() { return check::run_all(); }

@@ -119,6 +119,50 @@ TEST_CASE(attention_decode_reads_kv_cache) {
     reset_context();
 }
 
+TEST_CASE(attention_with_int8_kv_cache_quantises_on_store_and_dequantises_in_decode) {
+    // Values chosen so that quantisation is exact (absmax 127 -> scale 1): the result must equal plain attention.
+    CudaAllocator& alloc = CudaAllocator::instance();
+    const int D = 64;
+    Attention attention(2, 1, D, 4);
+    Tensor kc = Tensor::zeros({2, 4, 1, D}, ScalarType::kInt8, kDev, alloc), vc = Tensor::zeros({2, 4, 1, D}, ScalarType::kInt8, kDev, alloc);
+    Tensor ks = Tensor::zeros({2, 4, 1}, ScalarType::kFloat16, kDev, alloc), vs = Tensor::zeros({2, 4, 1}, ScalarType::kFloat16, kDev, alloc);
+    attention.set_kv_cache_int8(kc, vc, ks, vs);
+    CHECK(attention.is_int8());
+    std::vector<float> q(2 * D, 0.0f), k1(D, 0.0f), v1(D, 0.0f), k2(D, 0.0f), v2(D, 0.0f);
+    q[0] = 0.01f; q[D + 1] = 0.02f;           // head 0 looks along dimension 0, head 1 along dimension 1
+    k1[0] = 127.0f; k1[1] = -127.0f;
+    v1[0] = 127.0f; v1[1] = 64.0f; v1[2] = -32.0f;
+    v2[3] = 127.0f; v2[0] = -1.0f;            // k2 is the zero vector: scale floors to 0, every score 0
+    Tensor tq = device_floats({1, 2, D}, q);
+    // token 1 -> physical block 1, row 4; a single key: the output is the dequantised value row, whatever the score
+    set_context(false, Tensor(), Tensor(), 0, 0, device_ints({1}, {4}), device_ints({1}, {1}), device_ints({1, 2}, {1, 0}));
+    std::vector<float> got = to_host(attention.forward(tq, device_floats({1, 1, D}, k1), device_floats({1, 1, D}, v1), alloc));
+    for (int h = 0; h < 2; ++h) {
+        CHECK_NEAR(got[h * D + 0], 127.0f, 1e-4);
+        CHECK_NEAR(got[h * D + 1], 64.0f, 1e-4);
+        CHECK_NEAR(got[h * D + 2], -32.0f, 1e-4);
+        CHECK_NEAR(got[h * D + 3], 0.0f, 1e-6);
+    }
+    // token 2 -> row 5; two keys with scores (q . k1) / sqrt(D) and 0
+    set_context(false, Tensor(), Tensor(), 0, 0, device_ints({1}, {5}), device_ints({1}, {2}), device_ints({1, 2}, {1, 0}));
+    got = to_host(attention.forward(tq, device_floats({1, 1, D}, k2), device_floats({1, 1, D}, v2), alloc));
+    const std::vector<float> again = to_host(attention.forward_decode_flash_only(tq, alloc));
+    reset_context();
+    const float inv_sqrt_d = 1.0f / std::sqrt(static_cast<float>(D));
+    const float s_h0 = 0.01f * 127.0f * inv_sqrt_d, s_h1 = 0.02f * -127.0f * inv_sqrt_d;
+    const float scores[2] = {s_h0, s_h1};
+    for (int h = 0; h < 2; ++h) {
+        const float p1 = std::exp(scores[h]) / (std::exp(scores[h]) + 1.0f), p2 = 1.0f - p1;
+        CHECK_NEAR(got[h * D + 0], p1 * 127.0f + p2 * -1.0f, 2e-4);
+        CHECK_NEAR(got[h * D + 1], p1 * 64.0f, 2e-4);
+        CHECK_NEAR(got[h * D + 3], p2 * 127.0f, 2e-4);
+        CHECK_NEAR(again[h * D + 0], got[h * D + 0], 1e-6);
+    }
+    // float (not fp16) scales and non-int8 caches are rejected
+    CHECK_THROWS(attention.set_kv_cache_int8(kc, vc, device_floats({2, 4, 1}, std::vector<float>(8)), vs), std::invalid_argument);
+    CHECK_THROWS(attention.set_kv_cache_int8(device_floats({2, 4, 1, D}, std::vector<float>(8 * D)), vc, ks, vs), std::invalid_argument);
+}
+
 TEST_CASE(attention_prefill_with_prefix_cache_reads_paged_kv_cache) {
     CudaAllocator& alloc = CudaAllocator::instance();
     Attention attention(1, 1, 2, 2);
