@@ -394,8 +394,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e"],
-                    help="decode is the benchmark; prefill / store / prologue / mixed time the remaining kernels of the path "
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e", "decode_int8"],
+                    help="decode is the benchmark; prefill / store / prologue / mixed / decode_int8 time the remaining kernels of the path "
                          "(1 GPU); e2e reports output tokens per second of the whole decoder, tensor-parallel over --gpus")
     ap.add_argument("--e2e-layers", type=int, default=36, help="e2e workload: decoder layers (36 = the named model)")
     ap.add_argument("--e2e-seqs", type=int, default=256, help="e2e workload: number of sequences")
@@ -488,6 +488,8 @@ def main():
             line = kb.bench_prefill(nvk, torch, dev, steps, args.warmup, args.seqs, min(512, args.qmax), args.qmax)
         elif args.workload == "store":
             line = kb.bench_store(nvk, torch, dev, steps, args.warmup)
+        elif args.workload == "decode_int8":
+            line = kb.bench_decode_int8(nvk, torch, dev, steps, args.warmup, batch=args.batch)
         elif args.workload == "mixed":
             line = kb.bench_mixed(nvk, torch, dev, min(steps, 10), min(args.warmup, 3), layers=args.layers)
         else:

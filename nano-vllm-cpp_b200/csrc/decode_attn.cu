@@ -269,34 +269,34 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p,
 //
 // Same block / split / merge structure as decode_split_kernel; what streams from HBM is half as wide:
 // per token and KV head 128 int8 of K, 128 of V and two fp16 scales.  Each warp's cp.async ring carries
-// the int8 tiles (16 tokens x 128 B for K, the same for V); once a tile has landed every lane widens the
-// 16-byte pieces it copied itself to fp16 (x ^ 0x80 glued under the exponent of 1024.0, minus 1152.0:
-// exact, 5 instructions per 4 elements) into one fp16 tile per warp, laid out exactly like the 16-bit
-// kernel's tiles, so ldmatrix and the MMAs are unchanged (run as f16 whatever the query type: the query
-// is converted once, probabilities are <= 1).  The scales never touch the tiles: k_scale multiplies the
-// score of its key after the first MMA, v_scale multiplies the probability of its key before the second
-// (the row sum uses the unscaled probability).  Scales are fetched two tiles ahead into registers by
-// lanes 0-15 (K) and 16-31 (V).
+// the int8 tiles (16 tokens x 128 B for K, the same for V) and the MMA fragments are built from them in
+// registers -- no widened copy in shared memory, no ldmatrix:
+//   * an int8 x becomes the fp16 number 1024 + (x + 128) by gluing the byte (x ^ 0x80) under the exponent
+//     byte 0x64 (one PRMT per pair); the constant 1152 is taken out afterwards: q . (k' - 1152) =
+//     q . k' - 1152 * sum(q), and P (v' - 1152) = P v' - 1152 * sum(P), where sum(P) comes from one extra
+//     MMA per tile against a row of ones, i.e. from exactly the rounded probabilities the other MMAs used;
+//   * the MMAs contract over d (scores) and over keys (output); a contraction does not care in which order
+//     its index runs, and neither does the output care which accumulator row holds which d, so every lane
+//     takes whole 16-byte pieces: for K, piece 4q + t of key row g supplies its k-steps 4q .. 4q + 3 (the
+//     query fragment is loaded with the same permutation); for V, piece g of key rows 2t, 2t+1, 2t+8, 2t+9
+//     supplies all eight d-tiles after a byte interleave of row pairs (two PRMTs), and accumulator row g /
+//     g + 8 of d-tile 2a + e holds d = 16 g + 4 a + 2 e (+ 1);
+//   * pieces are XOR-swizzled in the ring so that those 16-byte reads are conflict free.
+// The scales never touch the tiles: k_scale multiplies the score of its key after the first MMA, v_scale
+// the probability of its key before the second (the row sum uses the unscaled probability).  They are
+// fetched two tiles ahead into registers by lanes 0-15 (K) and 16-31 (V).  MMAs run as f16 whatever the
+// query type: the query is converted once, probabilities are <= 1.
 // ---------------------------------------------------------------------------------------------
 constexpr int kRowBytesI8 = kHeadDim;                      // one head row of int8 K or V
 constexpr int kTileBytesI8 = kTileTokens * kRowBytesI8;    // 2 KiB
 constexpr int kStageBytesI8 = 2 * kTileBytesI8;            // K + V
-constexpr int kWarpBytesI8 = kStages * kStageBytesI8 + kStageBytes;   // ring + one widened K / V tile pair
-constexpr int kSmemBytesI8 = kWarps * kWarpBytesI8;        // 80 KiB -> two blocks per SM
+constexpr int kWarpBytesI8 = kStages * kStageBytesI8;      // 12 KiB
+constexpr int kSmemBytesI8 = kWarps * kWarpBytesI8;        // 48 KiB -> three blocks per SM
+constexpr float kI8Offset = 1152.0f;                       // 1024 (exponent glue) + 128 (sign flip)
 
-// 16 int8 (one 16-byte piece) -> 16 fp16 (two 16-byte pieces)
-__device__ __forceinline__ void widen_i8x16(const uint4& in, uint4& lo, uint4& hi) {
-    const uint32_t w[4] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u, in.z ^ 0x80808080u, in.w ^ 0x80808080u};
-    uint32_t h[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t a = __byte_perm(w[i], 0x64646464u, 0x4140);   // {1024 + b0, 1024 + b1}
-        const uint32_t b = __byte_perm(w[i], 0x64646464u, 0x4342);   // {1024 + b2, 1024 + b3}
-        asm("sub.f16x2 %0, %1, %2;\n" : "=r"(h[2 * i]) : "r"(a), "r"(0x64806480u));      // - 1152 = - (1024 + 128)
-        asm("sub.f16x2 %0, %1, %2;\n" : "=r"(h[2 * i + 1]) : "r"(b), "r"(0x64806480u));
-    }
-    lo = make_uint4(h[0], h[1], h[2], h[3]);
-    hi = make_uint4(h[4], h[5], h[6], h[7]);
+__device__ __forceinline__ uint32_t lds32x4(uint32_t addr, uint32_t (&w)[4]) {
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+    return 0;
 }
 
 struct DecodeInt8Params {
@@ -305,7 +305,7 @@ struct DecodeInt8Params {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const DecodeInt8Params pp) {
+__global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const DecodeInt8Params pp) {
     const DecodeParams& p = pp.base;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_blocks[kMaxChunkBlocks];
@@ -339,32 +339,36 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const De
     }
     __syncthreads();
 
-    // Query fragments as f16: rows g < G of the 16-row A tile, rows 8..15 are zero.
+    // Query fragments as f16, rows g < G of the 16-row A tile (rows 8..15 are zero), in the K permutation:
+    // k-step ks = 4 q + w, positions {2t, 2t+1 | 2t+8, 2t+9} <- d = 64 q + 16 t + 4 w + {0, 1 | 2, 3}.
     uint32_t qa[8][2];
+    float qsum = 0.0f;   // sum over d of the (f16-rounded) query row g
     {
         const T* qrow = static_cast<const T*>(p.q) + (b * p.num_heads + kvh * G + (g < G ? g : 0)) * kHeadDim;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
+            const int d0 = 64 * (ks >> 2) + 16 * t + 4 * (ks & 3);
 #pragma unroll
             for (int hlf = 0; hlf < 2; ++hlf) {
-                const int d = ks * 16 + hlf * 8 + 2 * t;
-                const float x0 = ElemTraits<T>::to_float(qrow[d]), x1 = ElemTraits<T>::to_float(qrow[d + 1]);
-                qa[ks][hlf] = g < G ? ElemTraits<__half>::pack2(x0, x1) : 0u;
+                const __half2 h2 = __floats2half2_rn(ElemTraits<T>::to_float(qrow[d0 + 2 * hlf]), ElemTraits<T>::to_float(qrow[d0 + 2 * hlf + 1]));
+                qa[ks][hlf] = g < G ? *reinterpret_cast<const uint32_t*>(&h2) : 0u;
+                if (g < G) qsum += __low2float(h2) + __high2float(h2);
             }
         }
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
     }
+    const float q_off = kI8Offset * qsum;
 
-    unsigned char* ring = smem + warp * kWarpBytesI8;
-    const uint32_t ring_u32 = smem_u32(ring);
-    unsigned char* wide = ring + kStages * kStageBytesI8;          // widened K tile, then widened V tile
-    const uint32_t wide_u32 = smem_u32(wide);
+    const uint32_t ring_u32 = smem_u32(smem + warp * kWarpBytesI8);
     const int num_tiles = (t1 - t0 + kTileTokens - 1) / kTileTokens;
     const int my_tiles = num_tiles > warp ? (num_tiles - warp + kWarps - 1) / kWarps : 0;
     const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kRowBytesI8;   // bytes between tokens
     const unsigned char* kc = static_cast<const unsigned char*>(p.k_cache) + static_cast<size_t>(kvh) * kRowBytesI8;
     const unsigned char* vc = static_cast<const unsigned char*>(p.v_cache) + static_cast<size_t>(kvh) * kRowBytesI8;
 
-    // Lane's pieces of a tile: 16-byte column c of rows r = 4 * i + (lane >> 3), i = 0..3 (K and V alike).
+    // Copy pattern: 16-byte piece c of rows r = 4 i + (lane >> 3), i = 0..3.  Ring swizzles: K piece c of row r sits at
+    // c ^ ((r & 1) << 2), V piece c of row r at c ^ (r & 6).
     const int c = lane & 7, rq = lane >> 3;
 
     auto issue = [&](int j) {
@@ -380,9 +384,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const De
                 const int r = 4 * i + rq;
                 const int bytes = (phys >= 0 && tok0 + r < t1) ? 16 : 0;
                 const size_t src = base + (bytes ? r * row_stride : 0);
-                const uint32_t dst = stage + r * kRowBytesI8 + c * 16;
-                cp_async16(dst, kc + src, bytes);
-                cp_async16(dst + kTileBytesI8, vc + src, bytes);
+                cp_async16(stage + r * kRowBytesI8 + ((c ^ ((r & 1) << 2)) << 4), kc + src, bytes);
+                cp_async16(stage + kTileBytesI8 + r * kRowBytesI8 + ((c ^ (r & 6)) << 4), vc + src, bytes);
             }
         }
         cp_async_commit();
@@ -391,8 +394,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const De
     auto fetch_scale = [&](int j) -> float {
         if (j >= my_tiles) return 0.0f;
         const int tok = t0 + (warp + j * kWarps) * kTileTokens + (lane & 15);
-        const int blk = tok / p.block_size;
         if (tok >= t1) return 0.0f;
+        const int blk = tok / p.block_size;
         const int phys = s_blocks[blk - blk0];
         if (phys < 0) return 0.0f;
         const size_t row = static_cast<size_t>(phys) * p.block_size + (tok - blk * p.block_size);
@@ -403,58 +406,47 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const De
     float o[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float osum[4] = {0.f, 0.f, 0.f, 0.f};   // sum of the (scaled, rounded) probabilities per head, from the ones-row MMA
     float m_run = -INFINITY, l_run = 0.0f;
 
     issue(0);
     issue(1);
     float sc_cur = fetch_scale(0), sc_next = fetch_scale(1);
 
-    const int k_row = ((lane >> 4) << 3) + (lane & 7);
-    const int k_sel = (lane >> 3) & 1;
-    const int v_row = (((lane >> 3) >> 1) << 3) + (lane & 7);
-    const int v_sel = (lane >> 3) & 1;
+    constexpr uint32_t kGlue = 0x64646464u;   // exponent byte of 1024.0 in f16
+    constexpr uint32_t kOnes = 0x3C003C00u;   // {1.0, 1.0}
 
     for (int j = 0; j < my_tiles; ++j) {
         issue(j + kStages - 1);
         const float sc_after = fetch_scale(j + 2);
         cp_async_wait<kStages - 1>();
-        // widen the pieces this lane copied (its own cp.async groups are complete: no cross-lane wait needed)
-        {
-            const unsigned char* stage = ring + (j % kStages) * kStageBytesI8;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = 4 * i + rq;
-#pragma unroll
-                for (int kv = 0; kv < 2; ++kv) {
-                    const uint4 in = *reinterpret_cast<const uint4*>(stage + kv * kTileBytesI8 + r * kRowBytesI8 + c * 16);
-                    uint4 lo, hi;
-                    widen_i8x16(in, lo, hi);
-                    unsigned char* dst = wide + kv * kTileBytes + r * kRowBytes;
-                    *reinterpret_cast<uint4*>(dst + (((2 * c) ^ (r & 7)) << 4)) = lo;
-                    *reinterpret_cast<uint4*>(dst + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
-                }
-            }
-        }
         __syncwarp();
+        const uint32_t stage = ring_u32 + (j % kStages) * kStageBytesI8;
         const int tok0 = t0 + (warp + j * kWarps) * kTileTokens;
 
+        // ---- scores: keys g (n-tile 0) and g + 8 (n-tile 1)
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            uint32_t b0, b1, b2, b3;
-            const int chunk = 2 * ks + k_sel;
-            ldmatrix_x4(b0, b1, b2, b3, wide_u32 + k_row * kRowBytes + ((chunk ^ (k_row & 7)) << 4));
-            mma_16816<__half>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-            mma_16816<__half>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        for (int q = 0; q < 2; ++q) {
+            uint32_t w0[4], w1[4];
+            lds32x4(stage + g * kRowBytesI8 + (((4 * q + t) ^ ((g & 1) << 2)) << 4), w0);
+            lds32x4(stage + (g + 8) * kRowBytesI8 + (((4 * q + t) ^ ((g & 1) << 2)) << 4), w1);
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const int ks = 4 * q + wi;
+                const uint32_t x0 = w0[wi] ^ 0x80808080u, x1 = w1[wi] ^ 0x80808080u;
+                mma_16816<__half>(s0, qa[ks][0], 0u, qa[ks][1], 0u, __byte_perm(x0, kGlue, 0x4140), __byte_perm(x0, kGlue, 0x4342));
+                mma_16816<__half>(s1, qa[ks][0], 0u, qa[ks][1], 0u, __byte_perm(x1, kGlue, 0x4140), __byte_perm(x1, kGlue, 0x4342));
+            }
         }
-        // scores of head g: tokens tok0 + {2t, 2t+1, 8+2t, 9+2t}; each carries its key's K scale
+        // scores of head g: tokens tok0 + {2t, 2t+1, 8+2t, 9+2t}; remove the offset, apply each key's K scale
         const float ks0 = __shfl_sync(0xffffffffu, sc_cur, 2 * t), ks1 = __shfl_sync(0xffffffffu, sc_cur, 2 * t + 1);
         const float ks2 = __shfl_sync(0xffffffffu, sc_cur, 8 + 2 * t), ks3 = __shfl_sync(0xffffffffu, sc_cur, 9 + 2 * t);
         const float vs0 = __shfl_sync(0xffffffffu, sc_cur, 16 + 2 * t), vs1 = __shfl_sync(0xffffffffu, sc_cur, 17 + 2 * t);
         const float vs2 = __shfl_sync(0xffffffffu, sc_cur, 24 + 2 * t), vs3 = __shfl_sync(0xffffffffu, sc_cur, 25 + 2 * t);
         float sc[4];
-        sc[0] = s0[0] * ks0 * p.scale_log2; sc[1] = s0[1] * ks1 * p.scale_log2;
-        sc[2] = s1[0] * ks2 * p.scale_log2; sc[3] = s1[1] * ks3 * p.scale_log2;
+        sc[0] = (s0[0] - q_off) * ks0 * p.scale_log2; sc[1] = (s0[1] - q_off) * ks1 * p.scale_log2;
+        sc[2] = (s1[0] - q_off) * ks2 * p.scale_log2; sc[3] = (s1[1] - q_off) * ks3 * p.scale_log2;
         const int tk = tok0 + 2 * t;
         if (tk >= t1) sc[0] = -INFINITY;
         if (tk + 1 >= t1) sc[1] = -INFINITY;
@@ -473,15 +465,32 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const De
         const uint32_t pb1 = ElemTraits<__half>::pack2(p2 * vs2, p3 * vs3);
         const float c0 = __shfl_sync(0xffffffffu, corr, 8 * t);
         const float c1 = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+
+        // ---- output: V rows 2t, 2t+1, 2t+8, 2t+9, piece g (d = 16 g .. 16 g + 15)
+        uint32_t v0[4], v1[4], v2[4], v3[4];
+        const uint32_t vbase = stage + kTileBytesI8;
+        lds32x4(vbase + (2 * t) * kRowBytesI8 + ((g ^ ((2 * t) & 6)) << 4), v0);
+        lds32x4(vbase + (2 * t + 1) * kRowBytesI8 + ((g ^ ((2 * t + 1) & 6)) << 4), v1);
+        lds32x4(vbase + (2 * t + 8) * kRowBytesI8 + ((g ^ ((2 * t + 8) & 6)) << 4), v2);
+        lds32x4(vbase + (2 * t + 9) * kRowBytesI8 + ((g ^ ((2 * t + 9) & 6)) << 4), v3);
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            uint32_t a0, a1, a2, a3;
-            const int chunk = 2 * mt + v_sel;
-            ldmatrix_x4_trans(a0, a1, a2, a3, wide_u32 + kTileBytes + v_row * kRowBytes + ((chunk ^ (v_row & 7)) << 4));
-            o[mt][0] *= c0; o[mt][1] *= c1; o[mt][2] *= c0; o[mt][3] *= c1;
-            mma_16816<__half>(o[mt], a0, a1, a2, a3, pb0, pb1);
+        for (int a = 0; a < 4; ++a) {
+            const uint32_t x0 = v0[a] ^ 0x80808080u, x1 = v1[a] ^ 0x80808080u, x2 = v2[a] ^ 0x80808080u, x3 = v3[a] ^ 0x80808080u;
+            // bytes of one d from two consecutive keys, side by side
+            const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
+            const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
+            float (&oe)[4] = o[2 * a];
+            float (&oo)[4] = o[2 * a + 1];
+            oe[0] *= c0; oe[1] *= c1; oe[2] *= c0; oe[3] *= c1;
+            oo[0] *= c0; oo[1] *= c1; oo[2] *= c0; oo[3] *= c1;
+            mma_16816<__half>(oe, __byte_perm(lo01, kGlue, 0x4140), __byte_perm(lo01, kGlue, 0x4342),
+                              __byte_perm(lo23, kGlue, 0x4140), __byte_perm(lo23, kGlue, 0x4342), pb0, pb1);
+            mma_16816<__half>(oo, __byte_perm(hi01, kGlue, 0x4140), __byte_perm(hi01, kGlue, 0x4342),
+                              __byte_perm(hi23, kGlue, 0x4140), __byte_perm(hi23, kGlue, 0x4342), pb0, pb1);
         }
-        __syncwarp();   // the widened tile is rewritten in the next iteration
+        osum[0] *= c0; osum[1] *= c1; osum[2] *= c0; osum[3] *= c1;
+        mma_16816<__half>(osum, kOnes, kOnes, kOnes, kOnes, pb0, pb1);
+        __syncwarp();   // the stage is refilled two iterations from now by other lanes' copies
         sc_cur = sc_next;
         sc_next = sc_after;
     }
@@ -497,9 +506,13 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_int8_kernel(const De
     if (t == 0) { sm_m[warp * kMaxGroup + g] = m_run; sm_l[warp * kMaxGroup + g] = l_run; }
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) {
-        const int d = mt * 16 + g;
+        // accumulator rows g / g + 8 of d-tile mt = 2 a + e hold d = 16 g + 4 a + 2 e (+ 1); columns are heads 2t, 2t + 1
+        const int d = 16 * g + 4 * (mt >> 1) + 2 * (mt & 1);
         float* dst = sm_o + (warp * kMaxGroup + 2 * t) * kHeadDim + d;
-        dst[0] = o[mt][0]; dst[kHeadDim] = o[mt][1]; dst[8] = o[mt][2]; dst[kHeadDim + 8] = o[mt][3];
+        dst[0] = o[mt][0] - kI8Offset * osum[0];
+        dst[kHeadDim] = o[mt][1] - kI8Offset * osum[1];
+        dst[1] = o[mt][2] - kI8Offset * osum[0];
+        dst[kHeadDim + 1] = o[mt][3] - kI8Offset * osum[1];
     }
     __syncthreads();
 
