@@ -289,14 +289,23 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p,
 // ---------------------------------------------------------------------------------------------
 constexpr int kRowBytesI8 = kHeadDim;                      // one head row of int8 K or V
 constexpr int kTileBytesI8 = kTileTokens * kRowBytesI8;    // 2 KiB
-constexpr int kStageBytesI8 = 2 * kTileBytesI8;            // K + V
-constexpr int kWarpBytesI8 = kStages * kStageBytesI8;      // 12 KiB
-constexpr int kSmemBytesI8 = kWarps * kWarpBytesI8;        // 48 KiB -> three blocks per SM
+constexpr int kScaleBytesI8 = 2 * kTileTokens * 4;         // one 32-bit word per (K | V, token): the word that holds its fp16 scale
+constexpr int kStageBytesI8 = 2 * kTileBytesI8 + kScaleBytesI8;   // K + V + scales
+#ifndef NVK_I8_STAGES
+#define NVK_I8_STAGES 4
+#endif
+constexpr int kStagesI8 = NVK_I8_STAGES;                   // tiles in flight per warp: kStagesI8 - 1
+constexpr int kWarpBytesI8 = kStagesI8 * kStageBytesI8;    // 16.5 KiB
+constexpr int kSmemBytesI8 = kWarps * kWarpBytesI8;        // 66 KiB -> three blocks per SM
 constexpr float kI8Offset = 1152.0f;                       // 1024 (exponent glue) + 128 (sign flip)
 
 __device__ __forceinline__ uint32_t lds32x4(uint32_t addr, uint32_t (&w)[4]) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
     return 0;
+}
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 
 struct DecodeInt8Params {
@@ -378,7 +387,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
             const int phys = s_blocks[blk - blk0];
             const int off = tok0 - blk * p.block_size;
             const size_t base = (static_cast<size_t>(phys < 0 ? 0 : phys) * p.block_size + off) * row_stride + c * 16;
-            const uint32_t stage = ring_u32 + (j % kStages) * kStageBytesI8;
+            const uint32_t stage = ring_u32 + (j % kStagesI8) * kStageBytesI8;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int r = 4 * i + rq;
@@ -387,21 +396,19 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
                 cp_async16(stage + r * kRowBytesI8 + ((c ^ ((r & 1) << 2)) << 4), kc + src, bytes);
                 cp_async16(stage + kTileBytesI8 + r * kRowBytesI8 + ((c ^ (r & 6)) << 4), vc + src, bytes);
             }
+            // the scale of token (lane & 15): lanes 0-15 K, lanes 16-31 V; copied as the aligned 32-bit word around it
+            const int tr = lane & 15;
+            const int sbytes = (phys >= 0 && tok0 + tr < t1) ? 4 : 0;
+            const size_t sidx = sbytes ? ((static_cast<size_t>(phys) * p.block_size + off + tr) * p.num_kv_heads + kvh) : 0;
+            const __half* sbase = lane < 16 ? pp.k_scale : pp.v_scale;
+            cp_async4(stage + 2 * kTileBytesI8 + lane * 4, sbase + (sidx & ~static_cast<size_t>(1)), sbytes);
         }
         cp_async_commit();
     };
-    // Scale of this lane's token of tile j: lanes 0-15 K, lanes 16-31 V (0 outside the chunk or the cache).
-    auto fetch_scale = [&](int j) -> float {
-        if (j >= my_tiles) return 0.0f;
-        const int tok = t0 + (warp + j * kWarps) * kTileTokens + (lane & 15);
-        if (tok >= t1) return 0.0f;
-        const int blk = tok / p.block_size;
-        const int phys = s_blocks[blk - blk0];
-        if (phys < 0) return 0.0f;
-        const size_t row = static_cast<size_t>(phys) * p.block_size + (tok - blk * p.block_size);
-        const __half* src = (lane < 16 ? pp.k_scale : pp.v_scale) + row * p.num_kv_heads + kvh;
-        return __half2float(*src);
-    };
+    // which half of the copied word is this lane's scale: cache rows of a tile start at an even row, so the parity of
+    // row * Hkv + kvh is that of (token & Hkv & 1) + kvh
+    const bool scale_hi = (((lane & p.num_kv_heads) ^ kvh) & 1) != 0;
+    const float scale_mul = lane < 16 ? p.scale_log2 : 1.0f;   // the softmax scale rides on the K scale
 
     float o[8][4];
 #pragma unroll
@@ -409,20 +416,25 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
     float osum[4] = {0.f, 0.f, 0.f, 0.f};   // sum of the (scaled, rounded) probabilities per head, from the ones-row MMA
     float m_run = -INFINITY, l_run = 0.0f;
 
-    issue(0);
-    issue(1);
-    float sc_cur = fetch_scale(0), sc_next = fetch_scale(1);
+#pragma unroll
+    for (int s = 0; s < kStagesI8 - 1; ++s) issue(s);
 
     constexpr uint32_t kGlue = 0x64646464u;   // exponent byte of 1024.0 in f16
     constexpr uint32_t kOnes = 0x3C003C00u;   // {1.0, 1.0}
 
     for (int j = 0; j < my_tiles; ++j) {
-        issue(j + kStages - 1);
-        const float sc_after = fetch_scale(j + 2);
-        cp_async_wait<kStages - 1>();
+        issue(j + kStagesI8 - 1);
+        cp_async_wait<kStagesI8 - 1>();
         __syncwarp();
-        const uint32_t stage = ring_u32 + (j % kStages) * kStageBytesI8;
+        const uint32_t stage = ring_u32 + (j % kStagesI8) * kStageBytesI8;
         const int tok0 = t0 + (warp + j * kWarps) * kTileTokens;
+        float sc_cur;
+        {
+            uint32_t word;
+            asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(word) : "r"(stage + 2 * kTileBytesI8 + lane * 4));
+            const __half2 pair = *reinterpret_cast<const __half2*>(&word);
+            sc_cur = (scale_hi ? __high2float(pair) : __low2float(pair)) * scale_mul;
+        }
 
         // ---- scores: keys g (n-tile 0) and g + 8 (n-tile 1)
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -445,26 +457,36 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
         const float vs0 = __shfl_sync(0xffffffffu, sc_cur, 16 + 2 * t), vs1 = __shfl_sync(0xffffffffu, sc_cur, 17 + 2 * t);
         const float vs2 = __shfl_sync(0xffffffffu, sc_cur, 24 + 2 * t), vs3 = __shfl_sync(0xffffffffu, sc_cur, 25 + 2 * t);
         float sc[4];
-        sc[0] = (s0[0] - q_off) * ks0 * p.scale_log2; sc[1] = (s0[1] - q_off) * ks1 * p.scale_log2;
-        sc[2] = (s1[0] - q_off) * ks2 * p.scale_log2; sc[3] = (s1[1] - q_off) * ks3 * p.scale_log2;
-        const int tk = tok0 + 2 * t;
-        if (tk >= t1) sc[0] = -INFINITY;
-        if (tk + 1 >= t1) sc[1] = -INFINITY;
-        if (tk + 8 >= t1) sc[2] = -INFINITY;
-        if (tk + 9 >= t1) sc[3] = -INFINITY;
+        sc[0] = (s0[0] - q_off) * ks0; sc[1] = (s0[1] - q_off) * ks1;
+        sc[2] = (s1[0] - q_off) * ks2; sc[3] = (s1[1] - q_off) * ks3;
+        if (tok0 + kTileTokens > t1) {   // only a chunk's last tile can reach past its end (warp-uniform)
+            const int tk = tok0 + 2 * t;
+            if (tk >= t1) sc[0] = -INFINITY;
+            if (tk + 1 >= t1) sc[1] = -INFINITY;
+            if (tk + 8 >= t1) sc[2] = -INFINITY;
+            if (tk + 9 >= t1) sc[3] = -INFINITY;
+        }
         float m_tile = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
         m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
         m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
-        const float m_new = fmaxf(m_run, m_tile);   // finite: token tok0 is always valid
-        const float corr = fast_exp2(m_run - m_new);
-        const float p0 = fast_exp2(sc[0] - m_new), p1 = fast_exp2(sc[1] - m_new);
-        const float p2 = fast_exp2(sc[2] - m_new), p3 = fast_exp2(sc[3] - m_new);
-        l_run = l_run * corr + ((p0 + p1) + (p2 + p3));
-        m_run = m_new;
+        // The running maximum of a head moves on a handful of tiles only; the 36 accumulator multiplies are skipped
+        // on all the others (warp-uniform branch).
+        if (__any_sync(0xffffffffu, m_tile > m_run)) {
+            const float m_new = fmaxf(m_run, m_tile);   // finite: token tok0 is always valid
+            const float corr = fast_exp2(m_run - m_new);
+            l_run *= corr;
+            m_run = m_new;
+            const float c0 = __shfl_sync(0xffffffffu, corr, 8 * t);
+            const float c1 = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) { o[mt][0] *= c0; o[mt][1] *= c1; o[mt][2] *= c0; o[mt][3] *= c1; }
+            osum[0] *= c0; osum[1] *= c1; osum[2] *= c0; osum[3] *= c1;
+        }
+        const float p0 = fast_exp2(sc[0] - m_run), p1 = fast_exp2(sc[1] - m_run);
+        const float p2 = fast_exp2(sc[2] - m_run), p3 = fast_exp2(sc[3] - m_run);
+        l_run += (p0 + p1) + (p2 + p3);
         const uint32_t pb0 = ElemTraits<__half>::pack2(p0 * vs0, p1 * vs1);
         const uint32_t pb1 = ElemTraits<__half>::pack2(p2 * vs2, p3 * vs3);
-        const float c0 = __shfl_sync(0xffffffffu, corr, 8 * t);
-        const float c1 = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
 
         // ---- output: V rows 2t, 2t+1, 2t+8, 2t+9, piece g (d = 16 g .. 16 g + 15)
         uint32_t v0[4], v1[4], v2[4], v3[4];
@@ -481,18 +503,13 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
             const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
             float (&oe)[4] = o[2 * a];
             float (&oo)[4] = o[2 * a + 1];
-            oe[0] *= c0; oe[1] *= c1; oe[2] *= c0; oe[3] *= c1;
-            oo[0] *= c0; oo[1] *= c1; oo[2] *= c0; oo[3] *= c1;
             mma_16816<__half>(oe, __byte_perm(lo01, kGlue, 0x4140), __byte_perm(lo01, kGlue, 0x4342),
                               __byte_perm(lo23, kGlue, 0x4140), __byte_perm(lo23, kGlue, 0x4342), pb0, pb1);
             mma_16816<__half>(oo, __byte_perm(hi01, kGlue, 0x4140), __byte_perm(hi01, kGlue, 0x4342),
                               __byte_perm(hi23, kGlue, 0x4140), __byte_perm(hi23, kGlue, 0x4342), pb0, pb1);
         }
-        osum[0] *= c0; osum[1] *= c1; osum[2] *= c0; osum[3] *= c1;
         mma_16816<__half>(osum, kOnes, kOnes, kOnes, kOnes, pb0, pb1);
         __syncwarp();   // the stage is refilled two iterations from now by other lanes' copies
-        sc_cur = sc_next;
-        sc_next = sc_after;
     }
     cp_async_wait<0>();
     __syncthreads();  // every ring is idle from here on: reuse the shared memory for the cross-warp merge
@@ -680,7 +697,8 @@ bool decode_int8_mma_supported(const DecodeInt8Args& x) {
     if (a.num_heads / a.num_kv_heads > kMaxGroup) return false;
     if (a.block_size < kTileTokens || a.block_size % kTileTokens != 0) return false;
     if (!aligned_to(a.q, 2) || !aligned_to(a.k_cache, 16) || !aligned_to(a.v_cache, 16) || !aligned_to(a.out, 8)) return false;
-    if (!aligned_to(x.k_scale, 2) || !aligned_to(x.v_scale, 2)) return false;
+    if (!aligned_to(x.k_scale, 4) || !aligned_to(x.v_scale, 4)) return false;   // scales are copied as aligned 32-bit words
+    if ((a.num_cache_blocks * a.block_size * a.num_kv_heads) % 2 != 0) return false;
     if (a.workspace == nullptr && a.max_blocks > kMaxChunkBlocks) return false;
     return true;
 }
