@@ -18,7 +18,7 @@ RING = 64   # pinned metadata slots in flight
 
 
 def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None, num_seqs=256, len_lo=100, len_hi=1024,
-            seed=0, use_graph=True):
+            seed=0, use_graph=True, kv_dtype="bf16"):
     cfg = cfg or DecoderConfig()
     bs = cfg.block_size
     prompts, output_lens = make_requests(num_seqs, cfg.vocab, len_lo, len_hi, seed)
@@ -26,7 +26,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
     table_width = (2 * len_hi + bs - 1) // bs
     num_blocks = blocks_needed(prompt_lens, output_lens, bs) + 8
     t0 = time.time()
-    model = Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=num_blocks, seed=seed)
+    model = Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=num_blocks, seed=seed, kv_dtype=kv_dtype)
     torch.cuda.synchronize()
     build_s = time.time() - t0
     model.ensure_workspace(num_seqs, table_width)
@@ -89,7 +89,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
     total_ms, prefill_ms, decode_ms = ev[0].elapsed_time(ev[2]), ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
     eager_launches = nvk.launch_count - launches0
     # kernels of this library per step: prologue + prefill attention per layer in prefill; prologue + split + merge in decode
-    our_launches = len(batches) * cfg.layers * 2 + steps * cfg.layers * 3
+    our_launches = (len(batches) * cfg.layers * 2 + steps * cfg.layers * 3) + (len(batches) + steps) * cfg.layers * (1 if model.int8 else 0)
 
     # ---- attention share of a decode step, on the metadata of a step a quarter into the run ----------------------------
     attn_ms = None
@@ -102,12 +102,20 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
         q = torch.empty((num_seqs, model.hq, cfg.head_dim), device=dev, dtype=torch.bfloat16)
         out = torch.empty_like(q)
 
+        attend = model.attend_decode(ctx, tables)
+        k_step = torch.empty((num_seqs, model.hkv, cfg.head_dim), device=dev, dtype=torch.bfloat16)
+        v_step = torch.empty_like(k_step)
+        rows = torch.arange(num_seqs, device=dev, dtype=torch.int32)
+
         def attention_only():
             for l, w in enumerate(model.layers):
-                nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, model.cos_sin, slots,
-                                                model.kv_cache[0, l], model.kv_cache[1, l], model.hq, model.hkv, cfg.head_dim, q)
-                nvk.launch_decode_attention_paged(q, model.kv_cache[0, l], model.kv_cache[1, l], ctx, tables, model.hkv,
-                                                  cfg.head_dim, bs, model.scale, out, model.workspace)
+                if model.int8:   # prologue into the dense scratch; the quantising store is skipped (all slots are -1)
+                    nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, model.cos_sin, rows,
+                                                    k_step, v_step, model.hq, model.hkv, cfg.head_dim, q)
+                else:
+                    nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, model.cos_sin, slots,
+                                                    model.kv_cache[0, l], model.kv_cache[1, l], model.hq, model.hkv, cfg.head_dim, q)
+                attend(l, q, k_step, v_step, out)
 
         for _ in range(3):
             attention_only()
@@ -132,6 +140,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
                                f"head_dim {cfg.head_dim}, FFN {cfg.ffn}, vocab {cfg.vocab}, random-init bf16 weights; {num_seqs} sequences, "
                                f"prompt and output lengths U[{len_lo},{len_hi}], greedy, ignore_eos",
                    "parallelism": f"tp{world} (KV-head shards, NCCL all-reduce after o_proj / down_proj)",
+                   "kv_cache": "int8 with fp16 per-(token, head) scales" if model.int8 else "bf16",
                    "decode": "one captured CUDA graph of %d fixed rows" % num_seqs if graph is not None else "eager",
                    "prefill_batches": len(batches), "decode_steps": steps, "kv_blocks": num_blocks,
                    "l2": "weights (16.4 GB / tp) and KV cache exceed the 126 MB L2"},

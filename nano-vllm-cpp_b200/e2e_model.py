@@ -45,7 +45,7 @@ def rope_table(torch, dev, max_positions, head_dim, theta):
 class Decoder:
     """One tensor-parallel rank of the decoder."""
 
-    def __init__(self, nvk, torch, dev, cfg: DecoderConfig, rank=0, world=1, dist=None, num_blocks=0, seed=0):
+    def __init__(self, nvk, torch, dev, cfg: DecoderConfig, rank=0, world=1, dist=None, num_blocks=0, seed=0, kv_dtype="bf16"):
         if cfg.num_kv_heads % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, ffn and vocab must divide by the tensor-parallel size")
         self.nvk, self.torch, self.dev, self.cfg = nvk, torch, dev, cfg
@@ -87,7 +87,14 @@ class Decoder:
         self.scale = 1.0 / math.sqrt(d)
         # [2, layers, blocks, block_size, Hkv/t, D] as in allocate_kv_cache (src/engine/model_runner.cpp:355-472)
         self.num_blocks = int(num_blocks)
-        self.kv_cache = torch.zeros((2, cfg.layers, self.num_blocks, cfg.block_size, self.hkv, d), device=dev, dtype=bf)
+        if kv_dtype not in ("bf16", "int8"):
+            raise ValueError("kv_dtype must be bf16 or int8")
+        self.int8 = kv_dtype == "int8"
+        self.kv_cache = torch.zeros((2, cfg.layers, self.num_blocks, cfg.block_size, self.hkv, d), device=dev,
+                                    dtype=torch.int8 if self.int8 else bf)
+        # int8 cache: one fp16 scale per (cache row, KV head), the reference's format (include/kernels/kvcache.h:14-24)
+        self.kv_scale = (torch.zeros((2, cfg.layers, self.num_blocks, cfg.block_size, self.hkv), device=dev, dtype=torch.float16)
+                         if self.int8 else None)
         self.workspace = None
 
     # ---- pieces ---------------------------------------------------------------------------------------------
@@ -106,24 +113,62 @@ class Decoder:
             self.workspace = self.torch.empty(max(need, 1), device=self.dev, dtype=self.torch.uint8)
 
     def forward(self, tokens, positions, slot_mapping, attend):
-        """Hidden states after the last layer.  ``attend(layer_index, q, out)`` runs attention for one layer."""
+        """Hidden states after the last layer.  ``attend(layer_index, q, k, v, out)`` runs attention for one layer
+        (``k`` / ``v`` are the step's normalised and rotated keys / values when the cache is int8, else None)."""
         torch, nvk, cfg = self.torch, self.nvk, self.cfg
         h = self.embed[tokens]
         n = h.shape[0]
         q = torch.empty((n, self.hq, cfg.head_dim), device=self.dev, dtype=h.dtype)
         attn = torch.empty_like(q)
+        k_step = v_step = rows = None
+        if self.int8:
+            # As in the reference, an int8 cache takes the unfused route (src/models/transformer.cpp:126-129): the prologue
+            # writes the step's K / V into a dense scratch (slot = row), the quantising store then files them in the cache.
+            k_step = torch.empty((n, self.hkv, cfg.head_dim), device=self.dev, dtype=h.dtype)
+            v_step = torch.empty_like(k_step)
+            rows = torch.arange(n, device=self.dev, dtype=torch.int32)
         for l, w in enumerate(self.layers):
             x = self.rmsnorm(h, w["norm_in"])
             qkv = x @ w["w_qkv"].t()
-            nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, slot_mapping,
-                                            self.kv_cache[0, l], self.kv_cache[1, l], self.hq, self.hkv, cfg.head_dim, q)
-            attend(l, q, attn)
+            if self.int8:
+                nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, rows,
+                                                k_step, v_step, self.hq, self.hkv, cfg.head_dim, q)
+                nvk.store_kvcache_int8(k_step, v_step, self.kv_cache[0, l], self.kv_cache[1, l], self.kv_scale[0, l],
+                                       self.kv_scale[1, l], slot_mapping)
+            else:
+                nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, slot_mapping,
+                                                self.kv_cache[0, l], self.kv_cache[1, l], self.hq, self.hkv, cfg.head_dim, q)
+            attend(l, q, k_step, v_step, attn)
             h = h + self.all_reduce(attn.view(n, -1) @ w["w_o"].t())
             x = self.rmsnorm(h, w["norm_post"])
             gu = x @ w["w_gate_up"].t()
             act = torch.nn.functional.silu(gu[:, :self.ffn]) * gu[:, self.ffn:]
             h = h + self.all_reduce(act @ w["w_down"].t())
         return h
+
+    def attend_prefill(self, cu_q, cu_k, tables):
+        nvk, cfg = self.nvk, self.cfg
+
+        def attend(l, q, k, v, out):
+            if self.int8:   # no prefix hits in this benchmark: the dense keys / values of the step are the whole context
+                nvk.launch_prefill_attention_dense(q, cu_q, k, v, cu_k, self.hkv, cfg.head_dim, self.scale, out)
+            else:
+                nvk.launch_prefill_attention_paged(q, cu_q, self.kv_cache[0, l], self.kv_cache[1, l], cu_k, tables, self.hkv,
+                                                   cfg.head_dim, cfg.block_size, self.scale, out)
+        return attend
+
+    def attend_decode(self, ctx, tables):
+        nvk, cfg = self.nvk, self.cfg
+
+        def attend(l, q, k, v, out):
+            if self.int8:
+                nvk.launch_decode_attention_paged_int8(q, self.kv_cache[0, l], self.kv_cache[1, l], self.kv_scale[0, l],
+                                                       self.kv_scale[1, l], ctx, tables, self.hkv, cfg.head_dim, cfg.block_size,
+                                                       self.scale, out, self.workspace)
+            else:
+                nvk.launch_decode_attention_paged(q, self.kv_cache[0, l], self.kv_cache[1, l], ctx, tables, self.hkv,
+                                                  cfg.head_dim, cfg.block_size, self.scale, out, self.workspace)
+        return attend
 
     def sample(self, h_rows):
         """Greedy sampling over the vocabulary shards: local max and arg-max, then one gather."""
@@ -146,11 +191,7 @@ class Decoder:
         tokens, positions, slots = up(arrays["tokens"]), up(arrays["positions"]), up(arrays["slot_mapping"])
         cu_q, cu_k, tables = up(arrays["cu_seqlens_q"]), up(arrays["cu_seqlens_k"]), up(arrays["block_tables"])
 
-        def attend(l, q, out):
-            nvk.launch_prefill_attention_paged(q, cu_q, self.kv_cache[0, l], self.kv_cache[1, l], cu_k, tables, self.hkv,
-                                               cfg.head_dim, cfg.block_size, self.scale, out)
-
-        h = self.forward(tokens, positions, slots, attend)
+        h = self.forward(tokens, positions, slots, self.attend_prefill(cu_q, cu_k, tables))
         return self.sample(h[up(arrays["last_rows"])])
 
     def decode_forward(self, tokens, meta):
@@ -159,8 +200,4 @@ class Decoder:
         positions, slots, ctx = meta[:, 0].contiguous(), meta[:, 1].contiguous(), meta[:, 2].contiguous()
         tables = meta[:, 3:].contiguous()
 
-        def attend(l, q, out):
-            nvk.launch_decode_attention_paged(q, self.kv_cache[0, l], self.kv_cache[1, l], ctx, tables, self.hkv,
-                                              cfg.head_dim, cfg.block_size, self.scale, out, self.workspace)
-
-        return self.sample(self.forward(tokens, positions, slots, attend))
+        return self.sample(self.forward(tokens, positions, slots, self.attend_decode(ctx, tables)))

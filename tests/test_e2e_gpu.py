@@ -26,7 +26,8 @@ def tiny(em, layers=2):
                             max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=2048)
 
 
-def test_decode_continues_a_sequence_like_a_longer_prefill(mods):
+@pytest.mark.parametrize("kv_dtype,tol", [("bf16", 0.03), ("int8", 0.06)])
+def test_decode_continues_a_sequence_like_a_longer_prefill(mods, kv_dtype, tol):
     torch, nvk, em, es, _ = mods
     dev = torch.device("cuda:0")
     cfg = tiny(em)
@@ -34,7 +35,7 @@ def test_decode_continues_a_sequence_like_a_longer_prefill(mods):
     lens = [37, 300, 256]                       # inside a block, across a block boundary, exactly at one
     extra = 3                                   # tokens continued by decode steps
     full = [rng.integers(0, cfg.vocab, size=n + extra) for n in lens]
-    model = em.Decoder(nvk, torch, dev, cfg, num_blocks=16, seed=1)
+    model = em.Decoder(nvk, torch, dev, cfg, num_blocks=16, seed=1, kv_dtype=kv_dtype)
     model.ensure_workspace(len(lens), 4)
 
     hidden = {}
@@ -45,9 +46,7 @@ def test_decode_continues_a_sequence_like_a_longer_prefill(mods):
         up = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(dev)  # noqa: E731
         cu, tables = up(a["cu_seqlens_q"]), up(a["block_tables"])
 
-        def attend(l, q, out):
-            nvk.launch_prefill_attention_paged(q, cu, m.kv_cache[0, l], m.kv_cache[1, l], cu, tables, m.hkv, cfg.head_dim,
-                                               cfg.block_size, m.scale, out)
+        attend = m.attend_prefill(cu, cu, tables)
         hidden[key] = m.forward(up(a["tokens"]), up(a["positions"]), up(a["slot_mapping"]), attend).float().cpu().numpy()
         return s, a
 
@@ -65,21 +64,19 @@ def test_decode_continues_a_sequence_like_a_longer_prefill(mods):
         tokens = torch.tensor([int(f[n + step]) for f, n in zip(full, lens)], device=dev)
         positions, slots, ctx, tables = (m[:, 0].contiguous(), m[:, 1].contiguous(), m[:, 2].contiguous(), m[:, 3:].contiguous())
 
-        def attend(l, q, out):
-            nvk.launch_decode_attention_paged(q, model.kv_cache[0, l], model.kv_cache[1, l], ctx, tables, model.hkv,
-                                              cfg.head_dim, cfg.block_size, model.scale, out, model.workspace)
+        attend = model.attend_decode(ctx, tables)
         h = model.forward(tokens, positions, slots, attend).float().cpu().numpy()
         for i, n in enumerate(lens):
             want = hidden["full"][cu_full[i] + n + step]
             err = np.abs(h[i] - want).max()
-            assert err <= 0.03 * max(1.0, np.abs(want).max()), (i, step, err, np.abs(want).max())
+            assert err <= tol * max(1.0, np.abs(want).max()), (i, step, err, np.abs(want).max())
 
 
-@pytest.mark.parametrize("use_graph", [True, False])
-def test_benchmark_loop_runs(mods, use_graph):
+@pytest.mark.parametrize("use_graph,kv_dtype", [(True, "bf16"), (False, "bf16"), (True, "int8")])
+def test_benchmark_loop_runs(mods, use_graph, kv_dtype):
     torch, nvk, em, _, eb = mods
     line = eb.run_e2e(nvk, torch, None, 0, 1, torch.device("cuda:0"), tiny(em, layers=2), num_seqs=6, len_lo=5, len_hi=300,
-                      seed=2, use_graph=use_graph)
+                      seed=2, use_graph=use_graph, kv_dtype=kv_dtype)
     assert line["output_tokens"] > 0 and line["value"] > 0
     assert line["config"]["decode_steps"] == line["steps"] - line["config"]["prefill_batches"]
     assert line["gpu_launches"] > 0
