@@ -6,9 +6,9 @@
 //
 // Format (the reference's): K and V as int8 [cache_rows, Hkv, D]; one fp16 scale per (cache row, KV head) in
 // k_scale / v_scale [cache_rows, Hkv]; scale = max(absmax / 127, 1e-10), q = clamp(rint(x * 127 / max(absmax, 1e-10)), +-127).
-// The store is HBM-bound (reads 2 * tokens * Hkv * D elements, writes half as many bytes plus the scales): one warp
-// per (token, KV head), every lane holds D / 32 contiguous elements of K and of V (one 4/8/16-byte load each), the
-// absolute maximum is a shuffle reduction, the quantised bytes leave as one packed store per lane.  The arithmetic is
+// The store is HBM-bound (reads 2 * tokens * Hkv * D elements, writes half as many bytes plus the scales): a head
+// vector is spread over head_dim / 8 lanes (16-byte loads of K and of V per lane, two vectors per warp at head_dim 128), the
+// absolute maximum is a shuffle reduction inside that lane group, the quantised bytes leave as one packed store per lane.  The arithmetic is
 // the reference's operation for operation (IEEE division, round-to-nearest-even conversion), so caches and scales are
 // bit-identical to the reference's.
 #include "nvk_internal.cuh"
@@ -38,45 +38,50 @@ __device__ __forceinline__ void load_elems(const T* src, float (&x)[V]) {
     }
 }
 
-template <int V>
-__device__ __forceinline__ void quantise_and_store(const float (&x)[V], int8_t* dst, __half* scale_dst, int lane) {
-    float absmax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < V; ++i) absmax = fmaxf(absmax, fabsf(x[i]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, o));
-    const float sc = fmaxf(__fdiv_rn(absmax, 127.0f), 1e-10f);
-    const float inv_sc = __fdiv_rn(127.0f, fmaxf(absmax, 1e-10f));
-    union { typename PackOf<V>::out v; int8_t e[V]; } q;
-#pragma unroll
-    for (int i = 0; i < V; ++i) {
-        int v = __float2int_rn(__fmul_rn(x[i], inv_sc));
-        v = max(-127, min(127, v));
-        q.e[i] = static_cast<int8_t>(v);
-    }
-    *reinterpret_cast<typename PackOf<V>::out*>(dst + lane * V) = q.v;
-    if (lane == 0) *scale_dst = __float2half(sc);
-}
-
-template <typename T, int V>
+// One warp quantises 32 / LANES (token, KV head) vectors at a time: 16-bit inputs are read as 16-byte pieces (V = 8,
+// LANES = head_dim / 8), fp32 inputs as V = 4.
+template <typename T, int V, int LANES>
 __global__ void __launch_bounds__(kStoreWarps * 32)
 store_int8_kernel(const T* __restrict__ key, const T* __restrict__ value, int8_t* __restrict__ k_cache,
                   int8_t* __restrict__ v_cache, __half* __restrict__ k_scale, __half* __restrict__ v_scale,
                   const int32_t* __restrict__ slot_mapping, int64_t num_tokens, int num_kv_heads, int64_t cache_rows) {
-    constexpr int D = V * 32;
+    constexpr int D = V * LANES;
+    constexpr int kPerWarp = 32 / LANES;
     const int lane = threadIdx.x & 31;
-    const int64_t work = static_cast<int64_t>(blockIdx.x) * kStoreWarps + (threadIdx.x >> 5);   // (token, head)
-    if (work >= num_tokens * num_kv_heads) return;
+    const int sub = lane % LANES;
+    const int64_t total = num_tokens * num_kv_heads;
+    int64_t work = (static_cast<int64_t>(blockIdx.x) * kStoreWarps + (threadIdx.x >> 5)) * kPerWarp + lane / LANES;   // (token, head)
+    // lanes past the end repeat the last vector (same values, same destination) so that the shuffles stay full-warp
+    if (work >= total) work = total - 1;
     const int64_t token = work / num_kv_heads;
     const int head = static_cast<int>(work % num_kv_heads);
     const int64_t slot = slot_mapping[token];
-    if (slot < 0 || slot >= cache_rows) return;
+    const bool live = slot >= 0 && slot < cache_rows;
     float kx[V], vx[V];
-    load_elems<T, V>(key + work * D + lane * V, kx);
-    load_elems<T, V>(value + work * D + lane * V, vx);
-    const int64_t dst_row = slot * num_kv_heads + head;
-    quantise_and_store<V>(kx, k_cache + dst_row * D, k_scale + dst_row, lane);
-    quantise_and_store<V>(vx, v_cache + dst_row * D, v_scale + dst_row, lane);
+    load_elems<T, V>(key + work * D + sub * V, kx);
+    load_elems<T, V>(value + work * D + sub * V, vx);
+    const int64_t dst_row = (live ? slot : 0) * num_kv_heads + head;
+    // the reductions run for every lane; only live vectors are written
+    float kmax = 0.0f, vmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) { kmax = fmaxf(kmax, fabsf(kx[i])); vmax = fmaxf(vmax, fabsf(vx[i])); }
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) {
+        kmax = fmaxf(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    }
+    if (!live) return;
+    const float k_sc = fmaxf(__fdiv_rn(kmax, 127.0f), 1e-10f), k_inv = __fdiv_rn(127.0f, fmaxf(kmax, 1e-10f));
+    const float v_sc = fmaxf(__fdiv_rn(vmax, 127.0f), 1e-10f), v_inv = __fdiv_rn(127.0f, fmaxf(vmax, 1e-10f));
+    union { typename PackOf<V>::out v; int8_t e[V]; } kq, vq;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        kq.e[i] = static_cast<int8_t>(max(-127, min(127, __float2int_rn(__fmul_rn(kx[i], k_inv)))));
+        vq.e[i] = static_cast<int8_t>(max(-127, min(127, __float2int_rn(__fmul_rn(vx[i], v_inv)))));
+    }
+    *reinterpret_cast<typename PackOf<V>::out*>(k_cache + dst_row * D + sub * V) = kq.v;
+    *reinterpret_cast<typename PackOf<V>::out*>(v_cache + dst_row * D + sub * V) = vq.v;
+    if (sub == 0) { k_scale[dst_row] = __float2half(k_sc); v_scale[dst_row] = __float2half(v_sc); }
 }
 
 // General decode path: one warp per (sequence, query head), lane owns D / 32 contiguous elements; serial online
@@ -134,19 +139,23 @@ template <typename T>
 int launch_store_typed(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
                        const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,
                        cudaStream_t stream) {
+    constexpr int V = sizeof(T) == 2 ? 8 : 4;   // 16 bytes per lane
+    const int lanes = head_dim / V;
+    if (head_dim % V != 0 || (lanes != 8 && lanes != 16 && lanes != 32))
+        return fail(NVK_ERR_UNSUPPORTED, "store_kvcache_int8: head_dim must be 64, 128 or 256 (fp32: 32, 64 or 128); got %d", head_dim);
     const int64_t work = num_tokens * num_kv_heads;
-    const int64_t blocks = (work + kStoreWarps - 1) / kStoreWarps;
+    const int64_t per_block = static_cast<int64_t>(kStoreWarps) * (32 / lanes);
+    const int64_t blocks = (work + per_block - 1) / per_block;
     if (blocks > 0x7fffffffLL) return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: too many tokens");
-#define NVK_LAUNCH(V)                                                                                              \
-    store_int8_kernel<T, V><<<static_cast<unsigned>(blocks), kStoreWarps * 32, 0, stream>>>(                        \
+#define NVK_LAUNCH(L)                                                                                               \
+    store_int8_kernel<T, V, L><<<static_cast<unsigned>(blocks), kStoreWarps * 32, 0, stream>>>(                      \
         static_cast<const T*>(key), static_cast<const T*>(value), static_cast<int8_t*>(k_cache),                   \
         static_cast<int8_t*>(v_cache), static_cast<__half*>(k_scale), static_cast<__half*>(v_scale), slot_mapping, \
         num_tokens, num_kv_heads, cache_rows)
-    switch (head_dim) {
-        case 64: NVK_LAUNCH(2); break;
-        case 128: NVK_LAUNCH(4); break;
-        case 256: NVK_LAUNCH(8); break;
-        default: return fail(NVK_ERR_UNSUPPORTED, "store_kvcache_int8: head_dim must be 64, 128 or 256 (got %d)", head_dim);
+    switch (lanes) {
+        case 8: NVK_LAUNCH(8); break;
+        case 16: NVK_LAUNCH(16); break;
+        default: NVK_LAUNCH(32); break;
     }
 #undef NVK_LAUNCH
     return check_launch("store_kvcache_int8 kernel launch");

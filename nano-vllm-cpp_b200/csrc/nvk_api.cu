@@ -124,8 +124,7 @@ int nvk_store_kvcache_int8(const void* key, const void* value, void* k_cache, vo
     if (num_kv_heads <= 0 || head_dim <= 0 || cache_rows <= 0)
         return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: dimensions must be positive");
     if (num_tokens <= 0) return NVK_OK;   // the reference returns without a launch (kvcache.cu:327)
-    const size_t in_align = static_cast<size_t>(head_dim / 32) * (dtype == NVK_F32 ? 4 : 2);
-    if (!aligned_to(key, in_align > 16 ? 16 : in_align) || !aligned_to(value, in_align > 16 ? 16 : in_align) ||
+    if (!aligned_to(key, dtype == NVK_F32 ? 4 : 16) || !aligned_to(value, dtype == NVK_F32 ? 4 : 16) ||
         !aligned_to(k_cache, 8) || !aligned_to(v_cache, 8) || !aligned_to(k_scale, 2) || !aligned_to(v_scale, 2))
         return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: misaligned tensor");
     return launch_store_int8(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads,
