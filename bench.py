@@ -405,6 +405,7 @@ def main():
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
                     help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")
     ap.add_argument("--layers", type=int, default=36, help="mixed workload: layer caches per step")
+    ap.add_argument("--rows", type=int, default=256, help="prologue workload: token rows")
     ap.add_argument("--seqs", type=int, default=16, help="prefill workload: number of sequences")
     ap.add_argument("--qmax", type=int, default=4096, help="prefill workload: longest new-token run")
     ap.add_argument("--batch", type=int, default=CFG["batch"],
@@ -495,7 +496,7 @@ def main():
         elif args.workload == "mixed":
             line = kb.bench_mixed(nvk, torch, dev, min(steps, 10), min(args.warmup, 3), layers=args.layers)
         else:
-            line = kb.bench_prologue(nvk, torch, dev, steps, args.warmup)
+            line = kb.bench_prologue(nvk, torch, dev, steps, args.warmup, rows=args.rows)
         print(json.dumps(line), flush=True)
         return 0
 

@@ -206,3 +206,22 @@ def test_prefill_in_two_chunks_equals_single_shot(prefill_full):
                                          HKV, D, BS, w["scale"], out2)
     torch.cuda.synchronize()
     _close(out2, w["out"][idx])
+
+
+def test_prefill_launches_on_two_streams_do_not_disturb_each_other(prefill_full):
+    """The persistent prefill kernel takes its work items from per-launch ticket counters; launches that overlap on the
+    GPU (two streams) must each see a private counter.  Forty interleaved launches, every output compared."""
+    import torch
+    w = prefill_full
+    lib = nvk()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = [torch.empty_like(w["out"]) for _ in range(4)]
+    torch.cuda.synchronize()
+    for rep in range(10):
+        for k, stream in enumerate((s1, s2, s1, s2)):
+            with torch.cuda.stream(stream):
+                lib.launch_prefill_attention_paged(w["q"], w["cu_q"], w["k_cache"], w["v_cache"], w["cu_k"], w["block_tables"], HKV, D, BS,
+                                                   w["scale"], outs[k])
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o, w["out"])
