@@ -166,6 +166,11 @@ int nvk_decode_attention_paged_static(const void* query, const void* k_cache, co
  * Causal mask, bottom-right aligned: query i of a sequence sees keys
  * 0 .. (k_len - q_len) + i  (attention.cu:147, :244); rows with no visible key are zero.
  * max_seqlen_q may be 0 when unknown.
+ * The tensor-core path (F16 / BF16, head_dim 128, an even number of query heads per KV head) runs persistent
+ * blocks that take their work from a counter inside the library; 64 such counters rotate, one per call, and the
+ * last block of a launch re-arms its counter.  So up to 64 prefill launches may be in flight on one device at a
+ * time (any streams); a CUDA graph that captured the call keeps the counter it was given, and graphs replayed
+ * concurrently on one device must hold different ones (capture them back to back and they do).
  */
 int nvk_prefill_attention_varlen(const void* query, const void* key, const void* value,
                                  const void* k_cache, const void* v_cache,
