@@ -454,6 +454,8 @@ def main():
     ap.add_argument("--e2e-maxlen", type=int, default=1024, help="e2e workload: longest prompt / output")
     ap.add_argument("--no-graph", action="store_true", help="e2e workload: run decode steps eagerly")
     ap.add_argument("--e2e-kv", default="bf16", choices=["bf16", "int8"], help="e2e workload: KV cache format")
+    ap.add_argument("--e2e-allreduce", default="nccl", choices=["nccl", "peer"],
+                    help="e2e workload, N > 1: all-reduce of the decode steps through NCCL or the peer-memory kernel")
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
                     help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")
     ap.add_argument("--layers", type=int, default=36, help="mixed workload: layer caches per step")
@@ -495,7 +497,7 @@ def main():
         line = eb.run_e2e(nvk, torch, dist, rank, world, torch.device(f"cuda:{local_rank}"),
                           em.DecoderConfig(layers=args.e2e_layers), num_seqs=args.e2e_seqs,
                           len_lo=min(100, args.e2e_maxlen), len_hi=args.e2e_maxlen, use_graph=not args.no_graph,
-                          kv_dtype=args.e2e_kv)
+                          kv_dtype=args.e2e_kv, allreduce=args.e2e_allreduce)
         if sampler:
             line["clocks"] = sampler.finish()
         if rank == 0:

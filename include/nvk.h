@@ -155,6 +155,24 @@ int nvk_decode_attention_paged_static(const void* query, const void* k_cache, co
                                       float scale, void* output, int dtype, void* stream);
 
 /*
+ * Tensor-parallel all-reduce (sum, F16 / BF16) over NVLink peer memory for the latency-bound messages of a decode
+ * step.  Replaces, for that case, NcclTensorParallelCommunicator::all_reduce_sum
+ * (src/utils/tensor_parallel.cpp:331-353), called after o_proj and down_proj (src/layers/linear.cpp:315-318).
+ * One process per GPU; every rank owns an addend buffer, a result buffer and a flag area of
+ * nvk_tp_allreduce_flag_bytes() bytes (zeroed once), all mapped into every process (cudaIpc* or equivalent; plain peer
+ * mappings, no multicast).  in_ptrs / out_ptrs / flag_ptrs are HOST arrays of `world` device pointers as mapped in the
+ * calling process, index = rank.  Every rank calls with the same count (a multiple of 8 * world elements) in the same
+ * order; the result, identical on all ranks, is in the caller's own out buffer when the launch completes.  The launch
+ * may be captured in a CUDA graph.  Waits on peers are bounded (about one second); nvk_tp_allreduce_status copies the
+ * error word of the caller's flag area to the host (synchronises the stream): 0 = ok, 1 / 2 = a peer never arrived.
+ */
+#define NVK_TP_MAX_RANKS 8
+size_t nvk_tp_allreduce_flag_bytes(void);
+int nvk_tp_allreduce(const void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank, int world,
+                     int64_t count, int dtype, void* stream);
+int nvk_tp_allreduce_status(const void* own_flags, void* stream, int* status);
+
+/*
  * Replaces nano_vllm::launch_prefill_attention_dense / launch_prefill_attention_paged
  * (include/kernels/attention.h:7-29; kernels src/kernels/attention.cu:114-202 and :205-302)
  * and flash_attn_varlen_fwd (include/kernels/flash_attn.h:15-26).

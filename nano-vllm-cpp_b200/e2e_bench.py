@@ -18,7 +18,7 @@ RING = 64   # pinned metadata slots in flight
 
 
 def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None, num_seqs=256, len_lo=100, len_hi=1024,
-            seed=0, use_graph=True, kv_dtype="bf16"):
+            seed=0, use_graph=True, kv_dtype="bf16", allreduce="nccl"):
     cfg = cfg or DecoderConfig()
     bs = cfg.block_size
     prompts, output_lens = make_requests(num_seqs, cfg.vocab, len_lo, len_hi, seed)
@@ -26,7 +26,11 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
     table_width = (2 * len_hi + bs - 1) // bs
     num_blocks = blocks_needed(prompt_lens, output_lens, bs) + 8
     t0 = time.time()
-    model = Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=num_blocks, seed=seed, kv_dtype=kv_dtype)
+    comm = None
+    if allreduce == "peer" and world > 1:
+        from .tp_comm import PeerAllReduce
+        comm = PeerAllReduce(nvk, torch, dist, dev, rank, world, num_seqs * cfg.hidden, torch.bfloat16)
+    model = Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=num_blocks, seed=seed, kv_dtype=kv_dtype, peer_comm=comm)
     torch.cuda.synchronize()
     build_s = time.time() - t0
     model.ensure_workspace(num_seqs, table_width)
@@ -127,12 +131,13 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
         torch.cuda.synchronize()
         attn_ms = a0.elapsed_time(a1) / 10
 
+    comm_status = comm.status() if comm is not None else 0
     times = torch.tensor([total_ms, prefill_ms, decode_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms, prefill_ms, decode_ms = (float(x) for x in times.tolist())
     out_tokens = int(output_lens.sum())
-    return {
+    line = {
         "metric": "qwen3_8b_output_tokens_per_s", "value": out_tokens / (total_ms / 1e3), "unit": "tok/s", "n_gpus": world,
         "steps": len(batches) + steps, "warmup": 4, "ms_per_step": decode_ms / max(steps, 1), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -141,6 +146,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
                                f"prompt and output lengths U[{len_lo},{len_hi}], greedy, ignore_eos",
                    "parallelism": f"tp{world} (KV-head shards, NCCL all-reduce after o_proj / down_proj)",
                    "kv_cache": "int8 with fp16 per-(token, head) scales" if model.int8 else "bf16",
+                   "allreduce": ("decode steps: peer-memory kernel (nvk_tp_allreduce); prefill steps: NCCL" if comm is not None else "NCCL"),
                    "decode": "one captured CUDA graph of %d fixed rows" % num_seqs if graph is not None else "eager",
                    "prefill_batches": len(batches), "decode_steps": steps, "kv_blocks": num_blocks,
                    "l2": "weights (16.4 GB / tp) and KV cache exceed the 126 MB L2"},
@@ -149,10 +155,14 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
         "mean_active_rows": active_rows / max(steps, 1),
         "attention_ms_per_decode_step": attn_ms,
         "attention_share_of_decode_step": (attn_ms / (decode_ms / max(steps, 1))) if attn_ms else None,
-        "model_build_s": build_s,
+        "model_build_s": build_s, "peer_allreduce_status": comm_status,
         "gpu_launches": our_launches, "gpu_launches_issued_eagerly": eager_launches,
         "e2e": {"value": out_tokens / (total_ms / 1e3), "unit": "tok/s",
                 "h2d_bytes_per_step": num_seqs * width * 4, "d2h_bytes_per_step": 0,
                 "note": "the timed region already runs through the host scheduler and copies every step's metadata from pinned "
                         "memory; sampled tokens stay on the device (ignore_eos: the host needs no token to schedule)"},
     }
+    if comm is not None:
+        del graph
+        comm.close()
+    return line

@@ -45,11 +45,13 @@ def rope_table(torch, dev, max_positions, head_dim, theta):
 class Decoder:
     """One tensor-parallel rank of the decoder."""
 
-    def __init__(self, nvk, torch, dev, cfg: DecoderConfig, rank=0, world=1, dist=None, num_blocks=0, seed=0, kv_dtype="bf16"):
+    def __init__(self, nvk, torch, dev, cfg: DecoderConfig, rank=0, world=1, dist=None, num_blocks=0, seed=0, kv_dtype="bf16", peer_comm=None):
         if cfg.num_kv_heads % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, ffn and vocab must divide by the tensor-parallel size")
         self.nvk, self.torch, self.dev, self.cfg = nvk, torch, dev, cfg
         self.rank, self.world, self.dist = rank, world, dist
+        # optional tp_comm.PeerAllReduce: messages that fit its buffers take the peer-memory kernel, larger ones NCCL
+        self.peer_comm = peer_comm if world > 1 else None
         self.hq, self.hkv = cfg.num_heads // world, cfg.num_kv_heads // world
         self.ffn, self.vocab = cfg.ffn // world, cfg.vocab // world
         bf = torch.bfloat16
@@ -106,6 +108,17 @@ class Decoder:
             self.dist.all_reduce(x)
         return x
 
+    def row_parallel(self, a, w):
+        """``a @ w.T`` summed over the tensor-parallel ranks (o_proj / down_proj, src/layers/linear.cpp:306-320)."""
+        n, cols = a.shape[0], w.shape[0]
+        comm = self.peer_comm
+        if comm is not None and n * cols <= comm.max_elems and (n * cols) % (8 * self.world) == 0:
+            addend, result = comm.buffers(n, cols)
+            self.torch.matmul(a, w.t(), out=addend)      # the GEMM writes straight into the buffer the peers read
+            comm.all_reduce(n * cols)
+            return result
+        return self.all_reduce(a @ w.t())
+
     def ensure_workspace(self, batch, table_width):
         need = self.nvk.decode_attention_workspace_bytes(batch, self.hq, self.hkv, self.cfg.head_dim, table_width,
                                                          self.cfg.block_size)
@@ -139,11 +152,11 @@ class Decoder:
                 nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, slot_mapping,
                                                 self.kv_cache[0, l], self.kv_cache[1, l], self.hq, self.hkv, cfg.head_dim, q)
             attend(l, q, k_step, v_step, attn)
-            h = h + self.all_reduce(attn.view(n, -1) @ w["w_o"].t())
+            h = h + self.row_parallel(attn.view(n, -1), w["w_o"])
             x = self.rmsnorm(h, w["norm_post"])
             gu = x @ w["w_gate_up"].t()
             act = torch.nn.functional.silu(gu[:, :self.ffn]) * gu[:, self.ffn:]
-            h = h + self.all_reduce(act @ w["w_down"].t())
+            h = h + self.row_parallel(act, w["w_down"])
         return h
 
     def attend_prefill(self, cu_q, cu_k, tables):

@@ -8,14 +8,28 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def test_kv_head_sharded_decoder_matches_single_gpu():
+@pytest.mark.parametrize("peer", ["0", "1"])
+def test_kv_head_sharded_decoder_matches_single_gpu(peer):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_CHECK_PEER=peer)
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                          "127.0.0.1", "--master-port", "29533", os.path.join(here, "tp_check.py")], env=env,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "step 2" in res.stdout
+
+
+def test_peer_memory_all_reduce_matches_nccl():
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-                          "127.0.0.1", "--master-port", "29533", os.path.join(here, "tp_check.py")], env=env,
+                          "127.0.0.1", "--master-port", "29534", os.path.join(here, "tp_allreduce_check.py")], env=env,
                          capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    assert "step 2" in res.stdout
+    assert "timing world 2" in res.stdout

@@ -1,0 +1,102 @@
+"""Child program of tests/test_e2e_tp.py (torch.distributed.run, one process per GPU): the peer-memory all-reduce
+against NCCL on the same addends -- repeated eager calls (the launch counter in the flags advances), calls replayed from
+a CUDA graph, a ragged count, and a timing of both for the decode-step message (256 x 4096 bf16)."""
+import importlib
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    dist.init_process_group("nccl", device_id=dev)
+    nvk = entry.load_package()
+    nvk.lib()
+    tc = importlib.import_module(entry.PKG_NAME + ".tp_comm")
+    rows, cols = 256, 4096
+    comm = tc.PeerAllReduce(nvk, torch, dist, dev, rank, world, rows * cols, torch.bfloat16)
+    addend, result = comm.buffers(rows, cols)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(100 + rank)
+    ok = True
+    tol = 0.0 if world == 2 else 0.05      # two addends: one rounding either way; more: NCCL rounds between additions
+
+    def compare(tag, n):
+        nonlocal ok
+        want = addend.view(-1)[:n].clone()
+        dist.all_reduce(want)
+        torch.cuda.synchronize()
+        err = float((result.view(-1)[:n].float() - want.float()).abs().max())
+        if rank == 0:
+            print(f"{tag}: max |peer - nccl| = {err:.4e}", flush=True)
+        ok = ok and err <= tol
+
+    for it in range(20):                                   # eager calls, fresh data every time
+        addend.copy_(torch.randn((rows, cols), generator=gen, device=dev))
+        n = rows * cols if it % 3 else 8 * world * (1000 + it)   # also counts that do not fill every block
+        comm.all_reduce(n)
+        compare(f"eager {it}", n)
+
+    graph = torch.cuda.CUDAGraph()                          # replayed calls: three all-reduces per replay
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        comm.all_reduce(rows * cols)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    with torch.cuda.graph(graph):
+        for _ in range(3):
+            comm.all_reduce(rows * cols)
+    for it in range(5):
+        addend.copy_(torch.randn((rows, cols), generator=gen, device=dev))
+        graph.replay()
+        compare(f"graph {it}", rows * cols)
+    status = comm.status()
+    ok = ok and status == 0
+
+    # timing, 72 per replay as in a decode step of 36 layers
+    def timed(fn, reps=20):
+        g = torch.cuda.CUDAGraph()
+        fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.graph(g):
+            for _ in range(72):
+                fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps / 72 * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    scratch = torch.randn((rows, cols), generator=gen, device=dev).to(torch.bfloat16)
+    us_peer = timed(lambda: comm.all_reduce(rows * cols))
+    us_nccl = timed(lambda: dist.all_reduce(scratch))
+    if rank == 0:
+        print(f"timing world {world}: peer-memory all-reduce {us_peer:.2f} us, NCCL {us_nccl:.2f} us per 2 MiB message (in a graph)", flush=True)
+    comm.close()
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    return 0 if int(flag.item()) == 1 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

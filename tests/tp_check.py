@@ -45,7 +45,14 @@ def main():
                                     model.attend_decode(m[:, 2].contiguous(), m[:, 3:].contiguous())).float())
         return hs
 
-    sharded = run(em.Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=16, seed=4))
+    comm = None
+    if os.environ.get("TP_CHECK_PEER") == "1":   # decode-step all-reduces through the peer-memory kernel
+        tc = importlib.import_module(entry.PKG_NAME + ".tp_comm")
+        comm = tc.PeerAllReduce(nvk, torch, dist, dev, rank, world, 8 * cfg.hidden, torch.bfloat16)
+    sharded = run(em.Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=16, seed=4, peer_comm=comm))
+    if comm is not None:
+        assert comm.status() == 0
+        comm.close()
     ok = True
     if rank == 0:
         single = run(em.Decoder(nvk, torch, dev, cfg, 0, 1, None, num_blocks=16, seed=4))
