@@ -27,7 +27,6 @@ def main():
     gen = torch.Generator(device=dev)
     gen.manual_seed(100 + rank)
     ok = True
-    tol = 0.0 if world == 2 else 0.05      # two addends: one rounding either way; more: NCCL rounds between additions
 
     def compare(tag, n):
         nonlocal ok
@@ -35,8 +34,11 @@ def main():
         dist.all_reduce(want)
         torch.cuda.synchronize()
         err = float((result.view(-1)[:n].float() - want.float()).abs().max())
+        # two addends: one rounding either way, bit-identical; more: NCCL rounds to bf16 between additions, this kernel once
+        # at the end -- allow a few bf16 units in the last place of the largest sum
+        tol = 0.0 if world == 2 else 4.0 * 2.0 ** -8 * float(want.float().abs().max())
         if rank == 0:
-            print(f"{tag}: max |peer - nccl| = {err:.4e}", flush=True)
+            print(f"{tag}: max |peer - nccl| = {err:.4e} (allowed {tol:.4e})", flush=True)
         ok = ok and err <= tol
 
     for it in range(20):                                   # eager calls, fresh data every time
