@@ -171,6 +171,18 @@ size_t nvk_tp_allreduce_flag_bytes(void);
 int nvk_tp_allreduce(const void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank, int world,
                      int64_t count, int dtype, void* stream);
 int nvk_tp_allreduce_status(const void* own_flags, void* stream, int* status);
+/*
+ * The same all-reduce with the residual add and the RMSNorm that follow it in a decoder layer folded in:
+ *   h_new = residual + bf16(sum over ranks of addend)   -> every rank's out buffer   [rows, cols]
+ *   x     = rmsnorm(h_new, eps) * weight                -> every rank's norm buffer  [rows, cols]
+ * rows must be a multiple of world (a rank reduces rows / world whole rows), cols a multiple of 8, at most 8192.
+ * residual [rows, cols] is the caller's own copy (identical on all ranks), weight [cols]; both ordinary device memory.
+ * Rounding follows the unfused sequence (sum rounded to the 16-bit type, added to the residual in it, normalised from the
+ * rounded h_new), so results agree with all-reduce + add + rms_norm to within one unit of the 16-bit type.
+ */
+int nvk_tp_allreduce_add_rmsnorm(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
+                                 void* const* flag_ptrs, const void* residual, const void* weight, float eps,
+                                 int rank, int world, int rows, int cols, int dtype, void* stream);
 
 /*
  * Replaces nano_vllm::launch_prefill_attention_dense / launch_prefill_attention_paged

@@ -22,7 +22,7 @@
 namespace nvk {
 namespace {
 
-constexpr int kArBlocks = 96;            // most blocks a launch uses = flag slots per phase
+constexpr int kArBlocks = 128;           // most blocks a launch uses = flag slots per phase
 constexpr int kArUnroll = 2;             // vectors a thread has in flight
 constexpr int kArThreads = 256;
 constexpr long long kArWaitCycles = 2000000000LL;
@@ -137,6 +137,131 @@ __global__ void __launch_bounds__(kArThreads) allreduce_two_shot_kernel(const Ar
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same all-reduce with the two element-wise kernels that follow it in a decoder layer folded in:
+//     h_new = residual + sum over ranks of addend          (src/layers/linear.cpp:315-318 then the residual add)
+//     x     = rmsnorm(h_new) * weight                      (the layer norm that consumes h_new next)
+// A rank's chunk of the [rows, cols] message is rows / world whole rows, so the rank that reduces a row also has all of
+// it for the mean of squares: it adds its (replicated) residual row, rounds to T, normalises the rounded values as the
+// separate kernel would, and pushes both rows into every rank's `out` (h_new) and `norm` (x) buffers.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kNormMaxVecs = 4;   // 16-byte vectors of a row per thread: cols <= 256 * 4 * 8 = 8192
+
+struct ArNormParams {
+    ArParams ar;
+    void* norm[NVK_TP_MAX_RANKS];     // every rank's buffer for x
+    const void* residual;             // [rows, cols], this rank's copy (identical on all ranks)
+    const void* weight;               // [cols]
+    float eps;
+    int rows, cols;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kArThreads) allreduce_add_rmsnorm_kernel(const ArNormParams q) {
+    const ArParams& p = q.ar;
+    __shared__ int s_timed_out;
+    __shared__ float s_part[kArThreads / 32];
+    if (threadIdx.x == 0) s_timed_out = 0;
+    __syncthreads();
+    uint32_t* my_flags = p.flags[p.rank];
+    const uint32_t epoch = my_flags[0] + 1u;
+
+    bool ok = exchange(p, 0, epoch, &s_timed_out);
+
+    if (ok) {
+        const int rows_per_rank = q.rows / p.world;
+        const int row_vecs = q.cols / 8;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        for (int lr = blockIdx.x; lr < rows_per_rank; lr += gridDim.x) {
+            const int64_t row = static_cast<int64_t>(p.rank) * rows_per_rank + lr;
+            const int64_t base = row * row_vecs;
+            uint4 part[kNormMaxVecs][NVK_TP_MAX_RANKS];
+            uint4 res[kNormMaxVecs];
+#pragma unroll
+            for (int u = 0; u < kNormMaxVecs; ++u) {   // every load first
+                const int v = threadIdx.x + u * kArThreads;
+                if (v < row_vecs) {
+                    res[u] = static_cast<const uint4*>(q.residual)[base + v];
+#pragma unroll
+                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
+                        if (r < p.world) part[u][r] = ld_peer16(static_cast<const uint4*>(p.in[r]) + base + v);
+                }
+            }
+            float hn[kNormMaxVecs][8];
+            uint4 hpack[kNormMaxVecs];
+            float ss = 0.0f;
+#pragma unroll
+            for (int u = 0; u < kNormMaxVecs; ++u) {
+                const int v = threadIdx.x + u * kArThreads;
+                if (v < row_vecs) {
+                    float acc[8];
+                    const T* e0 = reinterpret_cast<const T*>(&res[u]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) {
+                        if (r < p.world) {
+                            const T* e = reinterpret_cast<const T*>(&part[u][r]);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[i] += ElemTraits<T>::to_float(e[i]);
+                        }
+                    }
+                    // the sum is rounded to T first (what the all-reduce alone would deliver), then the residual is added in T
+                    T* hp = reinterpret_cast<T*>(&hpack[u]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float s = ElemTraits<T>::to_float(ElemTraits<T>::from_float(acc[i]));
+                        hp[i] = ElemTraits<T>::from_float(ElemTraits<T>::to_float(e0[i]) + s);
+                        hn[u][i] = ElemTraits<T>::to_float(hp[i]);
+                        ss += hn[u][i] * hn[u][i];
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            __syncthreads();   // s_part of the previous row has been read by everyone
+            if (lane == 0) s_part[warp] = ss;
+            __syncthreads();
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kArThreads / 32; ++w) total += s_part[w];
+            const float inv_rms = rsqrtf(total / static_cast<float>(q.cols) + q.eps);
+#pragma unroll
+            for (int u = 0; u < kNormMaxVecs; ++u) {
+                const int v = threadIdx.x + u * kArThreads;
+                if (v < row_vecs) {
+                    const uint4 wv = static_cast<const uint4*>(q.weight)[v];
+                    const T* we = reinterpret_cast<const T*>(&wv);
+                    uint4 xpack;
+                    T* xp = reinterpret_cast<T*>(&xpack);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        xp[i] = ElemTraits<T>::from_float(hn[u][i] * inv_rms * ElemTraits<T>::to_float(we[i]));
+#pragma unroll
+                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) {
+                        if (r < p.world) {
+                            static_cast<uint4*>(p.out[r])[base + v] = hpack[u];
+                            static_cast<uint4*>(q.norm[r])[base + v] = xpack;
+                        }
+                    }
+                }
+            }
+        }
+        __threadfence_system();
+        __syncthreads();
+        ok = exchange(p, 1, epoch, &s_timed_out);
+    }
+
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(reinterpret_cast<unsigned int*>(my_flags + 1), 1u) == gridDim.x - 1) {
+            my_flags[1] = 0u;
+            my_flags[0] = epoch;
+            __threadfence();
+        }
+    }
+}
+
 }  // namespace
 }  // namespace nvk
 
@@ -184,4 +309,37 @@ extern "C" int nvk_tp_allreduce_status(const void* own_flags, void* stream, int*
     if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "tp all-reduce status: %s", cudaGetErrorString(e));
     *status = static_cast<int>(word);
     return NVK_OK;
+}
+
+extern "C" int nvk_tp_allreduce_add_rmsnorm(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
+                                            void* const* flag_ptrs, const void* residual, const void* weight, float eps,
+                                            int rank, int world, int rows, int cols, int dtype, void* stream) {
+    using namespace nvk;
+    if (!in_ptrs || !out_ptrs || !norm_ptrs || !flag_ptrs || !residual || !weight)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: every pointer must be defined");
+    if (world < 2 || world > NVK_TP_MAX_RANKS || rank < 0 || rank >= world)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: world must be 2..%d and rank inside it", NVK_TP_MAX_RANKS);
+    if (dtype != NVK_F16 && dtype != NVK_BF16) return fail(NVK_ERR_UNSUPPORTED, "tp all-reduce + add + rmsnorm: dtype must be F16 or BF16");
+    if (rows <= 0 || rows % world != 0) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: rows must be a positive multiple of world");
+    if (cols <= 0 || cols % 8 != 0 || cols > kArThreads * kNormMaxVecs * 8)
+        return fail(NVK_ERR_UNSUPPORTED, "tp all-reduce + add + rmsnorm: cols must be a multiple of 8 and at most %d", kArThreads * kNormMaxVecs * 8);
+    if (!aligned_to(residual, 16) || !aligned_to(weight, 16))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: residual and weight must be 16-byte aligned");
+    ArNormParams q{};
+    for (int r = 0; r < world; ++r) {
+        if (!in_ptrs[r] || !out_ptrs[r] || !norm_ptrs[r] || !flag_ptrs[r])
+            return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: null buffer of rank %d", r);
+        if (!aligned_to(in_ptrs[r], 16) || !aligned_to(out_ptrs[r], 16) || !aligned_to(norm_ptrs[r], 16) || !aligned_to(flag_ptrs[r], 4))
+            return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: buffers must be 16-byte aligned");
+        q.ar.in[r] = in_ptrs[r]; q.ar.out[r] = out_ptrs[r]; q.norm[r] = norm_ptrs[r]; q.ar.flags[r] = static_cast<uint32_t*>(flag_ptrs[r]);
+    }
+    q.ar.rank = rank; q.ar.world = world; q.ar.count = static_cast<int64_t>(rows) * cols;
+    q.residual = residual; q.weight = weight; q.eps = eps; q.rows = rows; q.cols = cols;
+    int blocks = rows / world;
+    if (blocks > kArBlocks) blocks = kArBlocks;
+    if (dtype == NVK_BF16)
+        allreduce_add_rmsnorm_kernel<__nv_bfloat16><<<blocks, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(q);
+    else
+        allreduce_add_rmsnorm_kernel<__half><<<blocks, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(q);
+    return check_launch("allreduce_add_rmsnorm_kernel launch");
 }

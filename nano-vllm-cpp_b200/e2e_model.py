@@ -108,16 +108,19 @@ class Decoder:
             self.dist.all_reduce(x)
         return x
 
-    def row_parallel(self, a, w):
-        """``a @ w.T`` summed over the tensor-parallel ranks (o_proj / down_proj, src/layers/linear.cpp:306-320)."""
+    def row_parallel_add_norm(self, a, w, h, norm_w):
+        """``h + (a @ w.T summed over the tensor-parallel ranks)`` and its RMSNorm with ``norm_w`` (o_proj / down_proj,
+        src/layers/linear.cpp:306-320, followed by the residual add and the next layer norm).  Messages that fit the peer
+        buffers take one fused launch (nvk_tp_allreduce_add_rmsnorm); the GEMM writes straight into the addend buffer."""
         n, cols = a.shape[0], w.shape[0]
         comm = self.peer_comm
-        if comm is not None and n * cols <= comm.max_elems and (n * cols) % (8 * self.world) == 0:
-            addend, result = comm.buffers(n, cols)
-            self.torch.matmul(a, w.t(), out=addend)      # the GEMM writes straight into the buffer the peers read
-            comm.all_reduce(n * cols)
-            return result
-        return self.all_reduce(a @ w.t())
+        if (comm is not None and n * cols <= comm.max_elems and n % self.world == 0 and cols % 8 == 0 and cols <= 8192
+                and h.is_contiguous()):
+            addend, _ = comm.buffers(n, cols)
+            self.torch.matmul(a, w.t(), out=addend)
+            return comm.all_reduce_add_rmsnorm(h, norm_w, self.cfg.eps, n, cols)
+        h = h + self.all_reduce(a @ w.t())
+        return h, self.rmsnorm(h, norm_w)
 
     def ensure_workspace(self, batch, table_width):
         need = self.nvk.decode_attention_workspace_bytes(batch, self.hq, self.hkv, self.cfg.head_dim, table_width,
@@ -140,8 +143,8 @@ class Decoder:
             k_step = torch.empty((n, self.hkv, cfg.head_dim), device=self.dev, dtype=h.dtype)
             v_step = torch.empty_like(k_step)
             rows = torch.arange(n, device=self.dev, dtype=torch.int32)
+        x = self.rmsnorm(h, self.layers[0]["norm_in"])
         for l, w in enumerate(self.layers):
-            x = self.rmsnorm(h, w["norm_in"])
             qkv = x @ w["w_qkv"].t()
             if self.int8:
                 nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, rows,
@@ -152,11 +155,11 @@ class Decoder:
                 nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, slot_mapping,
                                                 self.kv_cache[0, l], self.kv_cache[1, l], self.hq, self.hkv, cfg.head_dim, q)
             attend(l, q, k_step, v_step, attn)
-            h = h + self.row_parallel(attn.view(n, -1), w["w_o"])
-            x = self.rmsnorm(h, w["norm_post"])
+            h, x = self.row_parallel_add_norm(attn.view(n, -1), w["w_o"], h, w["norm_post"])
             gu = x @ w["w_gate_up"].t()
             act = torch.nn.functional.silu(gu[:, :self.ffn]) * gu[:, self.ffn:]
-            h = h + self.row_parallel(act, w["w_down"])
+            next_norm = self.layers[l + 1]["norm_in"] if l + 1 < len(self.layers) else self.final_norm
+            h, x = self.row_parallel_add_norm(act, w["w_down"], h, next_norm)
         return h
 
     def attend_prefill(self, cu_q, cu_k, tables):

@@ -35,7 +35,8 @@ class PeerAllReduce:
         lib = nvk.lib()
         lib.nvk_tp_allreduce_flag_bytes.restype = ctypes.c_size_t
         flag_bytes = int(lib.nvk_tp_allreduce_flag_bytes())
-        sizes = {"in": self.max_elems * 2, "out": self.max_elems * 2, "flags": (flag_bytes + 255) // 256 * 256}
+        sizes = {"in": self.max_elems * 2, "out": self.max_elems * 2, "norm": self.max_elems * 2,
+                 "flags": (flag_bytes + 255) // 256 * 256}
         self._own, handles = {}, {}
         for name, nbytes in sizes.items():
             err, ptr = cudart.cudaMalloc(nbytes)
@@ -65,10 +66,13 @@ class PeerAllReduce:
         self._in_tab = arr(*self._ptrs["in"])
         self._out_tab = arr(*self._ptrs["out"])
         self._flag_tab = arr(*self._ptrs["flags"])
+        self._norm_tab = arr(*self._ptrs["norm"])
+        self._norm_block = _DeviceBlock(*self._own["norm"])
         self._in_block = _DeviceBlock(*self._own["in"])
         self._out_block = _DeviceBlock(*self._own["out"])
         self.addend = torch.as_tensor(self._in_block, device=dev).view(dtype)    # [max_elems], this rank's addend
         self.result = torch.as_tensor(self._out_block, device=dev).view(dtype)   # [max_elems], the sum
+        self.normed = torch.as_tensor(self._norm_block, device=dev).view(dtype)  # [max_elems], rmsnorm of (residual + sum)
         dist.barrier()   # every rank has mapped every buffer before anyone launches
 
     def buffers(self, rows: int, cols: int):
@@ -88,6 +92,21 @@ class PeerAllReduce:
                                               ctypes.c_int(self.world), ctypes.c_int64(count),
                                               ctypes.c_int(nvk._dtype_code(self.addend)), stream))
         nvk.launch_count += 1
+
+    def all_reduce_add_rmsnorm(self, residual, weight, eps: float, rows: int, cols: int):
+        """``h = residual + sum of every rank's addend``, ``x = rmsnorm(h) * weight`` in one launch; returns views of
+        this rank's result and norm buffers shaped [rows, cols].  ``residual`` may be the result buffer itself."""
+        nvk, torch = self.nvk, self.torch
+        n = rows * cols
+        if n > self.max_elems or rows % self.world != 0:
+            raise ValueError("rows must be a multiple of world and the message must fit the peer buffers")
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nvk._check(nvk.lib().nvk_tp_allreduce_add_rmsnorm(
+            self._in_tab, self._out_tab, self._norm_tab, self._flag_tab, ctypes.c_void_p(residual.data_ptr()),
+            ctypes.c_void_p(weight.data_ptr()), ctypes.c_float(eps), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+            ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(nvk._dtype_code(self.addend)), stream))
+        nvk.launch_count += 1
+        return self.result[:n].view(rows, cols), self.normed[:n].view(rows, cols)
 
     def status(self) -> int:
         """0 when every wait on the peers completed; 1 / 2 when a peer never arrived (synchronises the stream)."""

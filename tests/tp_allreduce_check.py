@@ -62,6 +62,27 @@ def main():
         addend.copy_(torch.randn((rows, cols), generator=gen, device=dev))
         graph.replay()
         compare(f"graph {it}", rows * cols)
+    # fused form: h = residual + sum, x = rmsnorm(h) * weight, against NCCL + torch on the same data
+    weight = (1.0 + 0.1 * torch.randn(cols, generator=gen, device=dev)).to(torch.bfloat16)
+    dist.broadcast(weight, 0)
+    residual = torch.randn((rows, cols), generator=gen, device=dev).to(torch.bfloat16)
+    dist.broadcast(residual, 0)
+    for it in range(4):
+        addend.copy_(torch.randn((rows, cols), generator=gen, device=dev))
+        want_sum = addend.clone()
+        dist.all_reduce(want_sum)
+        want_h = residual + want_sum
+        want_x = torch.nn.functional.rms_norm(want_h, (cols,), weight, 1e-6)
+        h_new, x = comm.all_reduce_add_rmsnorm(residual, weight, 1e-6, rows, cols)
+        torch.cuda.synchronize()
+        eh = float((h_new.float() - want_h.float()).abs().max())
+        ex = float((x.float() - want_x.float()).abs().max())
+        tol_h = (0.0 if world == 2 else 4.0 * 2.0 ** -8 * float(want_h.float().abs().max()))
+        tol_x = 2.0 ** -6 * float(want_x.float().abs().max()) + (0.0 if world == 2 else 0.05)
+        if rank == 0:
+            print(f"fused {it}: max |h - ref| = {eh:.4e} (allowed {tol_h:.4e}), max |x - ref| = {ex:.4e} (allowed {tol_x:.4e})", flush=True)
+        ok = ok and eh <= tol_h and ex <= tol_x
+        residual = h_new.clone()      # next round continues from the new hidden state, as a decoder does
     status = comm.status()
     ok = ok and status == 0
 
@@ -91,8 +112,17 @@ def main():
     scratch = torch.randn((rows, cols), generator=gen, device=dev).to(torch.bfloat16)
     us_peer = timed(lambda: comm.all_reduce(rows * cols))
     us_nccl = timed(lambda: dist.all_reduce(scratch))
+    res_buf = residual.clone()
+
+    def unfused():
+        dist.all_reduce(scratch)
+        torch.nn.functional.rms_norm(res_buf + scratch, (cols,), weight, 1e-6)
+
+    us_fused = timed(lambda: comm.all_reduce_add_rmsnorm(res_buf, weight, 1e-6, rows, cols))
+    us_unfused = timed(unfused)
     if rank == 0:
         print(f"timing world {world}: peer-memory all-reduce {us_peer:.2f} us, NCCL {us_nccl:.2f} us per 2 MiB message (in a graph)", flush=True)
+        print(f"timing world {world}: fused all-reduce + add + rmsnorm {us_fused:.2f} us, NCCL + add + rms_norm {us_unfused:.2f} us", flush=True)
     comm.close()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
