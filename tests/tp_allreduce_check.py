@@ -1,6 +1,8 @@
 """Child program of tests/test_e2e_tp.py (torch.distributed.run, one process per GPU): the peer-memory all-reduce
 against NCCL on the same addends -- repeated eager calls (the launch counter in the flags advances), calls replayed from
-a CUDA graph, a ragged count, and a timing of both for the decode-step message (256 x 4096 bf16)."""
+a CUDA graph, a ragged count, the fused all-reduce + residual add + RMSNorm against NCCL + torch, chains of 32 dependent
+launches replayed from a graph (every replay and every rank must end with the same bits), and a timing of all of them
+for the decode-step message (256 x 4096 bf16)."""
 import importlib
 import os
 import sys
@@ -83,6 +85,73 @@ def main():
             print(f"fused {it}: max |h - ref| = {eh:.4e} (allowed {tol_h:.4e}), max |x - ref| = {ex:.4e} (allowed {tol_x:.4e})", flush=True)
         ok = ok and eh <= tol_h and ex <= tol_x
         residual = h_new.clone()      # next round continues from the new hidden state, as a decoder does
+    # back-to-back launches with a consumer between them, as in a decoder: round k's addend depends on round k-1's sum,
+    # so a launch that read an addend too early or left its result incomplete changes the end of the chain
+    rounds = 32
+    noise = torch.randn((rounds, rows, cols), generator=gen, device=dev).to(torch.bfloat16)
+    scratch_chain = torch.empty((rows, cols), device=dev, dtype=torch.bfloat16)
+
+    def chain_peer():
+        addend.copy_(noise[0])
+        for k in range(1, rounds):
+            comm.all_reduce(rows * cols)
+            torch.add(noise[k], result, alpha=1.0 / world, out=addend)
+        comm.all_reduce(rows * cols)
+
+    def chain_nccl():
+        scratch_chain.copy_(noise[0])
+        for k in range(1, rounds):
+            dist.all_reduce(scratch_chain)
+            torch.add(noise[k], scratch_chain, alpha=1.0 / world, out=scratch_chain)
+        dist.all_reduce(scratch_chain)
+
+    chain_nccl()
+    chain_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(chain_graph):
+        chain_peer()
+    firsts = None
+    for it in range(6):
+        chain_graph.replay()
+        torch.cuda.synchronize()
+        got = result.clone()
+        err = float((got.float() - scratch_chain.float()).abs().max())
+        tol = 0.0 if world == 2 else 0.02 * float(scratch_chain.float().abs().max())
+        same = True if firsts is None else bool(torch.equal(got, firsts))
+        firsts = got if firsts is None else firsts
+        if rank == 0:
+            print(f"chain of {rounds} replay {it}: max |peer - nccl| = {err:.4e} (allowed {tol:.4e}), identical to replay 0: {same}", flush=True)
+        ok = ok and err <= tol and same
+    # the fused kernel in the same kind of chain: every replay and every rank must end with the same bits
+    def chain_fused():
+        h = residual_start
+        addend.copy_(noise[0])
+        for k in range(1, rounds):
+            h, x = comm.all_reduce_add_rmsnorm(h, weight, 1e-6, rows, cols)
+            torch.add(noise[k], x, alpha=0.25, out=addend)
+        return comm.all_reduce_add_rmsnorm(h, weight, 1e-6, rows, cols)
+
+    residual_start = residual.clone()
+    fused_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(fused_graph):
+        h_end, x_end = chain_fused()
+    firsts = None
+    for it in range(6):
+        fused_graph.replay()
+        torch.cuda.synchronize()
+        got = torch.cat([h_end.reshape(-1), x_end.reshape(-1)]).clone()
+        if firsts is None:
+            firsts = got
+            gathered = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(gathered, got)
+            same_ranks = all(bool(torch.equal(g, got)) for g in gathered)
+            finite = bool(torch.isfinite(got.float()).all())
+            if rank == 0:
+                print(f"fused chain: identical on all ranks: {same_ranks}, finite: {finite}", flush=True)
+            ok = ok and same_ranks and finite
+        same = bool(torch.equal(got, firsts))
+        if rank == 0:
+            print(f"fused chain replay {it}: identical to replay 0: {same}", flush=True)
+        ok = ok and same
     status = comm.status()
     ok = ok and status == 0
 
