@@ -66,7 +66,9 @@ int nvk_store_kvcache(const void* key, const void* value, void* k_cache, void* v
  * cos_sin_cache [max_positions, head_dim] = [cos | sin] (rows outside [0, max_positions) stay
  * un-rotated), q -> q_out [rows, Hq, D], k and v -> cache row slot_mapping[row] when that slot
  * is >= 0 (and < cache_rows: the reference checks only the lower bound, writing out of bounds
- * otherwise).  dtype in {F16, BF16}; positions and slot_mapping are int32.
+ * otherwise).  dtype in {F16, BF16}; positions and slot_mapping are int32.  head_dim in {64, 128,
+ * 256}; num_q_heads + 2 * num_kv_heads <= 16384 / head_dim; every tensor (the table included) starts
+ * on a 16-byte boundary.
  */
 int nvk_fused_split_norm_rope_store(const void* qkv, const int32_t* positions,
                                     const void* q_norm_weight, const void* k_norm_weight,

@@ -72,7 +72,7 @@ int nvk_fused_split_norm_rope_store(const void* qkv, const int32_t* positions, c
         return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: sizes must be positive");
     if (rows == 0) return NVK_OK;
     if (!aligned_to(qkv, 16) || !aligned_to(q_out, 16) || !aligned_to(k_cache, 16) || !aligned_to(v_cache, 16) ||
-        !aligned_to(q_norm_weight, 16) || !aligned_to(k_norm_weight, 16) || !aligned_to(cos_sin_cache, 4))
+        !aligned_to(q_norm_weight, 16) || !aligned_to(k_norm_weight, 16) || !aligned_to(cos_sin_cache, 16))
         return fail(NVK_ERR_UNSUPPORTED, "fused_split_norm_rope_store: tensors must be 16-byte aligned");
     return launch_fused_prologue(qkv, positions, q_norm_weight, k_norm_weight, norm_eps, cos_sin_cache,
                                  max_positions, slot_mapping, k_cache, v_cache, cache_rows, rows, num_q_heads,

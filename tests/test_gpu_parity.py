@@ -334,10 +334,14 @@ def test_prefill_rows_without_visible_keys_are_zero():
 
 # ------------------------------------------------------------------------------- fused prologue
 
-@pytest.mark.parametrize("num_q_heads,num_kv_heads,head_dim", [(32, 8, 128), (4, 1, 128), (4, 2, 64)])
-def test_fused_split_norm_rope_store_matches_oracle(num_q_heads, num_kv_heads, head_dim):
+# (q heads, kv heads, head_dim, rows): 1 to 8 sixteen-byte pieces per lane, lane groups without a head (5 / 56 heads),
+# more rows than the persistent grid has blocks (each block then pipelines several rows)
+@pytest.mark.parametrize("num_q_heads,num_kv_heads,head_dim,rows", [
+    (32, 8, 128, 37), (4, 1, 128, 37), (4, 2, 64, 37), (3, 1, 128, 9), (40, 8, 64, 50), (8, 2, 256, 37), (32, 8, 256, 20),
+    (64, 16, 128, 37), (96, 16, 128, 21), (32, 8, 128, 700), (64, 8, 128, 401)])
+def test_fused_split_norm_rope_store_matches_oracle(num_q_heads, num_kv_heads, head_dim, rows):
     wl = workloads()
-    rows, cache_rows, max_pos = 37, 512, 300
+    cache_rows, max_pos = max(512, rows + 64), 300
     w = wl.make_prologue_workload(rows, num_q_heads, num_kv_heads, head_dim, cache_rows, max_pos, seed=12)
     w["slot_mapping"][3] = -1                      # padded row: nothing written
     w["positions"][5] = max_pos + 7                # out of table: left un-rotated (split_qkv.cu:123)
