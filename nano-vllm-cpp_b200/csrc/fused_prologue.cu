@@ -5,14 +5,15 @@
 // a 128-thread block per (row, head), one element per thread, a block reduction and a
 // shared-memory exchange per head).  Here an 8-warp block owns whole ROWS: position, slot, the row
 // of the cos/sin table and the norm weights are fetched once per row instead of once per head.
-// A head vector is spread over D/8 lanes, 8 contiguous elements (one 16-byte load and store) per
-// lane, so a warp works on 32 / (D/8) heads at a time and a lane holds PIECES 16-byte pieces of
-// the row.  The sum of squares is a shuffle reduction inside the lane group and the rotation
-// partner (d +- D/2) lives in lane ^ (D/16), so there is no shared memory and no barrier.  The grid
-// is persistent (about two blocks per SM) and software-pipelined over rows: the pieces, position and
-// slot of the block's next row are requested before the current row is computed.  HBM-bound in the
-// limit of many rows (rows * (Hq + 2 Hkv) * D elements read, the same number written); at decode
-// batch sizes it is latency-bound.
+// A head vector is spread over D/8 lanes; a lane holds four whole rotation pairs (d, d + D/2): elements
+// [4s, 4s+4) of both halves of the head (two 8-byte loads and stores), so RoPE needs no exchange and a
+// warp works on 32 / (D/8) heads at a time.  The sum of squares is a shuffle reduction inside the lane
+// group; there is no shared memory and no barrier.  Arithmetic runs on packed fp32 pairs (mul / fma
+// .f32x2): the kernel was issue-bound, not byte-bound, with scalar arithmetic and a shuffle per element.
+// The grid is persistent (about two blocks per SM) and software-pipelined over rows: the pieces,
+// position and slot of the block's next row are requested before the current row is computed.
+// HBM-bound in the limit of many rows (rows * (Hq + 2 Hkv) * D elements read, the same number
+// written); at decode batch sizes it is latency-bound.
 #include "nvk_internal.cuh"
 
 namespace nvk {
@@ -20,6 +21,38 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 constexpr int kMaxPieces = 8;
+
+// Packed fp32 pairs (one 64-bit register pair per two values; Blackwell executes f32x2 mul / fma at one issue slot).
+using F2 = unsigned long long;
+__device__ __forceinline__ F2 f2_make(float lo, float hi) {
+    F2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_split(F2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
+    F2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
+    F2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+template <typename T> __device__ __forceinline__ F2 f2_unpack(uint32_t w);   // two 16-bit elements -> two floats
+template <> __device__ __forceinline__ F2 f2_unpack<__nv_bfloat16>(uint32_t w) {
+    return f2_make(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ F2 f2_unpack<__half>(uint32_t w) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    return f2_make(f.x, f.y);
+}
+template <typename T> __device__ __forceinline__ uint32_t f2_pack(F2 v) {
+    float lo, hi;
+    f2_split(v, lo, hi);
+    return ElemTraits<T>::pack2(lo, hi);
+}
 
 template <typename T, int LANES, int PIECES>   // LANES = D / 8 lanes per head: 8, 16 or 32
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, PIECES <= 3 ? 2 : 1)
@@ -34,54 +67,58 @@ fused_prologue_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ pos
     constexpr int STRIDE = kWarpsPerBlock * GROUPS;         // heads the block handles at once
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane % LANES, group = lane / LANES;
-    const bool low_half = sub < LANES / 2;
     const int heads = hq + 2 * hkv;                         // <= STRIDE * PIECES (the launcher picks PIECES)
     const int first_head = warp * GROUPS + group;
+    // this lane's 8 elements of a head: [sub*4, sub*4+4) of the first half and the same of the second half, i.e. four
+    // whole rotation pairs (d, d + D/2)
+    const int lo_off = sub * 4, hi_off = D / 2 + sub * 4;
 
-    union Pack { uint4 v; T e[8]; };
-    Pack wq, wk;                                            // norm weights of this lane's 8 elements, kept packed
-    wq.v = *reinterpret_cast<const uint4*>(q_weight + sub * 8);
-    wk.v = *reinterpret_cast<const uint4*>(k_weight + sub * 8);
+    struct Piece { uint2 lo, hi; };
+    Piece wq, wk;                                           // norm weights of this lane's elements, kept packed
+    wq.lo = *reinterpret_cast<const uint2*>(q_weight + lo_off); wq.hi = *reinterpret_cast<const uint2*>(q_weight + hi_off);
+    wk.lo = *reinterpret_cast<const uint2*>(k_weight + lo_off); wk.hi = *reinterpret_cast<const uint2*>(k_weight + hi_off);
 
     int64_t row = blockIdx.x;
     if (row >= rows) return;
-    Pack in[PIECES];
+    Piece in[PIECES];
     int pos = positions[row];
     int64_t slot = slot_mapping[row];
+    auto request = [&](Piece (&dst)[PIECES], int64_t r) {
 #pragma unroll
-    for (int u = 0; u < PIECES; ++u) {
-        const int head = first_head + u * STRIDE;
-        in[u].v = head < heads ? *reinterpret_cast<const uint4*>(qkv + (row * heads + head) * D + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
-    }
+        for (int u = 0; u < PIECES; ++u) {
+            const int head = first_head + u * STRIDE;
+            if (head < heads) {
+                const T* src = qkv + (r * heads + head) * D;
+                dst[u].lo = *reinterpret_cast<const uint2*>(src + lo_off);
+                dst[u].hi = *reinterpret_cast<const uint2*>(src + hi_off);
+            } else {
+                dst[u].lo = make_uint2(0u, 0u);
+                dst[u].hi = make_uint2(0u, 0u);
+            }
+        }
+    };
+    request(in, row);
     for (; row < rows; row += gridDim.x) {
         const bool rotate = pos >= 0 && pos < max_positions;
         const bool store_kv = slot >= 0 && slot < cache_rows;
-        // cos / sin of this lane's 8 rotation pairs; the second half of a head uses x * cos + partner * sin
-        float cs[8], sn[8];
+        // cos / sin of this lane's four rotation pairs
+        F2 c01, c23, s01, s23, n01, n23;
         {
-            const float* table = cos_sin + static_cast<int64_t>(rotate ? pos : 0) * D + (sub % (LANES / 2)) * 8;
-            const float4 c0 = *reinterpret_cast<const float4*>(table), c1 = *reinterpret_cast<const float4*>(table + 4);
-            const float4 s0 = *reinterpret_cast<const float4*>(table + D / 2), s1 = *reinterpret_cast<const float4*>(table + D / 2 + 4);
-            cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-            sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-            if (!low_half) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) sn[i] = -sn[i];
-            }
+            const float* table = cos_sin + static_cast<int64_t>(rotate ? pos : 0) * D + lo_off;
+            const float4 c = *reinterpret_cast<const float4*>(table), sn = *reinterpret_cast<const float4*>(table + D / 2);
+            c01 = f2_make(c.x, c.y); c23 = f2_make(c.z, c.w);
+            s01 = f2_make(sn.x, sn.y); s23 = f2_make(sn.z, sn.w);
+            n01 = f2_make(-sn.x, -sn.y); n23 = f2_make(-sn.z, -sn.w);
         }
         // the block's next row: requested now, used in the next iteration
         const int64_t next = row + gridDim.x;
-        Pack nxt[PIECES];
+        Piece nxt[PIECES];
         int pos_next = 0;
         int64_t slot_next = -1;
         if (next < rows) {
             pos_next = positions[next];
             slot_next = slot_mapping[next];
-#pragma unroll
-            for (int u = 0; u < PIECES; ++u) {
-                const int head = first_head + u * STRIDE;
-                nxt[u].v = head < heads ? *reinterpret_cast<const uint4*>(qkv + (next * heads + head) * D + sub * 8) : make_uint4(0u, 0u, 0u, 0u);
-            }
+            request(nxt, next);
         }
 #pragma unroll
         for (int u = 0; u < PIECES; ++u) {
@@ -90,22 +127,36 @@ fused_prologue_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ pos
             const bool valid = head < heads;          // lanes without a head still take part in the shuffles
             const bool is_q = head < hq;
             const bool is_k = !is_q && head < hq + hkv;
-            float x[8];
-            float ss = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { x[i] = ElemTraits<T>::to_float(in[u].e[i]); ss += x[i] * x[i]; }
+            F2 a01 = f2_unpack<T>(in[u].lo.x), a23 = f2_unpack<T>(in[u].lo.y);   // first half
+            F2 b01 = f2_unpack<T>(in[u].hi.x), b23 = f2_unpack<T>(in[u].hi.y);   // second half
+            float ss;
+            {
+                F2 sq = f2_mul(a01, a01);
+                sq = f2_fma(a23, a23, sq);
+                sq = f2_fma(b01, b01, sq);
+                sq = f2_fma(b23, b23, sq);
+                float s0, s1;
+                f2_split(sq, s0, s1);
+                ss = s0 + s1;
+            }
 #pragma unroll
             for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float inv_rms = rsqrtf(ss / static_cast<float>(D) + eps);
-            const Pack& w = is_q ? wq : wk;
-            Pack out;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                x[i] = x[i] * inv_rms * ElemTraits<T>::to_float(w.e[i]);
-                const float partner = __shfl_xor_sync(0xffffffffu, x[i], LANES / 2);
-                // positions outside the table leave the value un-rotated; sn carries the sign of this half
-                const float rot = x[i] * cs[i] - partner * sn[i];
-                out.e[i] = ElemTraits<T>::from_float(rotate ? rot : x[i]);
+            const F2 inv2 = f2_make(inv_rms, inv_rms);
+            const Piece& w = is_q ? wq : wk;
+            a01 = f2_mul(f2_mul(a01, inv2), f2_unpack<T>(w.lo.x));
+            a23 = f2_mul(f2_mul(a23, inv2), f2_unpack<T>(w.lo.y));
+            b01 = f2_mul(f2_mul(b01, inv2), f2_unpack<T>(w.hi.x));
+            b23 = f2_mul(f2_mul(b23, inv2), f2_unpack<T>(w.hi.y));
+            Piece out;
+            if (rotate) {   // first half: x cos - partner sin; second half: x cos + partner sin
+                out.lo.x = f2_pack<T>(f2_fma(a01, c01, f2_mul(b01, n01)));
+                out.lo.y = f2_pack<T>(f2_fma(a23, c23, f2_mul(b23, n23)));
+                out.hi.x = f2_pack<T>(f2_fma(b01, c01, f2_mul(a01, s01)));
+                out.hi.y = f2_pack<T>(f2_fma(b23, c23, f2_mul(a23, s23)));
+            } else {        // positions outside the table leave the value un-rotated
+                out.lo.x = f2_pack<T>(a01); out.lo.y = f2_pack<T>(a23);
+                out.hi.x = f2_pack<T>(b01); out.hi.y = f2_pack<T>(b23);
             }
             if (!valid) continue;
             T* dst;
@@ -115,9 +166,10 @@ fused_prologue_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ pos
                 if (!store_kv) continue;
                 const int kv = is_k ? head - hq : head - hq - hkv;
                 dst = (is_k ? k_cache : v_cache) + (slot * hkv + kv) * D;
-                if (!is_k) out.v = in[u].v;           // v heads: plain copy
+                if (!is_k) out = in[u];               // v heads: plain copy
             }
-            *reinterpret_cast<uint4*>(dst + sub * 8) = out.v;
+            *reinterpret_cast<uint2*>(dst + lo_off) = out.lo;
+            *reinterpret_cast<uint2*>(dst + hi_off) = out.hi;
         }
 #pragma unroll
         for (int u = 0; u < PIECES; ++u) in[u] = nxt[u];
