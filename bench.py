@@ -454,7 +454,7 @@ def main():
     ap.add_argument("--e2e-maxlen", type=int, default=1024, help="e2e workload: longest prompt / output")
     ap.add_argument("--no-graph", action="store_true", help="e2e workload: run decode steps eagerly")
     ap.add_argument("--e2e-kv", default="bf16", choices=["bf16", "int8"], help="e2e workload: KV cache format")
-    ap.add_argument("--e2e-allreduce", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--e2e-allreduce", default="peer", choices=["nccl", "peer"],
                     help="e2e workload, N > 1: all-reduce of the decode steps through NCCL or the peer-memory kernel")
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
                     help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")

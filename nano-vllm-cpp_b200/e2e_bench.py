@@ -1,7 +1,8 @@
 """Output tokens per second of the end-to-end decoder (``bench.py --workload e2e``), one process per GPU.
 
 Requests, scheduling and block tables come from ``e2e_schedule.py``, the decoder from ``e2e_model.py``.  With N
-processes the model is tensor-parallel over N GPUs (KV-head sharding, NCCL all-reduce after o_proj / down_proj).
+processes the model is tensor-parallel over N GPUs (KV-head sharding, all-reduce after o_proj / down_proj: this
+library's peer-memory kernel in the decode steps unless ``allreduce="nccl"``, NCCL in the prefill steps).
 Timed region: from the first prefill step to the last decode step, host scheduling and the per-step host-to-device
 metadata copy included, CUDA events on the compute stream, maximum over ranks.
 """
@@ -18,7 +19,7 @@ RING = 64   # pinned metadata slots in flight
 
 
 def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None, num_seqs=256, len_lo=100, len_hi=1024,
-            seed=0, use_graph=True, kv_dtype="bf16", allreduce="nccl"):
+            seed=0, use_graph=True, kv_dtype="bf16", allreduce="peer"):
     cfg = cfg or DecoderConfig()
     bs = cfg.block_size
     prompts, output_lens = make_requests(num_seqs, cfg.vocab, len_lo, len_hi, seed)
@@ -93,7 +94,10 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
     total_ms, prefill_ms, decode_ms = ev[0].elapsed_time(ev[2]), ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
     eager_launches = nvk.launch_count - launches0
     # kernels of this library per step: prologue + prefill attention per layer in prefill; prologue + split + merge in decode
+    # (+ the quantising store with an int8 cache, + the two all-reduces per layer with the peer-memory kernel)
     our_launches = (len(batches) * cfg.layers * 2 + steps * cfg.layers * 3) + (len(batches) + steps) * cfg.layers * (1 if model.int8 else 0)
+    if comm is not None:   # two fused all-reduce launches per layer in every decode step
+        our_launches += steps * cfg.layers * 2
 
     # ---- attention share of a decode step, on the metadata of a step a quarter into the run ----------------------------
     attn_ms = None
@@ -144,9 +148,10 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
         "config": {"workload": f"end-to-end decoder, {cfg.layers} layers, hidden {cfg.hidden}, {cfg.num_heads}/{cfg.num_kv_heads} heads, "
                                f"head_dim {cfg.head_dim}, FFN {cfg.ffn}, vocab {cfg.vocab}, random-init bf16 weights; {num_seqs} sequences, "
                                f"prompt and output lengths U[{len_lo},{len_hi}], greedy, ignore_eos",
-                   "parallelism": f"tp{world} (KV-head shards, NCCL all-reduce after o_proj / down_proj)",
+                   "parallelism": f"tp{world} (KV-head shards, all-reduce after o_proj / down_proj)",
                    "kv_cache": "int8 with fp16 per-(token, head) scales" if model.int8 else "bf16",
-                   "allreduce": ("decode steps: peer-memory kernel (nvk_tp_allreduce); prefill steps: NCCL" if comm is not None else "NCCL"),
+                   "allreduce": ("decode steps: peer-memory all-reduce fused with the residual add and the RMSNorm "
+                                 "(nvk_tp_allreduce_add_rmsnorm); prefill steps: NCCL" if comm is not None else "NCCL"),
                    "decode": "one captured CUDA graph of %d fixed rows" % num_seqs if graph is not None else "eager",
                    "prefill_batches": len(batches), "decode_steps": steps, "kv_blocks": num_blocks,
                    "l2": "weights (16.4 GB / tp) and KV cache exceed the 126 MB L2"},
