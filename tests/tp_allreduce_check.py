@@ -1,8 +1,8 @@
 """Child program of tests/test_e2e_tp.py (torch.distributed.run, one process per GPU): the peer-memory all-reduce
 against NCCL on the same addends -- repeated eager calls (the launch counter in the flags advances), calls replayed from
 a CUDA graph, a ragged count, the fused all-reduce + residual add + RMSNorm against NCCL + torch, chains of 32 dependent
-launches replayed from a graph (every replay and every rank must end with the same bits), and a timing of all of them
-for the decode-step message (256 x 4096 bf16)."""
+launches replayed from a graph (every replay and every rank must end with the same bits), the fp16 instantiations, and
+a timing of all of them for the decode-step message (256 x 4096 bf16)."""
 import importlib
 import os
 import sys
@@ -162,6 +162,34 @@ def main():
         if rank == 0:
             print(f"fused chain replay {it}: identical to replay 0: {same}", flush=True)
         ok = ok and same
+    # the fp16 instantiations of both kernels, on a second set of peer buffers
+    comm16 = tc.PeerAllReduce(nvk, torch, dist, dev, rank, world, rows * cols, torch.float16)
+    addend16, result16 = comm16.buffers(rows, cols)
+    weight16 = weight.to(torch.float16)
+    residual16 = (0.5 * torch.randn((rows, cols), generator=gen, device=dev)).to(torch.float16)
+    dist.broadcast(residual16, 0)
+    for it in range(3):
+        addend16.copy_(torch.randn((rows, cols), generator=gen, device=dev))
+        want = addend16.clone()
+        dist.all_reduce(want)
+        comm16.all_reduce(rows * cols)
+        torch.cuda.synchronize()
+        err = float((result16.float() - want.float()).abs().max())
+        tol = 0.0 if world == 2 else 4.0 * 2.0 ** -11 * float(want.float().abs().max())
+        want_h = residual16 + want
+        want_x = torch.nn.functional.rms_norm(want_h, (cols,), weight16, 1e-6)
+        h16, x16 = comm16.all_reduce_add_rmsnorm(residual16, weight16, 1e-6, rows, cols)
+        torch.cuda.synchronize()
+        eh = float((h16.float() - want_h.float()).abs().max())
+        ex = float((x16.float() - want_x.float()).abs().max())
+        tol_h = 0.0 if world == 2 else 4.0 * 2.0 ** -11 * float(want_h.float().abs().max())
+        tol_x = 2.0 ** -9 * float(want_x.float().abs().max()) + (0.0 if world == 2 else 0.01)
+        if rank == 0:
+            print(f"fp16 {it}: max |sum - nccl| = {err:.4e} (allowed {tol:.4e}), max |h - ref| = {eh:.4e} (allowed {tol_h:.4e}), "
+                  f"max |x - ref| = {ex:.4e} (allowed {tol_x:.4e})", flush=True)
+        ok = ok and err <= tol and eh <= tol_h and ex <= tol_x
+    ok = ok and comm16.status() == 0
+    comm16.close()
     status = comm.status()
     ok = ok and status == 0
 
