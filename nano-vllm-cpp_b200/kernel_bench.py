@@ -238,13 +238,17 @@ def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
 
 
 def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_lo=512, ctx_hi=16384, prefill_seqs=4,
-                prefill_len=2048, mem_fraction=0.80, hq=HQ, hkv=HKV):
+                prefill_len=2048, mem_fraction=0.80, hq=HQ, hkv=HKV, single_launch=False):
     """Config 4: one continuous-batching step of attention over ``layers`` layer caches -- per layer the store of the
     prefill tokens, the varlen prefill (no prefix), the store of the decode tokens and the paged decode attention,
     all on one stream (the reference never fuses prefill and decode into one launch, src/engine/scheduler.cpp:65-67).
     36 distinct caches of this shape need about 226 GiB, more than one GPU holds, so as many distinct physical
     caches as fit are allocated and the logical layers are mapped onto them round-robin; every physical cache has
-    its own block-table permutation and each is far larger than L2, so the reuse brings no cache hits."""
+    its own block-table permutation and each is far larger than L2, so the reuse brings no cache hits.
+
+    ``single_launch`` runs the same step as ONE store and ONE varlen paged-prefill launch per layer, the decode
+    sequences entering as sequences of one new token whose prefix is their context (the "true mixed step" the
+    reference lists as future work, docs/interview_star.md:54) -- for comparison with the two-kernel step."""
     from . import workloads as wl
     rng = np.random.default_rng(4040)
     ctx = rng.integers(ctx_lo, ctx_hi + 1, size=decode_seqs).astype(np.int32)
@@ -273,8 +277,12 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
         pslots = np.concatenate([pblocks[s, pos // BS].astype(np.int64) * BS + pos % BS for s in range(prefill_seqs)]).astype(np.int32)
         kc = torch.empty((pool, BS, hkv, D), device=dev, dtype=bf).normal_(generator=gen)
         vc = torch.empty((pool, BS, hkv, D), device=dev, dtype=bf).normal_(generator=gen)
+        all_tables = np.zeros((prefill_seqs + decode_seqs, tables.shape[1]), np.int32)
+        all_tables[:prefill_seqs, :pblocks.shape[1]] = pblocks
+        all_tables[prefill_seqs:] = tables
         caches.append({"k": kc, "v": vc, "tables": torch.from_numpy(tables).to(dev), "dslots": torch.from_numpy(dslots).to(dev),
-                       "pslots": torch.from_numpy(pslots).to(dev)})
+                       "pslots": torch.from_numpy(pslots).to(dev), "all_tables": torch.from_numpy(all_tables).to(dev),
+                       "all_slots": torch.from_numpy(np.concatenate([pslots, dslots])).to(dev)})
     total_pq = prefill_seqs * prefill_len
     cu = torch.arange(0, total_pq + 1, prefill_len, dtype=torch.int32, device=dev)
     pq = torch.randn((total_pq, hq, D), generator=gen, device=dev).to(bf)
@@ -290,6 +298,20 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
     max_blocks = caches[0]["tables"].shape[1]
     ws = torch.empty(max(16, nvk.decode_attention_workspace_bytes(decode_seqs, hq, hkv, D, max_blocks, BS)), dtype=torch.uint8, device=dev)
 
+    # the same step as one varlen batch: prefill sequences first, then one-token sequences with their context as prefix
+    q_lens = np.concatenate([np.full(prefill_seqs, prefill_len, np.int64), np.ones(decode_seqs, np.int64)])
+    k_lens = np.concatenate([np.full(prefill_seqs, prefill_len, np.int64), ctx.astype(np.int64)])
+    cu_q_all = torch.from_numpy(np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)).to(dev)
+    cu_k_all = torch.from_numpy(np.concatenate([[0], np.cumsum(k_lens)]).astype(np.int32)).to(dev)
+    aq, ak, av = torch.cat([pq, dq]), torch.cat([pk, dk]), torch.cat([pv, dv])
+    aout = torch.empty_like(aq)
+
+    def step_single():
+        for layer in range(layers):
+            c = caches[layer % phys]
+            nvk.store_kvcache(ak, av, c["k"], c["v"], c["all_slots"])
+            nvk.launch_prefill_attention_paged(aq, cu_q_all, c["k"], c["v"], cu_k_all, c["all_tables"], hkv, D, BS, scale, aout)
+
     def step():
         for layer in range(layers):
             c = caches[layer % phys]
@@ -298,7 +320,7 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
             nvk.store_kvcache(dk, dv, c["k"], c["v"], c["dslots"])
             nvk.launch_decode_attention_paged(dq, c["k"], c["v"], ctx_dev, c["tables"], hkv, D, BS, scale, dout, ws)
 
-    mean_ms, med_ms = _time(torch, step, steps, warmup)
+    mean_ms, med_ms = _time(torch, step_single if single_launch else step, steps, warmup)
     dec_bytes = int(ctx.astype(np.int64).sum()) * 2 * hkv * D * 2 + 2 * decode_seqs * hq * D * 2
     pre_bytes = 2 * total_pq * hq * D * 2 + 2 * total_pq * hkv * D * 2
     store_bytes = 2 * (2 * (total_pq + decode_seqs) * hkv * D * 2)
@@ -313,11 +335,13 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
             "config": {"workload": f"mixed continuous-batching step, Qwen3-8B attention shape: {prefill_seqs} prefill sequences x "
                                    f"{prefill_len} new tokens + {decode_seqs} decode sequences with context U[{ctx_lo},{ctx_hi}], "
                                    f"{layers} layers per step",
+                       "launches": ("one store + one varlen paged-prefill launch per layer (decode sequences as one-token sequences)"
+                                    if single_launch else "per layer: store + dense prefill + store + paged decode (split-K + merge)"),
                        "physical_layer_caches": phys, "bytes_per_layer_cache": bytes_per_layer,
                        "note": "logical layers are mapped round-robin onto the physical caches that fit in HBM",
                        "bytes_per_layer": bytes_layer, "prefill_flops_per_layer": flops_layer,
                        "l2": "each layer cache (GiB) exceeds the 126 MB L2"},
-            "roofline": {"bound": "hbm", "kernel": "decode_split_kernel (dominant; prefill_tc4_kernel second)", "achieved": ach,
+            "roofline": {"bound": "hbm", "kernel": ("prefill_tc5_kernel" if single_launch else "decode_split_kernel (dominant; prefill_tc5_kernel second)"), "achieved": ach,
                          "peak": hbm, "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm,
                          "ideal_ms_per_step": ideal_ms, "frac_of_ideal_time": ideal_ms / mean_ms, "traffic": None},
-            "gpu_launches": steps * layers * 5}
+            "gpu_launches": steps * layers * (2 if single_launch else 5)}
