@@ -106,8 +106,7 @@ def physical_gpu_index(local_rank):
 
 def make_workload(torch, dev, seed):
     """Builds the decode configuration on the device (values drawn on the GPU from a seeded generator)."""
-    entry.load_package()
-    wl = __import__("importlib").import_module(entry.PKG_NAME + ".workloads")
+    from benchmarks import workloads as wl
     rng = np.random.default_rng(seed)
     ctx = rng.integers(CFG["ctx_lo"], CFG["ctx_hi"] + 1, size=CFG["batch"]).astype(np.int32)
     tables, pool = wl.build_block_tables(rng, ctx, CFG["block_size"])
@@ -490,9 +489,7 @@ def main():
             dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
         nvk = entry.load_package()
         nvk.lib()
-        importlib = __import__("importlib")
-        eb = importlib.import_module(entry.PKG_NAME + ".e2e_bench")
-        em = importlib.import_module(entry.PKG_NAME + ".e2e_model")
+        from benchmarks import e2e_bench as eb, e2e_model as em
         sampler = ClockSampler(physical_gpu_index(local_rank)) if rank == 0 else None
         if sampler:
             sampler.start()
@@ -515,7 +512,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
         nvk = entry.load_package()
         nvk.lib()
-        kb = __import__("importlib").import_module(entry.PKG_NAME + ".kernel_bench")
+        from benchmarks import kernel_bench as kb
         dev = torch.device(f"cuda:{local_rank}")
         if CFG["num_kv_heads"] % world:
             raise SystemExit("--gpus must divide the number of KV heads")
@@ -540,7 +537,7 @@ def main():
         torch.cuda.set_device(local_rank)
         nvk = entry.load_package()
         nvk.lib()
-        kb = __import__("importlib").import_module(entry.PKG_NAME + ".kernel_bench")
+        from benchmarks import kernel_bench as kb
         dev = torch.device(f"cuda:{local_rank}")
         steps = min(args.steps, 50)
         if args.workload == "prefill":

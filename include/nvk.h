@@ -16,6 +16,11 @@
  *
  * dtype codes follow the reference's ScalarType order (include/utils/tensor.h:21-28).
  * The stream argument is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *
+ * Index tensors (slot_mapping, context_lens, block_tables, cu_seqlens_q, cu_seqlens_k) are passed as
+ * `const void*` plus a dtype code, NVK_I32 or NVK_I64, one code per tensor: the reference's kernels take
+ * either width for each of them independently (src/kernels/attention.cu:644-660, :708-735,
+ * src/kernels/kvcache.cu:160).
  */
 #ifndef NVK_H
 #define NVK_H
@@ -67,8 +72,12 @@ int nvk_store_kvcache(const void* key, const void* value, void* k_cache, void* v
  * un-rotated), q -> q_out [rows, Hq, D], k and v -> cache row slot_mapping[row] when that slot
  * is >= 0 (and < cache_rows: the reference checks only the lower bound, writing out of bounds
  * otherwise).  dtype in {F16, BF16}; positions and slot_mapping are int32.  head_dim in {64, 128,
- * 256}; num_q_heads + 2 * num_kv_heads <= 16384 / head_dim; every tensor (the table included) starts
- * on a 16-byte boundary.
+ * 256}; every tensor (the table included) starts on a 16-byte boundary.
+ * Two forms serve the unfused route of the reference's TransformerAttention::forward
+ * (src/models/transformer.cpp:144-153: split_qkv, optional q / k norm, rotary) with the same kernel:
+ *   slot_mapping == NULL                   k and v of row r go to row r of k_cache / v_cache, which are then plain
+ *                                          [rows, Hkv, D] tensors (cache_rows = rows);
+ *   q_norm_weight == k_norm_weight == NULL the RMSNorm is skipped (models without q / k norm).
  */
 int nvk_fused_split_norm_rope_store(const void* qkv, const int32_t* positions,
                                     const void* q_norm_weight, const void* k_norm_weight,
@@ -91,18 +100,20 @@ size_t nvk_decode_attention_workspace_bytes(int64_t batch, int num_heads, int nu
  * (include/kernels/flash_attn.h:39-50).
  *   query, output   [batch, num_heads, head_dim]
  *   k_cache,v_cache [num_cache_blocks, block_size, num_kv_heads, head_dim]
- *   context_lens    [batch] int32 (includes the token being generated)
- *   block_tables    [batch, max_blocks] int32, zero padded
+ *   context_lens    [batch] int32 / int64 (includes the token being generated)
+ *   block_tables    [batch, max_blocks] int32 / int64, zero padded
  *   out[b,h] = softmax(scale * q[b,h] . K[b, h*Hkv/Hq]^T) V over context_lens[b] keys; key k of
  *   sequence b lives in cache row block_tables[b][k / block_size] * block_size + k % block_size.
- *   context_lens[b] <= 0 gives a zero row.
+ *   context_lens[b] <= 0 gives a zero row; a value beyond max_blocks * block_size (more keys than the table row
+ *   can address) is treated as max_blocks * block_size.
  * workspace may be NULL (then every sequence is processed by one thread block per KV head);
  * otherwise it must hold nvk_decode_attention_workspace_bytes(...) bytes, 16-byte aligned.
  * dtype F16/BF16 with head_dim 128 take the tensor-core path; other shapes and F32 take the
  * general SIMT path.
  */
 int nvk_decode_attention_paged(const void* query, const void* k_cache, const void* v_cache,
-                               const int32_t* context_lens, const int32_t* block_tables,
+                               const void* context_lens, int context_lens_dtype,
+                               const void* block_tables, int block_tables_dtype,
                                int64_t batch, int64_t max_blocks, int64_t num_cache_blocks,
                                int num_heads, int num_kv_heads, int head_dim, int block_size,
                                float scale, void* output, int dtype, void* workspace,
@@ -125,8 +136,9 @@ int nvk_store_kvcache_int8(const void* key, const void* value, void* k_cache, vo
                            void* v_scale, const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads,
                            int head_dim, int64_t cache_rows, int dtype, void* stream);
 int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, const void* v_cache,
-                                    const void* k_scale, const void* v_scale, const int32_t* context_lens,
-                                    const int32_t* block_tables, int64_t batch, int64_t max_blocks,
+                                    const void* k_scale, const void* v_scale, const void* context_lens,
+                                    int context_lens_dtype, const void* block_tables, int block_tables_dtype,
+                                    int64_t batch, int64_t max_blocks,
                                     int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim,
                                     int block_size, float scale, void* output, int dtype, void* workspace,
                                     size_t workspace_bytes, void* stream);
@@ -150,8 +162,10 @@ int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, cons
  *     The kernels overwrite every entry they later read, so no clearing is needed, but two calls
  *     whose kernels overlap on the GPU (different streams) race on it: serialise them.
  */
+size_t nvk_decode_attention_static_scratch_bytes(void);   /* the limit above, for callers that size their batches by it */
 int nvk_decode_attention_paged_static(const void* query, const void* k_cache, const void* v_cache,
-                                      const int32_t* context_lens, const int32_t* block_tables,
+                                      const void* context_lens, int context_lens_dtype,
+                                      const void* block_tables, int block_tables_dtype,
                                       int64_t batch, int64_t max_blocks, int64_t num_cache_blocks,
                                       int num_heads, int num_kv_heads, int head_dim, int block_size,
                                       float scale, void* output, int dtype, void* stream);
@@ -193,8 +207,8 @@ int nvk_tp_allreduce_add_rmsnorm(const void* const* in_ptrs, void* const* out_pt
  *   query, output  [total_q, num_heads, head_dim]
  *   dense keys:    key, value [total_k, num_kv_heads, head_dim], block_tables == NULL
  *   paged keys:    k_cache, v_cache [num_cache_blocks, block_size, num_kv_heads, head_dim] and
- *                  block_tables [num_seqs, max_blocks] int32; key/value ignored
- *   cu_seqlens_q, cu_seqlens_k  [num_seqs + 1] int32; both NULL (dense only) = one sequence
+ *                  block_tables [num_seqs, max_blocks] int32 / int64; key/value ignored
+ *   cu_seqlens_q, cu_seqlens_k  [num_seqs + 1] int32 / int64; both NULL (dense only) = one sequence
  * Causal mask, bottom-right aligned: query i of a sequence sees keys
  * 0 .. (k_len - q_len) + i  (attention.cu:147, :244); rows with no visible key are zero.
  * max_seqlen_q may be 0 when unknown.
@@ -203,11 +217,18 @@ int nvk_tp_allreduce_add_rmsnorm(const void* const* in_ptrs, void* const* out_pt
  * last block of a launch re-arms its counter.  So up to 64 prefill launches may be in flight on one device at a
  * time (any streams); a CUDA graph that captured the call keeps the counter it was given, and graphs replayed
  * concurrently on one device must hold different ones (capture them back to back and they do).
+ *
+ * Every wait inside the tensor-core kernels is bounded (about two seconds).  A block whose wait runs out stops, leaves
+ * its output rows unwritten and records which wait it was in a per-device error word; the launch itself still
+ * completes.  nvk_prefill_status synchronises `stream`, copies that word to *status (0 = every launch since the last
+ * call completed normally) and clears it.  The C++ layer turns a non-zero word into std::runtime_error.
  */
+int nvk_prefill_status(void* stream, int* status);
 int nvk_prefill_attention_varlen(const void* query, const void* key, const void* value,
                                  const void* k_cache, const void* v_cache,
-                                 const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                 const int32_t* block_tables, int64_t num_seqs, int64_t total_q,
+                                 const void* cu_seqlens_q, int cu_seqlens_q_dtype,
+                                 const void* cu_seqlens_k, int cu_seqlens_k_dtype,
+                                 const void* block_tables, int block_tables_dtype, int64_t num_seqs, int64_t total_q,
                                  int64_t total_k, int64_t max_blocks, int64_t num_cache_blocks,
                                  int max_seqlen_q, int num_heads, int num_kv_heads, int head_dim,
                                  int block_size, float scale, void* output, int dtype,

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "nvk_prefill_attention_varlen", "nvk_decode_attention_paged_static",
     "nvk_store_kvcache_int8", "nvk_decode_attention_paged_int8",
     "nvk_tp_allreduce_flag_bytes", "nvk_tp_allreduce", "nvk_tp_allreduce_status", "nvk_tp_allreduce_add_rmsnorm",
+    "nvk_prefill_status", "nvk_decode_attention_static_scratch_bytes",
 )
 
 _lib = None
@@ -52,6 +53,7 @@ def lib() -> ctypes.CDLL:
         L.nvk_decode_attention_workspace_bytes.restype = ctypes.c_size_t
         L.nvk_decode_attention_workspace_bytes.argtypes = [
             ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int]
+        L.nvk_decode_attention_static_scratch_bytes.restype = ctypes.c_size_t
         _lib = L
     return _lib
 
@@ -78,6 +80,16 @@ def _ptr(t):
 def _stream():
     import torch
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _index(name, t):
+    """(pointer, dtype code) of an index tensor; int32 and int64 are accepted, as by the reference's kernels."""
+    if t is None:
+        return ctypes.c_void_p(0), ctypes.c_int(I32)
+    import torch
+    if t.dtype not in (torch.int32, torch.int64):
+        raise ValueError(f"{name} must be int32 or int64")
+    return _ptr(t), ctypes.c_int(_dtype_code(t))
 
 
 def _require_cuda(name, t):
@@ -115,12 +127,16 @@ def store_kvcache(key, value, k_cache, v_cache, slot_mapping) -> None:
 def fused_split_norm_rope_store(qkv, positions, q_norm_weight, k_norm_weight, norm_eps, cos_sin_cache,
                                 slot_mapping, k_cache, v_cache, num_q_heads, num_kv_heads, head_dim,
                                 q_out) -> None:
-    """``fused_split_norm_rope_store`` (include/kernels/split_qkv.h:22-33)."""
+    """``fused_split_norm_rope_store`` (include/kernels/split_qkv.h:22-33).  ``slot_mapping=None`` writes k / v of
+    row r to row r of ``k_cache`` / ``v_cache`` (plain [rows, Hkv, D] tensors); both norm weights ``None`` skips the
+    RMSNorm -- the two forms that serve the reference's unfused route (split_qkv, optional norm, rotary)."""
     global launch_count
-    for n, t in (("qkv", qkv), ("positions", positions), ("q_norm_weight", q_norm_weight),
-                 ("k_norm_weight", k_norm_weight), ("cos_sin_cache", cos_sin_cache),
-                 ("slot_mapping", slot_mapping), ("k_cache", k_cache), ("v_cache", v_cache), ("q_out", q_out)):
+    for n, t in (("qkv", qkv), ("positions", positions), ("cos_sin_cache", cos_sin_cache),
+                 ("k_cache", k_cache), ("v_cache", v_cache), ("q_out", q_out)):
         _require_cuda(n, t)
+    for n, t in (("q_norm_weight", q_norm_weight), ("k_norm_weight", k_norm_weight), ("slot_mapping", slot_mapping)):
+        if t is not None:
+            _require_cuda(n, t)
     row = num_kv_heads * head_dim
     _check(lib().nvk_fused_split_norm_rope_store(
         _ptr(qkv), _ptr(positions), _ptr(q_norm_weight), _ptr(k_norm_weight), ctypes.c_float(norm_eps),
@@ -147,13 +163,11 @@ def launch_decode_attention_paged(query, k_cache, v_cache, context_lens, block_t
     for n, t in (("query", query), ("k_cache", k_cache), ("v_cache", v_cache),
                  ("context_lens", context_lens), ("block_tables", block_tables), ("output", output)):
         _require_cuda(n, t)
-    if context_lens.dtype.itemsize != 4 or block_tables.dtype.itemsize != 4:
-        raise ValueError("context_lens and block_tables must be int32")
     batch, num_heads = query.shape[0], query.shape[1]
     num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
     _check(lib().nvk_decode_attention_paged(
-        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(context_lens), _ptr(block_tables),
-        ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
+        _ptr(query), _ptr(k_cache), _ptr(v_cache), *_index("context_lens", context_lens),
+        *_index("block_tables", block_tables), ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
         ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
         ctypes.c_int(block_size), ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)),
         _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size() if workspace is not None else 0),
@@ -171,13 +185,11 @@ def launch_decode_attention_paged_static(query, k_cache, v_cache, context_lens, 
     for n, t in (("query", query), ("k_cache", k_cache), ("v_cache", v_cache),
                  ("context_lens", context_lens), ("block_tables", block_tables), ("output", output)):
         _require_cuda(n, t)
-    if context_lens.dtype.itemsize != 4 or block_tables.dtype.itemsize != 4:
-        raise ValueError("context_lens and block_tables must be int32")
     batch, num_heads = query.shape[0], query.shape[1]
     num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
     _check(lib().nvk_decode_attention_paged_static(
-        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(context_lens), _ptr(block_tables),
-        ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
+        _ptr(query), _ptr(k_cache), _ptr(v_cache), *_index("context_lens", context_lens),
+        *_index("block_tables", block_tables), ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
         ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
         ctypes.c_int(block_size), ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)),
         _stream()))
@@ -215,13 +227,11 @@ def launch_decode_attention_paged_int8(query, k_cache, v_cache, k_scale, v_scale
     for n, t in (("query", query), ("k_cache", k_cache), ("v_cache", v_cache), ("k_scale", k_scale), ("v_scale", v_scale),
                  ("context_lens", context_lens), ("block_tables", block_tables), ("output", output)):
         _require_cuda(n, t)
-    if context_lens.dtype.itemsize != 4 or block_tables.dtype.itemsize != 4:
-        raise ValueError("context_lens and block_tables must be int32")
     batch, num_heads = query.shape[0], query.shape[1]
     num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
     _check(lib().nvk_decode_attention_paged_int8(
-        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(context_lens), _ptr(block_tables),
-        ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
+        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), *_index("context_lens", context_lens),
+        *_index("block_tables", block_tables), ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
         ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim), ctypes.c_int(block_size),
         ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)), _ptr(workspace),
         ctypes.c_size_t(workspace.numel() * workspace.element_size() if workspace is not None else 0), _stream()))
@@ -238,12 +248,9 @@ def _prefill(query, key, value, k_cache, v_cache, cu_q, cu_k, block_tables, num_
     total_k = key.shape[0] if key is not None else 0
     max_blocks = block_tables.shape[1] if block_tables is not None else 0
     ncb = (k_cache.numel() // (block_size * num_kv_heads * head_dim)) if k_cache is not None else 0
-    for t in (cu_q, cu_k, block_tables):
-        if t is not None and t.dtype.itemsize != 4:
-            raise ValueError("cu_seqlens and block_tables must be int32")
     _check(lib().nvk_prefill_attention_varlen(
-        _ptr(query), _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(cu_q), _ptr(cu_k),
-        _ptr(block_tables), ctypes.c_int64(num_seqs), ctypes.c_int64(query.shape[0]), ctypes.c_int64(total_k),
+        _ptr(query), _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), *_index("cu_seqlens_q", cu_q),
+        *_index("cu_seqlens_k", cu_k), *_index("block_tables", block_tables), ctypes.c_int64(num_seqs), ctypes.c_int64(query.shape[0]), ctypes.c_int64(total_k),
         ctypes.c_int64(max_blocks), ctypes.c_int64(ncb), ctypes.c_int(max_seqlen_q),
         ctypes.c_int(query.shape[1]), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
         ctypes.c_int(block_size), ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)),
@@ -270,3 +277,15 @@ def launch_prefill_attention_paged(query, cu_seqlens_q, k_cache, v_cache, cu_seq
     _require_cuda("block_tables", block_tables)
     _prefill(query, None, None, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables, num_kv_heads,
              head_dim, block_size, scale, output)
+
+
+def prefill_status() -> int:
+    """Reads and clears the error word of the tensor-core prefill kernels on the current device (synchronises the
+    current stream): 0 = every launch since the last call completed normally."""
+    out = ctypes.c_int(0)
+    _check(lib().nvk_prefill_status(_stream(), ctypes.byref(out)))
+    return int(out.value)
+
+
+def decode_attention_static_scratch_bytes() -> int:
+    return int(lib().nvk_decode_attention_static_scratch_bytes())

@@ -21,9 +21,9 @@ constexpr int kKeysPerTrip = 4;
 
 struct RowwiseParams {
     const void* q; const void* k; const void* v; void* out;
-    const int32_t* cu_q; const int32_t* cu_k;      // prefill (may be null: one sequence)
-    const int32_t* context_lens;                   // decode
-    const int32_t* block_tables;                   // null = dense keys
+    IndexArray cu_q, cu_k;                         // prefill (may be null: one sequence)
+    IndexArray context_lens;                       // decode
+    IndexArray block_tables;                       // null = dense keys
     int64_t num_rows, num_seqs, total_k, max_blocks, cache_rows;
     int num_heads, num_kv_heads, head_dim, block_size;
     float scale;
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_rowwise_kernel(Rowwi
     }
     const T* kbase = static_cast<const T*>(p.k);
     const T* vbase = static_cast<const T*>(p.v);
-    const int32_t* table = p.block_tables ? p.block_tables + seq * p.max_blocks : nullptr;
+    const IndexArray table = p.block_tables ? p.block_tables + seq * p.max_blocks : IndexArray();
     const int64_t row_stride = static_cast<int64_t>(p.num_kv_heads) * p.head_dim;
     const int64_t head_off = static_cast<int64_t>(kv_head) * p.head_dim;
 

@@ -22,6 +22,7 @@
 //     shared-memory round trip); online softmax in the exp2 domain with warp shuffles.
 #include "nvk_internal.cuh"
 
+#include <atomic>
 #include <cmath>
 
 #include <cuda_fp16.h>
@@ -43,12 +44,20 @@ constexpr int kSmemBytes = kWarps * kStages * kStageBytes;  // 96 KiB -> two blo
 
 struct DecodeParams {
     const void* q; const void* k_cache; const void* v_cache;
-    const int32_t* context_lens; const int32_t* block_tables;
+    IndexArray context_lens; IndexArray block_tables;
     void* out; float* ws_o; float* ws_lse;
     int64_t max_blocks, num_cache_blocks;
     int num_heads, num_kv_heads, group, block_size, chunk_tokens, num_splits;
     float scale_log2;
 };
+
+// context_lens[b], limited to what the block table can address (max_blocks * block_size): a longer value would make
+// the split kernels read block_tables past the row and the merge kernel read partial results of the next row.
+__device__ __forceinline__ int clamped_context(const DecodeParams& p, int64_t b) {
+    const int64_t ctx = p.context_lens[b];
+    const int64_t cap = p.max_blocks * p.block_size;
+    return static_cast<int>(ctx < cap ? ctx : cap);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeParams p) {
@@ -62,7 +71,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeP
     const int g = lane >> 2, t = lane & 3;
     const int G = p.group;
 
-    const int ctx = p.context_lens[b];
+    const int ctx = clamped_context(p, b);
     const int t0 = split * p.chunk_tokens;
     T* out = static_cast<T*>(p.out);
     if (ctx <= 0) {
@@ -80,8 +89,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeP
     const int blk0 = t0 / p.block_size;
     const int nblk = (t1 - 1) / p.block_size - blk0 + 1;
     for (int i = tid; i < nblk; i += kThreads) {
-        const int id = p.block_tables[b * p.max_blocks + blk0 + i];
-        s_blocks[i] = (id >= 0 && id < p.num_cache_blocks) ? id : -1;
+        const int64_t id = p.block_tables[b * p.max_blocks + blk0 + i];
+        s_blocks[i] = (id >= 0 && id < p.num_cache_blocks) ? static_cast<int>(id) : -1;
     }
     __syncthreads();
 
@@ -242,7 +251,7 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p,
     const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
     if (row >= num_rows) return;
     const int lane = threadIdx.x & 31;
-    const int ctx = p.context_lens[row / p.num_heads];
+    const int ctx = clamped_context(p, row / p.num_heads);
     const int live = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
     if (ctx <= 0 || live <= 1) return;  // already final
     const float* lse = p.ws_lse + row * p.num_splits;
@@ -291,10 +300,7 @@ constexpr int kRowBytesI8 = kHeadDim;                      // one head row of in
 constexpr int kTileBytesI8 = kTileTokens * kRowBytesI8;    // 2 KiB
 constexpr int kScaleBytesI8 = 2 * kTileTokens * 4;         // one 32-bit word per (K | V, token): the word that holds its fp16 scale
 constexpr int kStageBytesI8 = 2 * kTileBytesI8 + kScaleBytesI8;   // K + V + scales
-#ifndef NVK_I8_STAGES
-#define NVK_I8_STAGES 4
-#endif
-constexpr int kStagesI8 = NVK_I8_STAGES;                   // tiles in flight per warp: kStagesI8 - 1
+constexpr int kStagesI8 = 4;                               // tiles in flight per warp: kStagesI8 - 1
 constexpr int kWarpBytesI8 = kStagesI8 * kStageBytesI8;    // 16.5 KiB
 constexpr int kSmemBytesI8 = kWarps * kWarpBytesI8;        // 66 KiB -> three blocks per SM
 constexpr float kI8Offset = 1152.0f;                       // 1024 (exponent glue) + 128 (sign flip)
@@ -326,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
     const int g = lane >> 2, t = lane & 3;
     const int G = p.group;
 
-    const int ctx = p.context_lens[b];
+    const int ctx = clamped_context(p, b);
     const int t0 = split * p.chunk_tokens;
     T* out = static_cast<T*>(p.out);
     if (ctx <= 0) {
@@ -343,8 +349,8 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
     const int blk0 = t0 / p.block_size;
     const int nblk = (t1 - 1) / p.block_size - blk0 + 1;
     for (int i = tid; i < nblk; i += kThreads) {
-        const int id = p.block_tables[b * p.max_blocks + blk0 + i];
-        s_blocks[i] = (id >= 0 && id < p.num_cache_blocks) ? id : -1;
+        const int64_t id = p.block_tables[b * p.max_blocks + blk0 + i];
+        s_blocks[i] = (id >= 0 && id < p.num_cache_blocks) ? static_cast<int>(id) : -1;
     }
     __syncthreads();
 
@@ -731,8 +737,7 @@ constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB: batch 256 x 32 hea
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {};
-bool g_scratch_ready[kMaxDevices] = {};
+std::atomic<void*> g_scratch_addr[kMaxDevices];   // null until the first call on that device (static storage: zeroed)
 
 // Resolves the device address of g_static_scratch for the current device (once per device).
 // In host code the symbol's name is only a handle; the kernels need the address returned here.
@@ -742,23 +747,25 @@ int static_scratch_for_current_device(void** out) {
     if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "decode attention (static scratch): cudaGetDevice: %s", cudaGetErrorString(e));
     if (device < 0 || device >= kMaxDevices)
         return fail(NVK_ERR_UNSUPPORTED, "decode attention (static scratch): device index %d not supported", device);
-    if (!g_scratch_ready[device]) {
-        void* ptr = nullptr;
+    void* ptr = g_scratch_addr[device].load(std::memory_order_acquire);
+    if (ptr == nullptr) {   // two threads racing here both look the same address up; either store is fine
         e = cudaGetSymbolAddress(&ptr, g_static_scratch);
         if (e != cudaSuccess || ptr == nullptr)
             return fail(NVK_ERR_CUDA, "decode attention (static scratch): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        g_scratch_addr[device] = ptr;
-        g_scratch_ready[device] = true;
+        g_scratch_addr[device].store(ptr, std::memory_order_release);
     }
-    *out = g_scratch_addr[device];
+    *out = ptr;
     return NVK_OK;
 }
 
 }  // namespace
 }  // namespace nvk
 
+extern "C" size_t nvk_decode_attention_static_scratch_bytes(void) { return nvk::kStaticScratchBytes; }
+
 extern "C" int nvk_decode_attention_paged_static(const void* query, const void* k_cache, const void* v_cache,
-                                                 const int32_t* context_lens, const int32_t* block_tables,
+                                                 const void* context_lens, int context_lens_dtype,
+                                                 const void* block_tables, int block_tables_dtype,
                                                  int64_t batch, int64_t max_blocks, int64_t num_cache_blocks,
                                                  int num_heads, int num_kv_heads, int head_dim, int block_size,
                                                  float scale, void* output, int dtype, void* stream) {
@@ -774,7 +781,7 @@ extern "C" int nvk_decode_attention_paged_static(const void* query, const void* 
     if (rc != NVK_OK) return rc;
     // The partials of a split are fully written before the merge kernel reads them, and only live
     // splits are read, so nothing in the array has to start at zero.
-    return nvk_decode_attention_paged(query, k_cache, v_cache, context_lens, block_tables, batch, max_blocks,
-                                      num_cache_blocks, num_heads, num_kv_heads, head_dim, block_size, scale, output,
+    return nvk_decode_attention_paged(query, k_cache, v_cache, context_lens, context_lens_dtype, block_tables,
+                                      block_tables_dtype, batch, max_blocks, num_cache_blocks, num_heads, num_kv_heads, head_dim, block_size, scale, output,
                                       dtype, scratch, kStaticScratchBytes, stream);
 }

@@ -3,24 +3,32 @@
 //
 // Replaces fused_split_norm_rope_store_kernel (src/kernels/split_qkv.cu:62-154 of the reference:
 // a 128-thread block per (row, head), one element per thread, a block reduction and a
-// shared-memory exchange per head).  Here an 8-warp block owns whole ROWS: position, slot, the row
-// of the cos/sin table and the norm weights are fetched once per row instead of once per head.
-// A head vector is spread over D/8 lanes; a lane holds four whole rotation pairs (d, d + D/2): elements
-// [4s, 4s+4) of both halves of the head (two 8-byte loads and stores), so RoPE needs no exchange and a
-// warp works on 32 / (D/8) heads at a time.  The sum of squares is a shuffle reduction inside the lane
-// group; there is no shared memory and no barrier.  Arithmetic runs on packed fp32 pairs (mul / fma
-// .f32x2): the kernel was issue-bound, not byte-bound, with scalar arithmetic and a shuffle per element.
-// The grid is persistent (about two blocks per SM) and software-pipelined over rows: the pieces,
-// position and slot of the block's next row are requested before the current row is computed.
-// HBM-bound in the limit of many rows (rows * (Hq + 2 Hkv) * D elements read, the same number
-// written); at decode batch sizes it is latency-bound.
+// shared-memory exchange per head).
+//
+// The op is a streaming copy with a little arithmetic: (Hq + 2 Hkv) * D elements read per row, the same
+// number written, one row of the fp32 cos / sin table per row.  It is HBM-bound when there are many rows
+// and launch / latency-bound at decode batch sizes, so the kernel is built for many light warps:
+//   * a head vector is spread over D / 16 lanes; a lane holds eight whole rotation pairs (d, d + D/2):
+//     elements [8s, 8s + 8) of both halves of the head, i.e. two 16-byte loads and two 16-byte stores, so
+//     RoPE needs no exchange and a warp works on 32 / (D/16) heads at a time;
+//   * a warp takes a unit = (row, kSteps consecutive head groups): all of a unit's loads are issued before
+//     any arithmetic; position, slot, the table row and the norm weights are fetched once per unit (the table
+//     row and the weights hit L1 / L2);
+//   * the sum of squares is a shuffle reduction inside the lane group; no shared memory, no barrier;
+//   * arithmetic on packed fp32 pairs (mul / fma .f32x2);
+//   * about 64 registers per thread, so four 256-thread blocks (32 warps) are resident per SM -- the first
+//     version of this kernel kept three heads and a prefetched row per thread in 122 registers and was
+//     latency-bound at 16 warps per SM.
+// The launch carries the programmatic-stream-serialization attribute: the kernel waits for its predecessor
+// in the stream with griddepcontrol.wait as its first action, so its launch latency overlaps the predecessor's
+// tail, and it releases its own dependents at once (they wait the same way).
 #include "nvk_internal.cuh"
 
 namespace nvk {
 namespace {
 
 constexpr int kWarpsPerBlock = 8;
-constexpr int kMaxPieces = 8;
+constexpr int kSteps = 2;   // head groups per unit
 
 // Packed fp32 pairs (one 64-bit register pair per two values; Blackwell executes f32x2 mul / fma at one issue slot).
 using F2 = unsigned long long;
@@ -54,127 +62,129 @@ template <typename T> __device__ __forceinline__ uint32_t f2_pack(F2 v) {
     return ElemTraits<T>::pack2(lo, hi);
 }
 
-template <typename T, int LANES, int PIECES>   // LANES = D / 8 lanes per head: 8, 16 or 32
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, PIECES <= 3 ? 2 : 1)
-fused_prologue_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ positions,
-                      const T* __restrict__ q_weight, const T* __restrict__ k_weight, float eps,
-                      const float* __restrict__ cos_sin, int max_positions,
-                      const int32_t* __restrict__ slot_mapping, T* __restrict__ k_cache,
-                      T* __restrict__ v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv,
-                      T* __restrict__ q_out) {
-    constexpr int D = LANES * 8;
+// Streaming 16-byte load of the packed rows (read once: no L1 allocation).
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+struct PrologueParams {
+    const void* qkv; const int32_t* positions; const void* q_weight; const void* k_weight;
+    const float* cos_sin; const int32_t* slot_mapping;
+    void* k_cache; void* v_cache; void* q_out;
+    int64_t cache_rows, rows;
+    int max_positions, hq, hkv;
+    float eps;
+};
+
+template <typename T, int D>   // D = head_dim: 64, 128 or 256
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) fused_prologue_kernel(const PrologueParams p) {
+    constexpr int LANES = D / 16;                           // lanes per head
     constexpr int GROUPS = 32 / LANES;                      // heads a warp handles at once
-    constexpr int STRIDE = kWarpsPerBlock * GROUPS;         // heads the block handles at once
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");    // the packed rows come from the kernel before this one
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane % LANES, group = lane / LANES;
-    const int heads = hq + 2 * hkv;                         // <= STRIDE * PIECES (the launcher picks PIECES)
-    const int first_head = warp * GROUPS + group;
-    // this lane's 8 elements of a head: [sub*4, sub*4+4) of the first half and the same of the second half, i.e. four
+    const int heads = p.hq + 2 * p.hkv;
+    const int units_per_row = (heads + GROUPS * kSteps - 1) / (GROUPS * kSteps);
+    const int64_t units = p.rows * units_per_row;
+    // this lane's 16 elements of a head: [8 sub, 8 sub + 8) of the first half and the same of the second half, i.e. eight
     // whole rotation pairs (d, d + D/2)
-    const int lo_off = sub * 4, hi_off = D / 2 + sub * 4;
+    const int lo_off = sub * 8, hi_off = D / 2 + sub * 8;
+    const T* qkv = static_cast<const T*>(p.qkv);
+    const bool normed = p.q_weight != nullptr;
 
-    struct Piece { uint2 lo, hi; };
-    Piece wq, wk;                                           // norm weights of this lane's elements, kept packed
-    wq.lo = *reinterpret_cast<const uint2*>(q_weight + lo_off); wq.hi = *reinterpret_cast<const uint2*>(q_weight + hi_off);
-    wk.lo = *reinterpret_cast<const uint2*>(k_weight + lo_off); wk.hi = *reinterpret_cast<const uint2*>(k_weight + hi_off);
-
-    int64_t row = blockIdx.x;
-    if (row >= rows) return;
-    Piece in[PIECES];
-    int pos = positions[row];
-    int64_t slot = slot_mapping[row];
-    auto request = [&](Piece (&dst)[PIECES], int64_t r) {
+    for (int64_t u = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp; u < units;
+         u += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+        const int64_t row = u / units_per_row;
+        const int head0 = static_cast<int>(u - row * units_per_row) * (GROUPS * kSteps) + group;
+        uint4 lo[kSteps], hi[kSteps];
 #pragma unroll
-        for (int u = 0; u < PIECES; ++u) {
-            const int head = first_head + u * STRIDE;
+        for (int s = 0; s < kSteps; ++s) {                  // every load of the unit first
+            const int head = head0 + s * GROUPS;
             if (head < heads) {
-                const T* src = qkv + (r * heads + head) * D;
-                dst[u].lo = *reinterpret_cast<const uint2*>(src + lo_off);
-                dst[u].hi = *reinterpret_cast<const uint2*>(src + hi_off);
+                const T* src = qkv + (row * heads + head) * D;
+                lo[s] = ld_stream16(src + lo_off);
+                hi[s] = ld_stream16(src + hi_off);
             } else {
-                dst[u].lo = make_uint2(0u, 0u);
-                dst[u].hi = make_uint2(0u, 0u);
+                lo[s] = make_uint4(0u, 0u, 0u, 0u);
+                hi[s] = make_uint4(0u, 0u, 0u, 0u);
             }
         }
-    };
-    request(in, row);
-    for (; row < rows; row += gridDim.x) {
-        const bool rotate = pos >= 0 && pos < max_positions;
-        const bool store_kv = slot >= 0 && slot < cache_rows;
-        // cos / sin of this lane's four rotation pairs
-        F2 c01, c23, s01, s23, n01, n23;
-        {
-            const float* table = cos_sin + static_cast<int64_t>(rotate ? pos : 0) * D + lo_off;
-            const float4 c = *reinterpret_cast<const float4*>(table), sn = *reinterpret_cast<const float4*>(table + D / 2);
-            c01 = f2_make(c.x, c.y); c23 = f2_make(c.z, c.w);
-            s01 = f2_make(sn.x, sn.y); s23 = f2_make(sn.z, sn.w);
-            n01 = f2_make(-sn.x, -sn.y); n23 = f2_make(-sn.z, -sn.w);
-        }
-        // the block's next row: requested now, used in the next iteration
-        const int64_t next = row + gridDim.x;
-        Piece nxt[PIECES];
-        int pos_next = 0;
-        int64_t slot_next = -1;
-        if (next < rows) {
-            pos_next = positions[next];
-            slot_next = slot_mapping[next];
-            request(nxt, next);
-        }
+        const int pos = __ldg(p.positions + row);
+        const int64_t slot = p.slot_mapping != nullptr ? static_cast<int64_t>(__ldg(p.slot_mapping + row)) : row;
+        const bool rotate = pos >= 0 && pos < p.max_positions;
+        const bool store_kv = slot >= 0 && slot < p.cache_rows;
+        const float* table = p.cos_sin + static_cast<int64_t>(rotate ? pos : 0) * D + lo_off;
 #pragma unroll
-        for (int u = 0; u < PIECES; ++u) {
-            const int head = first_head + u * STRIDE;
+        for (int s = 0; s < kSteps; ++s) {
+            const int head = head0 + s * GROUPS;
             if (head - group >= heads) break;         // warp-uniform: no lane group of this warp has a head left
             const bool valid = head < heads;          // lanes without a head still take part in the shuffles
-            const bool is_q = head < hq;
-            const bool is_k = !is_q && head < hq + hkv;
-            F2 a01 = f2_unpack<T>(in[u].lo.x), a23 = f2_unpack<T>(in[u].lo.y);   // first half
-            F2 b01 = f2_unpack<T>(in[u].hi.x), b23 = f2_unpack<T>(in[u].hi.y);   // second half
-            float ss;
-            {
-                F2 sq = f2_mul(a01, a01);
-                sq = f2_fma(a23, a23, sq);
-                sq = f2_fma(b01, b01, sq);
-                sq = f2_fma(b23, b23, sq);
-                float s0, s1;
-                f2_split(sq, s0, s1);
-                ss = s0 + s1;
-            }
+            const bool is_q = head < p.hq;
+            const bool is_k = !is_q && head < p.hq + p.hkv;
+            uint4 out_lo, out_hi;
+            {                                         // every lane runs the arithmetic (the shuffles need the whole warp)
+                float inv_rms = 1.0f;
+                if (normed) {
+                    F2 sq = f2_make(0.0f, 0.0f);
 #pragma unroll
-            for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const float inv_rms = rsqrtf(ss / static_cast<float>(D) + eps);
-            const F2 inv2 = f2_make(inv_rms, inv_rms);
-            const Piece& w = is_q ? wq : wk;
-            a01 = f2_mul(f2_mul(a01, inv2), f2_unpack<T>(w.lo.x));
-            a23 = f2_mul(f2_mul(a23, inv2), f2_unpack<T>(w.lo.y));
-            b01 = f2_mul(f2_mul(b01, inv2), f2_unpack<T>(w.hi.x));
-            b23 = f2_mul(f2_mul(b23, inv2), f2_unpack<T>(w.hi.y));
-            Piece out;
-            if (rotate) {   // first half: x cos - partner sin; second half: x cos + partner sin
-                out.lo.x = f2_pack<T>(f2_fma(a01, c01, f2_mul(b01, n01)));
-                out.lo.y = f2_pack<T>(f2_fma(a23, c23, f2_mul(b23, n23)));
-                out.hi.x = f2_pack<T>(f2_fma(b01, c01, f2_mul(a01, s01)));
-                out.hi.y = f2_pack<T>(f2_fma(b23, c23, f2_mul(a23, s23)));
-            } else {        // positions outside the table leave the value un-rotated
-                out.lo.x = f2_pack<T>(a01); out.lo.y = f2_pack<T>(a23);
-                out.hi.x = f2_pack<T>(b01); out.hi.y = f2_pack<T>(b23);
+                    for (int i = 0; i < 4; ++i) {
+                        const F2 a = f2_unpack<T>(word(lo[s], i)), b = f2_unpack<T>(word(hi[s], i));
+                        sq = f2_fma(a, a, sq);
+                        sq = f2_fma(b, b, sq);
+                    }
+                    float s0, s1;
+                    f2_split(sq, s0, s1);
+                    float ss = s0 + s1;
+#pragma unroll
+                    for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    inv_rms = rsqrtf(ss / static_cast<float>(D) + p.eps);
+                }
+                const F2 inv2 = f2_make(inv_rms, inv_rms);
+                const T* weight = static_cast<const T*>(is_q ? p.q_weight : p.k_weight);
+                uint4 w_lo = make_uint4(0u, 0u, 0u, 0u), w_hi = w_lo;
+                if (normed) {
+                    w_lo = __ldg(reinterpret_cast<const uint4*>(weight + lo_off));
+                    w_hi = __ldg(reinterpret_cast<const uint4*>(weight + hi_off));
+                }
+                uint32_t r_lo[4], r_hi[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {         // two rotation pairs per trip
+                    F2 a = f2_unpack<T>(word(lo[s], i)), b = f2_unpack<T>(word(hi[s], i));
+                    if (normed) {
+                        a = f2_mul(f2_mul(a, inv2), f2_unpack<T>(word(w_lo, i)));
+                        b = f2_mul(f2_mul(b, inv2), f2_unpack<T>(word(w_hi, i)));
+                    }
+                    if (rotate) {   // first half: x cos - partner sin; second half: x cos + partner sin
+                        const float2 c = __ldg(reinterpret_cast<const float2*>(table + 2 * i));
+                        const float2 sn = __ldg(reinterpret_cast<const float2*>(table + D / 2 + 2 * i));
+                        const F2 c2 = f2_make(c.x, c.y), s2 = f2_make(sn.x, sn.y), n2 = f2_make(-sn.x, -sn.y);
+                        r_lo[i] = f2_pack<T>(f2_fma(a, c2, f2_mul(b, n2)));
+                        r_hi[i] = f2_pack<T>(f2_fma(b, c2, f2_mul(a, s2)));
+                    } else {        // positions outside the table leave the value un-rotated
+                        r_lo[i] = f2_pack<T>(a);
+                        r_hi[i] = f2_pack<T>(b);
+                    }
+                }
+                out_lo = make_uint4(r_lo[0], r_lo[1], r_lo[2], r_lo[3]);
+                out_hi = make_uint4(r_hi[0], r_hi[1], r_hi[2], r_hi[3]);
             }
             if (!valid) continue;
+            if (!is_q && !is_k) { out_lo = lo[s]; out_hi = hi[s]; }   // v heads: plain copy
             T* dst;
             if (is_q) {
-                dst = q_out + (row * hq + head) * D;
+                dst = static_cast<T*>(p.q_out) + (row * p.hq + head) * D;
             } else {
                 if (!store_kv) continue;
-                const int kv = is_k ? head - hq : head - hq - hkv;
-                dst = (is_k ? k_cache : v_cache) + (slot * hkv + kv) * D;
-                if (!is_k) out = in[u];               // v heads: plain copy
+                const int kv = is_k ? head - p.hq : head - p.hq - p.hkv;
+                dst = static_cast<T*>(is_k ? p.k_cache : p.v_cache) + (slot * p.hkv + kv) * D;
             }
-            *reinterpret_cast<uint2*>(dst + lo_off) = out.lo;
-            *reinterpret_cast<uint2*>(dst + hi_off) = out.hi;
+            *reinterpret_cast<uint4*>(dst + lo_off) = out_lo;
+            *reinterpret_cast<uint4*>(dst + hi_off) = out_hi;
         }
-#pragma unroll
-        for (int u = 0; u < PIECES; ++u) in[u] = nxt[u];
-        pos = pos_next;
-        slot = slot_next;
     }
 }
 
@@ -190,43 +200,34 @@ int prologue_sm_count() {
     return sms[device];
 }
 
-template <typename T, int LANES>
-int launch_lanes(const void* qkv, const int32_t* positions, const void* qw, const void* kw, float eps,
-                 const float* cos_sin, int64_t max_positions, const int32_t* slot_mapping, void* k_cache,
-                 void* v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv, void* q_out, cudaStream_t stream) {
-    constexpr int STRIDE = kWarpsPerBlock * (32 / LANES);
-    const int heads = hq + 2 * hkv;
-    const int pieces = (heads + STRIDE - 1) / STRIDE;
-    if (pieces > kMaxPieces)
-        return fail(NVK_ERR_UNSUPPORTED, "fused_split_norm_rope_store: at most %d heads (q + 2 kv) at head_dim %d", STRIDE * kMaxPieces, LANES * 8);
-    const int64_t resident = static_cast<int64_t>(prologue_sm_count()) * (pieces <= 3 ? 2 : 1);
-    const unsigned grid = static_cast<unsigned>(rows < resident ? rows : resident);
-#define NVK_LAUNCH(PIECES)                                                                                     \
-    fused_prologue_kernel<T, LANES, PIECES><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                         \
-        static_cast<const T*>(qkv), positions, static_cast<const T*>(qw), static_cast<const T*>(kw), eps,     \
-        cos_sin, static_cast<int>(max_positions), slot_mapping, static_cast<T*>(k_cache),                      \
-        static_cast<T*>(v_cache), cache_rows, rows, hq, hkv, static_cast<T*>(q_out))
-    switch (pieces) {
-        case 1: NVK_LAUNCH(1); break;
-        case 2: NVK_LAUNCH(2); break;
-        case 3: NVK_LAUNCH(3); break;
-        case 4: NVK_LAUNCH(4); break;
-        case 5: case 6: NVK_LAUNCH(6); break;
-        default: NVK_LAUNCH(8); break;
-    }
-#undef NVK_LAUNCH
+template <typename T, int D>
+int launch_dim(const PrologueParams& p, cudaStream_t stream) {
+    constexpr int GROUPS = 32 / (D / 16);
+    const int heads = p.hq + 2 * p.hkv;
+    const int64_t units = p.rows * ((heads + GROUPS * kSteps - 1) / (GROUPS * kSteps));
+    const int64_t resident = static_cast<int64_t>(prologue_sm_count()) * 4;   // four blocks per SM
+    int64_t blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    if (blocks > resident) blocks = resident;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(kWarpsPerBlock * 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, fused_prologue_kernel<T, D>, p);
+    if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "fused_split_norm_rope_store kernel launch: %s", cudaGetErrorString(e));
     return check_launch("fused_split_norm_rope_store kernel launch");
 }
 
 template <typename T>
-int launch_typed(const void* qkv, const int32_t* positions, const void* qw, const void* kw, float eps,
-                 const float* cos_sin, int64_t max_positions, const int32_t* slot_mapping, void* k_cache,
-                 void* v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv, int d, void* q_out,
-                 cudaStream_t stream) {
+int launch_typed(const PrologueParams& p, int d, cudaStream_t stream) {
     switch (d) {
-        case 64: return launch_lanes<T, 8>(qkv, positions, qw, kw, eps, cos_sin, max_positions, slot_mapping, k_cache, v_cache, cache_rows, rows, hq, hkv, q_out, stream);
-        case 128: return launch_lanes<T, 16>(qkv, positions, qw, kw, eps, cos_sin, max_positions, slot_mapping, k_cache, v_cache, cache_rows, rows, hq, hkv, q_out, stream);
-        case 256: return launch_lanes<T, 32>(qkv, positions, qw, kw, eps, cos_sin, max_positions, slot_mapping, k_cache, v_cache, cache_rows, rows, hq, hkv, q_out, stream);
+        case 64: return launch_dim<T, 64>(p, stream);
+        case 128: return launch_dim<T, 128>(p, stream);
+        case 256: return launch_dim<T, 256>(p, stream);
         default: return fail(NVK_ERR_UNSUPPORTED, "fused_split_norm_rope_store: head_dim must be 64, 128 or 256 (got %d)", d);
     }
 }
@@ -237,11 +238,12 @@ int launch_fused_prologue(const void* qkv, const int32_t* positions, const void*
                           const float* cos_sin, int64_t max_positions, const int32_t* slot_mapping,
                           void* k_cache, void* v_cache, int64_t cache_rows, int64_t rows, int hq, int hkv,
                           int d, void* q_out, int dtype, cudaStream_t stream) {
-    if (dtype == NVK_BF16)
-        return launch_typed<__nv_bfloat16>(qkv, positions, qw, kw, eps, cos_sin, max_positions, slot_mapping,
-                                           k_cache, v_cache, cache_rows, rows, hq, hkv, d, q_out, stream);
-    return launch_typed<__half>(qkv, positions, qw, kw, eps, cos_sin, max_positions, slot_mapping, k_cache,
-                                v_cache, cache_rows, rows, hq, hkv, d, q_out, stream);
+    PrologueParams p{};
+    p.qkv = qkv; p.positions = positions; p.q_weight = qw; p.k_weight = kw; p.cos_sin = cos_sin;
+    p.slot_mapping = slot_mapping; p.k_cache = k_cache; p.v_cache = v_cache; p.q_out = q_out;
+    p.cache_rows = cache_rows; p.rows = rows; p.max_positions = static_cast<int>(max_positions);
+    p.hq = hq; p.hkv = hkv; p.eps = eps;
+    return dtype == NVK_BF16 ? launch_typed<__nv_bfloat16>(p, d, stream) : launch_typed<__half>(p, d, stream);
 }
 
 }  // namespace nvk

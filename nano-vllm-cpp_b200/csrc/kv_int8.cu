@@ -90,7 +90,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(128)
 decode_int8_rowwise_kernel(const T* __restrict__ query, const int8_t* __restrict__ k_cache, const int8_t* __restrict__ v_cache,
                            const __half* __restrict__ k_scale, const __half* __restrict__ v_scale,
-                           const int32_t* __restrict__ context_lens, const int32_t* __restrict__ block_tables,
+                           const IndexArray context_lens, const IndexArray block_tables,
                            int64_t batch, int64_t max_blocks, int64_t num_cache_blocks, int num_heads, int num_kv_heads,
                            int block_size, float scale, T* __restrict__ output) {
     constexpr int D = V * 32;
@@ -106,7 +106,7 @@ decode_int8_rowwise_kernel(const T* __restrict__ query, const int8_t* __restrict
     for (int i = 0; i < V; ++i) acc[i] = 0.0f;
     const int64_t k_len = context_lens[seq];
     float running_max = -INFINITY, running_sum = 0.0f;
-    const int32_t* table = block_tables + seq * max_blocks;
+    const IndexArray table = block_tables + seq * max_blocks;
     for (int64_t k = 0; k < k_len; ++k) {
         const int64_t block = table[k / block_size];
         const bool inside = block >= 0 && block < num_cache_blocks;   // ids outside the cache read as zeros

@@ -30,6 +30,8 @@ int check_launch(const char* what) {
 namespace {
 
 bool is_compute_dtype(int dtype) { return dtype == NVK_F16 || dtype == NVK_BF16 || dtype == NVK_F32; }
+bool is_index_dtype(int dtype) { return dtype == NVK_I32 || dtype == NVK_I64; }
+IndexArray index_array(const void* p, int dtype) { return IndexArray(p, dtype == NVK_I64 ? 1 : 0); }
 
 }  // namespace
 }  // namespace nvk
@@ -38,7 +40,7 @@ using namespace nvk;
 
 extern "C" {
 
-int nvk_abi_version(void) { return 1; }
+int nvk_abi_version(void) { return 2; }
 
 const char* nvk_last_error(void) { return g_last_error.c_str(); }
 
@@ -65,9 +67,10 @@ int nvk_fused_split_norm_rope_store(const void* qkv, const int32_t* positions, c
                                     int num_kv_heads, int head_dim, void* q_out, int dtype, void* stream) {
     if (dtype != NVK_F16 && dtype != NVK_BF16)
         return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store only supports bf16/fp16");
-    if (!qkv || !positions || !q_norm_weight || !k_norm_weight || !cos_sin_cache || !slot_mapping || !k_cache ||
-        !v_cache || !q_out)
+    if (!qkv || !positions || !cos_sin_cache || !k_cache || !v_cache || !q_out)
         return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: all tensors must be defined");
+    if ((q_norm_weight == nullptr) != (k_norm_weight == nullptr))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: q_norm_weight and k_norm_weight go together");
     if (rows < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || max_positions <= 0 || cache_rows <= 0)
         return fail(NVK_ERR_INVALID_ARGUMENT, "fused_split_norm_rope_store: sizes must be positive");
     if (rows == 0) return NVK_OK;
@@ -85,12 +88,14 @@ size_t nvk_decode_attention_workspace_bytes(int64_t batch, int num_heads, int nu
 }
 
 int nvk_decode_attention_paged(const void* query, const void* k_cache, const void* v_cache,
-                               const int32_t* context_lens, const int32_t* block_tables, int64_t batch,
-                               int64_t max_blocks, int64_t num_cache_blocks, int num_heads, int num_kv_heads,
-                               int head_dim, int block_size, float scale, void* output, int dtype,
-                               void* workspace, size_t workspace_bytes, void* stream) {
+                               const void* context_lens, int context_lens_dtype, const void* block_tables,
+                               int block_tables_dtype, int64_t batch, int64_t max_blocks, int64_t num_cache_blocks,
+                               int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
+                               void* output, int dtype, void* workspace, size_t workspace_bytes, void* stream) {
     if (!query || !k_cache || !v_cache || !context_lens || !block_tables || !output)
         return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention requires KV cache, context_lens, and block_tables");
+    if (!is_index_dtype(context_lens_dtype) || !is_index_dtype(block_tables_dtype))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "context_lens and block_tables must be int32 or int64");
     if (!is_compute_dtype(dtype)) return fail(NVK_ERR_INVALID_ARGUMENT, "unsupported dtype for decode_attention_paged");
     if (batch < 0 || max_blocks <= 0 || num_cache_blocks <= 0 || num_heads <= 0 || num_kv_heads <= 0 ||
         head_dim <= 0 || block_size <= 0)
@@ -98,7 +103,8 @@ int nvk_decode_attention_paged(const void* query, const void* k_cache, const voi
     if (num_heads % num_kv_heads != 0)
         return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
     if (batch == 0) return NVK_OK;
-    DecodeArgs a{query, k_cache, v_cache, context_lens, block_tables, output, batch, max_blocks, num_cache_blocks,
+    DecodeArgs a{query, k_cache, v_cache, index_array(context_lens, context_lens_dtype),
+                 index_array(block_tables, block_tables_dtype), output, batch, max_blocks, num_cache_blocks,
                  num_heads, num_kv_heads, head_dim, block_size, scale, dtype, workspace, workspace_bytes,
                  static_cast<cudaStream_t>(stream)};
     if (decode_mma_supported(a)) {
@@ -132,12 +138,15 @@ int nvk_store_kvcache_int8(const void* key, const void* value, void* k_cache, vo
 }
 
 int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, const void* v_cache, const void* k_scale,
-                                    const void* v_scale, const int32_t* context_lens, const int32_t* block_tables,
-                                    int64_t batch, int64_t max_blocks, int64_t num_cache_blocks, int num_heads,
-                                    int num_kv_heads, int head_dim, int block_size, float scale, void* output, int dtype,
-                                    void* workspace, size_t workspace_bytes, void* stream) {
+                                    const void* v_scale, const void* context_lens, int context_lens_dtype,
+                                    const void* block_tables, int block_tables_dtype, int64_t batch, int64_t max_blocks,
+                                    int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim,
+                                    int block_size, float scale, void* output, int dtype, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
     if (!query || !k_cache || !v_cache || !k_scale || !v_scale || !context_lens || !block_tables || !output)
         return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (int8) requires KV cache, scales, context_lens, and block_tables");
+    if (!is_index_dtype(context_lens_dtype) || !is_index_dtype(block_tables_dtype))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "context_lens and block_tables must be int32 or int64");
     if (!is_compute_dtype(dtype)) return fail(NVK_ERR_INVALID_ARGUMENT, "unsupported query dtype for decode_attention_paged_int8");
     if (batch < 0 || max_blocks <= 0 || num_cache_blocks <= 0 || num_heads <= 0 || num_kv_heads <= 0 ||
         head_dim <= 0 || block_size <= 0)
@@ -145,7 +154,8 @@ int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, cons
     if (num_heads % num_kv_heads != 0)
         return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
     if (batch == 0) return NVK_OK;
-    DecodeInt8Args a{{query, k_cache, v_cache, context_lens, block_tables, output, batch, max_blocks, num_cache_blocks,
+    DecodeInt8Args a{{query, k_cache, v_cache, index_array(context_lens, context_lens_dtype),
+                      index_array(block_tables, block_tables_dtype), output, batch, max_blocks, num_cache_blocks,
                       num_heads, num_kv_heads, head_dim, block_size, scale, dtype, workspace, workspace_bytes,
                       static_cast<cudaStream_t>(stream)},
                      k_scale, v_scale};
@@ -164,8 +174,9 @@ int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, cons
 }
 
 int nvk_prefill_attention_varlen(const void* query, const void* key, const void* value, const void* k_cache,
-                                 const void* v_cache, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
-                                 const int32_t* block_tables, int64_t num_seqs, int64_t total_q, int64_t total_k,
+                                 const void* v_cache, const void* cu_seqlens_q, int cu_seqlens_q_dtype,
+                                 const void* cu_seqlens_k, int cu_seqlens_k_dtype, const void* block_tables,
+                                 int block_tables_dtype, int64_t num_seqs, int64_t total_q, int64_t total_k,
                                  int64_t max_blocks, int64_t num_cache_blocks, int max_seqlen_q, int num_heads,
                                  int num_kv_heads, int head_dim, int block_size, float scale, void* output,
                                  int dtype, void* stream) {
@@ -175,6 +186,9 @@ int nvk_prefill_attention_varlen(const void* query, const void* key, const void*
         return fail(NVK_ERR_INVALID_ARGUMENT, "attention dimensions must be positive");
     if (num_heads % num_kv_heads != 0)
         return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
+    if ((cu_seqlens_q && !is_index_dtype(cu_seqlens_q_dtype)) || (cu_seqlens_k && !is_index_dtype(cu_seqlens_k_dtype)) ||
+        (block_tables && !is_index_dtype(block_tables_dtype)))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "cu_seqlens and block_tables must be int32 or int64");
     const bool paged = block_tables != nullptr;
     if (paged) {
         if (!cu_seqlens_q || !cu_seqlens_k)
@@ -189,7 +203,8 @@ int nvk_prefill_attention_varlen(const void* query, const void* key, const void*
     }
     if (cu_seqlens_q && num_seqs <= 0) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill attention: num_seqs must be positive");
     if (total_q == 0) return NVK_OK;
-    PrefillArgs a{query, key, value, k_cache, v_cache, cu_seqlens_q, cu_seqlens_k, block_tables, output, num_seqs,
+    PrefillArgs a{query, key, value, k_cache, v_cache, index_array(cu_seqlens_q, cu_seqlens_q_dtype),
+                  index_array(cu_seqlens_k, cu_seqlens_k_dtype), index_array(block_tables, block_tables_dtype), output, num_seqs,
                   total_q, total_k, max_blocks, num_cache_blocks, max_seqlen_q, num_heads, num_kv_heads, head_dim,
                   block_size, scale, dtype, static_cast<cudaStream_t>(stream)};
     if (prefill_tc_supported(a)) return launch_prefill_tc(a);

@@ -33,10 +33,31 @@ inline size_t dtype_size(int dtype) {
     }
 }
 
+// An index tensor of the boundary (cu_seqlens_*, context_lens, block_tables): int32 or int64 elements, each tensor
+// on its own, as the reference's kernels accept them (src/kernels/attention.cu:644-660, :708-735).  The width is a
+// launch-uniform flag read where an index is loaded; values are widened to 64 bits.
+struct IndexArray {
+    const void* ptr = nullptr;
+    int wide = 0;   // 1 = int64 elements, 0 = int32
+    IndexArray() = default;
+    __host__ __device__ IndexArray(const void* p, int w) : ptr(p), wide(w) {}
+    __host__ __device__ explicit operator bool() const { return ptr != nullptr; }
+    __host__ __device__ bool operator==(std::nullptr_t) const { return ptr == nullptr; }
+    __host__ __device__ bool operator!=(std::nullptr_t) const { return ptr != nullptr; }
+    __host__ __device__ IndexArray operator+(int64_t n) const {
+        return IndexArray(static_cast<const char*>(ptr) + n * (wide ? 8 : 4), wide);
+    }
+#ifdef __CUDACC__
+    __device__ __forceinline__ int64_t operator[](int64_t i) const {
+        return wide ? static_cast<const int64_t*>(ptr)[i] : static_cast<int64_t>(static_cast<const int32_t*>(ptr)[i]);
+    }
+#endif
+};
+
 // ---- launchers (one per .cu file) -----------------------------------------------------------
 struct DecodeArgs {
     const void* q; const void* k_cache; const void* v_cache;
-    const int32_t* context_lens; const int32_t* block_tables;
+    IndexArray context_lens; IndexArray block_tables;
     void* out;
     int64_t batch, max_blocks, num_cache_blocks;
     int num_heads, num_kv_heads, head_dim, block_size;
@@ -52,7 +73,7 @@ struct DecodeInt8Args {          // int8 caches with one fp16 scale per (cache r
 struct PrefillArgs {
     const void* q; const void* k; const void* v;          // dense keys (k, v) or paged (caches)
     const void* k_cache; const void* v_cache;
-    const int32_t* cu_q; const int32_t* cu_k; const int32_t* block_tables;
+    IndexArray cu_q; IndexArray cu_k; IndexArray block_tables;
     void* out;
     int64_t num_seqs, total_q, total_k, max_blocks, num_cache_blocks;
     int max_seqlen_q, num_heads, num_kv_heads, head_dim, block_size;

@@ -34,7 +34,7 @@ constexpr int kSmemBytes = kQBytes + kStages * kStageBytes;  // 80 KiB
 
 struct PrefillParams {
     const void* q; const void* k; const void* v; void* out;
-    const int32_t* cu_q; const int32_t* cu_k; const int32_t* block_tables;
+    IndexArray cu_q, cu_k, block_tables;
     int64_t num_seqs, total_q, total_k, max_blocks, key_rows;   // key_rows: rows addressable in k / v
     int num_heads, num_kv_heads, block_size;
     float scale_log2;
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tile_kernel(const Prefill
     unsigned char* q_smem = smem;
     const uint32_t q_u32 = smem_u32(q_smem);
     const uint32_t kv_u32 = q_u32 + kQBytes;
-    const int32_t* table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : nullptr;
+    const IndexArray table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : IndexArray();
     const size_t kv_row_stride = static_cast<size_t>(p.num_kv_heads) * kRowBytes;
     const unsigned char* kbase = static_cast<const unsigned char*>(p.k) + static_cast<size_t>(kvh) * kRowBytes;
     const unsigned char* vbase = static_cast<const unsigned char*>(p.v) + static_cast<size_t>(kvh) * kRowBytes;
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_tile_kernel(const Prefill
         int64_t tile_row0 = 0;
         bool tile_ok = true;
         if (table) {   // a 64-key tile never straddles a cache block (block_size % 64 == 0)
-            const int id = table[key0 / p.block_size];
+            const int64_t id = table[key0 / p.block_size];
             tile_row0 = static_cast<int64_t>(id) * p.block_size + key0 % p.block_size;
             tile_ok = id >= 0;
         } else {

@@ -5,9 +5,8 @@
 // src/kernels/flash_attn.cpp:203-300); prefill_attn.cu (mma.sync) remains the path for shapes this
 // kernel does not take.
 //
-// Three kernels live here: the single-tile kernel described next (taken for odd GQA group sizes), and two
-// head-pair kernels further down ("Version 4": one block per item, probabilities through shared memory;
-// "Version 5": the same made persistent, the default for even group sizes).
+// Two kernels live here, chosen by shape: the single-tile kernel described next (odd GQA group sizes) and the
+// persistent head-pair kernel further down (even group sizes: the two query heads of a pair share their K / V tiles).
 //
 // Single-tile kernel: one thread block = 128 query rows of one (sequence, head); 128 threads, thread t owns row t.
 //   * Q (128 x 128), K tile (128 keys x 128) and V tile live in shared memory as two 128-byte-wide
@@ -54,8 +53,8 @@ constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 __device__ int g_tc_error = 0;
 
 struct TcParams {
-    const int32_t* cu_q; const int32_t* cu_k; const int32_t* block_tables;
-    void* out; float* dbg; long long* dbg_clk;
+    IndexArray cu_q, cu_k, block_tables;
+    void* out;
     int64_t num_seqs, total_q, total_k, max_blocks, key_rows, num_cache_blocks;
     int num_heads, num_kv_heads, block_size;
     float scale_log2;
@@ -349,12 +348,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t t_s = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lanes, S / P columns
     const uint32_t t_o = t_s + 128;                                               // O columns
 
-    const int32_t* table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : nullptr;
+    const IndexArray table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : IndexArray();
     auto key_row = [&](int key0) -> int {   // row coordinate of a key tile; out-of-range ids -> zero-filled box
         if (table) {
-            const int id = table[key0 / p.block_size];
+            const int64_t id = table[key0 / p.block_size];
             if (id < 0 || id >= p.num_cache_blocks) return static_cast<int>(p.key_rows);
-            return id * p.block_size + key0 % p.block_size;
+            return static_cast<int>(id) * p.block_size + key0 % p.block_size;
         }
         return static_cast<int>(kb) + key0;
     };
@@ -376,12 +375,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     float m_ref = -INFINITY, l_run = 0.0f;
     bool alive = true;
 
-    const bool clk_on = p.dbg_clk != nullptr && blockIdx.x == 0 && blockIdx.y == gridDim.y / 2;
-#define NVK_STAMP(slot, who) do { if (clk_on && tid == (who) && j < 64) p.dbg_clk[j * 8 + (slot)] = clock64(); } while (0)
     for (int j = 0; j < num_kt && alive; ++j) {
         const int key0 = j * kBN;
         const uint32_t ph = j & 1;
-        NVK_STAMP(0, 33);
         // ---- S = Q K^T ------------------------------------------------------------------------------
         if (tid == 0) {
             bool ok = true;
@@ -389,7 +385,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             ok = ok && mbar_wait(bar_k, ph, abort_flag, 2);
             if (ok) {
                 tc_fence_after();
-                NVK_STAMP(5, 0);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
@@ -403,7 +398,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         alive = warp_mbar_wait(bar_s, ph, abort_flag, 3);
         if (!alive) break;
         tc_fence_after();
-        NVK_STAMP(1, 33);
         // S_j done => PV_{j-1} done (MMAs retire in order): the K and V buffers are free again.
         if (tid == 0) {
             if (j + 1 < num_kt) {
@@ -428,14 +422,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_ld32(t_s, ra);
         tc_wait_ld(); reg_fence32(ra);
         tmem_ld32(t_s + 32, rb);
-        if (p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == gridDim.y - 1 && j == 0) {
-            for (int c = 0; c < 4; ++c) {
-                uint32_t t[32];
-                tmem_ld32(t_s + c * 32, t);
-                tc_wait_ld(); reg_fence32(t);
-                for (int i = 0; i < 32; ++i) p.dbg[tid * kBN + c * 32 + i] = __uint_as_float(t[i]);
-            }
-        }
         if (need_mask) {
             mx = chunk_max<true>(ra, key0, lim);
             tc_wait_ld(); reg_fence32(rb);
@@ -457,7 +443,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tc_wait_ld(); reg_fence32(rb);
             mx = fmaxf(mx, chunk_max<false>(rb, 0, 0));
         }
-        NVK_STAMP(2, 33);
         // start re-reading the scores for pass 2 while the maximum is settled
         tmem_ld32(t_s, ra);
         mx *= p.scale_log2;
@@ -504,7 +489,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_st16(t_s + 48, pk);
         }
         tc_wait_st();
-        NVK_STAMP(3, 33);
 
         // ---- last tile: rows of V past the sequence may hold anything; zero them (0 * NaN = NaN) ---------
         if (key0 + kBN > k_len) {
@@ -521,7 +505,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         tc_fence_before();
         __syncthreads();
-        NVK_STAMP(4, 33);
 
         // ---- O += P V ---------------------------------------------------------------------------------
         if (tid == 0 && !*abort_flag) {
@@ -533,11 +516,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 tc_commit(bar_o);
-                NVK_STAMP(6, 0);
             }
         }
     }
-#undef NVK_STAMP
 
     // ---- epilogue ----------------------------------------------------------------------------------------
     __syncwarp();
@@ -599,18 +580,16 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // =================================================================================================
-// Version 4: one head pair per block (the two query heads of a pair that share a KV head: K and V tiles are
-// loaded once for both), warp specialised (8 softmax warps, thread = row; one MMA-issuer warp; one TMA-producer
-// warp), 128-key tiles.  The probabilities go to SHARED memory (canonical K-major 128-byte-swizzled panels, consumed as the A
-// operand of an SS MMA) instead of overwriting the scores in TMEM.  A softmax thread pulls its whole
-// score row into registers first and releases the score columns at once, so S_t(j+1) is computed
-// while softmax_t(j) is still running and a tile's softmax steps follow each other back to back;
-// P.V_t(j) runs under softmax_t(j+1).  K is double buffered, V single buffered, 224 KiB of shared
-// memory and 512 TMEM columns per block.
+// Head-pair kernel: shared-memory layout and the softmax step.  A block works on the two query heads of a pair
+// that share a KV head (K and V tiles are loaded once for both) with 128-key tiles.  The probabilities go to
+// SHARED memory (canonical K-major 128-byte-swizzled panels, consumed as the A operand of an SS MMA) instead of
+// overwriting the scores in TMEM.  A softmax thread pulls its whole score row into registers first and releases
+// the score columns at once, so S_t(j+1) is computed while softmax_t(j) is still running and a tile's softmax
+// steps follow each other back to back; P.V_t(j) runs under softmax_t(j+1).  K is double buffered, V single
+// buffered, 224 KiB of shared memory and 512 TMEM columns per block.
 // =================================================================================================
 constexpr int kOff4Q = 0, kOff4K = 2 * kTileBytes, kOff4V = 4 * kTileBytes, kOff4P = 5 * kTileBytes, kOff4Bar = 7 * kTileBytes;
 constexpr int kSmemBytes4 = kOff4Bar + 256 + 1024;
-constexpr int kThreads4 = 320;
 
 // One 128-key online-softmax step of a row.  Scores are read once into registers; `on_scores_read` runs as
 // soon as they are (the caller releases the TMEM columns there); probabilities are written to `p_row`
@@ -695,274 +674,8 @@ __device__ __forceinline__ bool softmax_row_to_smem(uint32_t t_s, uint32_t t_o, 
 
 
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads4, 1)
-prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ int s_info[4];
-    __shared__ uint32_t s_tmem_base;
-    __shared__ int s_abort;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int head0 = 2 * blockIdx.x;
-    const int kvh = head0 * p.num_kv_heads / p.num_heads;
-
-    if (tid == 0) {
-        const int64_t want = static_cast<int64_t>(gridDim.y) - 1 - blockIdx.y;
-        int64_t acc = 0;
-        int found = -1, q0 = 0;
-        if (p.cu_q == nullptr) {
-            if (want * kBM < p.total_q) { found = 0; q0 = static_cast<int>(want * kBM); }
-        } else {
-            for (int64_t s = 0; s < p.num_seqs; ++s) {
-                const int64_t tiles = (static_cast<int64_t>(p.cu_q[s + 1]) - p.cu_q[s] + kBM - 1) / kBM;
-                if (want < acc + tiles) { found = static_cast<int>(s); q0 = static_cast<int>((want - acc) * kBM); break; }
-                acc += tiles;
-            }
-        }
-        s_info[0] = found; s_info[1] = q0;
-        s_abort = 0;
-    }
-    __syncthreads();
-    const int seq = s_info[0];
-    if (seq < 0) return;
-    const int q0 = s_info[1];
-    int64_t qb, kb;
-    int q_len, k_len;
-    if (p.cu_q == nullptr) { qb = 0; kb = 0; q_len = static_cast<int>(p.total_q); k_len = static_cast<int>(p.total_k); }
-    else {
-        qb = p.cu_q[seq]; kb = p.cu_k[seq];
-        q_len = p.cu_q[seq + 1] - static_cast<int>(qb); k_len = p.cu_k[seq + 1] - static_cast<int>(kb);
-    }
-    const int rows_here = min(kBM, q_len - q0);
-    const int shift = k_len - q_len;
-    int k_hi = shift + q0 + rows_here;
-    if (k_hi > k_len) k_hi = k_len;
-    const int num_kt = k_hi > 0 ? (k_hi + kBN - 1) / kBN : 0;
-    const size_t out_stride = static_cast<size_t>(p.num_heads) * kHeadDim;
-
-    if (num_kt == 0) {
-        for (int t = 0; t < 2; ++t) {
-            T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(qb + q0) * p.num_heads + head0 + t) * kHeadDim;
-            for (int i = tid; i < rows_here * (kHeadDim / 8); i += kThreads4) {
-                const int r = i / (kHeadDim / 8), c = i % (kHeadDim / 8);
-                *reinterpret_cast<uint4*>(o0 + r * out_stride + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-            }
-        }
-        return;
-    }
-
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t sm_q = smem_base + kOff4Q, sm_k = smem_base + kOff4K, sm_v = smem_base + kOff4V, sm_p = smem_base + kOff4P;
-    const uint32_t bars = smem_base + kOff4Bar;
-    const uint32_t bar_q = bars, bar_vfix = bars + 8, bar_vfull = bars + 16, bar_vempty = bars + 24;
-    auto bar_kfull = [&](int s) { return bars + 32 + 8 * s; };
-    auto bar_kempty = [&](int s) { return bars + 48 + 8 * s; };
-    auto bar_sfull = [&](int t) { return bars + 64 + 8 * t; };
-    auto bar_sread = [&](int t) { return bars + 80 + 8 * t; };
-    auto bar_pfull = [&](int t) { return bars + 96 + 8 * t; };
-    auto bar_odone = [&](int t) { return bars + 112 + 8 * t; };
-    auto bar_ofinal = [&](int t) { return bars + 128 + 8 * t; };
-    volatile int* abort_flag = &s_abort;
-
-    if (tid == 0) {
-        mbar_init(bar_q, 1); mbar_init(bar_vfix, 1); mbar_init(bar_vfull, 1); mbar_init(bar_vempty, 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_kfull(i), 1); mbar_init(bar_kempty(i), 1);
-            mbar_init(bar_sfull(i), 1); mbar_init(bar_sread(i), 4); mbar_init(bar_pfull(i), 4);
-            mbar_init(bar_odone(i), 1); mbar_init(bar_ofinal(i), 1);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    __syncwarp();
-    if (warp == 8) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&s_tmem_base)), "r"(kTmemCols2) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = s_tmem_base;
-    const int last_partial = (num_kt * kBN > k_len) ? num_kt - 1 : -1;
-
-    if (warp == 9) {
-        // ------------------------------------------------------------------ TMA producer
-        const int32_t* table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : nullptr;
-        auto key_row = [&](int key0) -> int {
-            if (table) {
-                const int id = table[key0 / p.block_size];
-                if (id < 0 || id >= p.num_cache_blocks) return static_cast<int>(p.key_rows);
-                return id * p.block_size + key0 % p.block_size;
-            }
-            return static_cast<int>(kb) + key0;
-        };
-        auto load_k = [&](int j) -> bool {   // lane 0 only: K_j into slot j & 1
-            const int s = j & 1;
-            if (j >= 2 && !mbar_wait(bar_kempty(s), ((j >> 1) & 1) ^ 1, abort_flag, 11)) return false;
-            const int r = key_row(j * kBN);
-            mbar_expect_tx(bar_kfull(s), kTileBytes);
-            tma_load_3d(sm_k + s * kTileBytes, &tm_k, 0, kvh, r, bar_kfull(s));
-            tma_load_3d(sm_k + s * kTileBytes + kPanelBytes, &tm_k, 64, kvh, r, bar_kfull(s));
-            return true;
-        };
-        bool ok = true;
-        if (lane == 0) {
-            mbar_expect_tx(bar_q, 2 * kTileBytes);
-            for (int t = 0; t < 2; ++t) {
-                tma_load_3d(sm_q + t * kTileBytes, &tm_q, 0, head0 + t, static_cast<int>(qb) + q0, bar_q);
-                tma_load_3d(sm_q + t * kTileBytes + kPanelBytes, &tm_q, 64, head0 + t, static_cast<int>(qb) + q0, bar_q);
-            }
-            ok = load_k(0);
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        for (int j = 0; j < num_kt && ok; ++j) {
-            if (lane == 0) {
-                if (j + 1 < num_kt) ok = load_k(j + 1);            // K runs one tile ahead of V
-                if (ok && j >= 1) ok = mbar_wait(bar_vempty, (j - 1) & 1, abort_flag, 12);
-                if (ok) {
-                    const int r = key_row(j * kBN);
-                    mbar_expect_tx(bar_vfull, kTileBytes);
-                    tma_load_3d(sm_v, &tm_v, 0, kvh, r, bar_vfull);
-                    tma_load_3d(sm_v + kPanelBytes, &tm_v, 64, kvh, r, bar_vfull);
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (ok && j == last_partial) {
-                ok = warp_mbar_wait(bar_vfull, j & 1, abort_flag, 13);
-                if (ok) {
-                    const int first_bad = k_len - j * kBN;   // in (0, 128)
-                    for (int i = lane; i < (kBN - first_bad) * 16; i += 32) {
-                        const int r = first_bad + i / 16, c16 = i % 16;
-                        *reinterpret_cast<uint4*>(smem_gen + kOff4V + (c16 >> 3) * kPanelBytes + r * 128 + (c16 & 7) * 16) =
-                            make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_vfix);
-                }
-            }
-        }
-    } else if (warp == 8) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            auto issue_s = [&](int t, int j) {
-                const int s = j & 1;
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * kPanelBytes + (ks & 3) * 32;
-                    umma_ss(tmem_base + t * 128, make_smem_desc(sm_q + t * kTileBytes + off, 16, 1024),
-                            make_smem_desc(sm_k + s * kTileBytes + off, 16, 1024), p.idesc_s, ks > 0 ? 1u : 0u);
-                }
-                tc_commit(bar_sfull(t));
-            };
-            bool ok = mbar_wait(bar_q, 0, abort_flag, 21) && mbar_wait(bar_kfull(0), 0, abort_flag, 22);
-            if (ok) {
-                tc_fence_after();
-                issue_s(0, 0);
-                issue_s(1, 0);
-                tc_commit(bar_kempty(0));
-            }
-            for (int j = 0; j < num_kt && ok; ++j) {
-                if (j + 1 < num_kt) {   // next scores as soon as this step's scores have been read
-                    ok = mbar_wait(bar_kfull((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, 26);
-                    for (int t = 0; t < 2 && ok; ++t) {
-                        ok = mbar_wait(bar_sread(t), j & 1, abort_flag, 27);
-                        if (!ok) break;
-                        tc_fence_after();
-                        issue_s(t, j + 1);
-                    }
-                    if (ok) tc_commit(bar_kempty((j + 1) & 1));
-                }
-                if (ok) ok = mbar_wait(bar_vfull, j & 1, abort_flag, 23);
-                if (ok && j == last_partial) ok = mbar_wait(bar_vfix, 0, abort_flag, 24);
-                for (int t = 0; t < 2 && ok; ++t) {
-                    ok = mbar_wait(bar_pfull(t), j & 1, abort_flag, 25);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        umma_ss(tmem_base + 256 + t * 128,
-                                make_smem_desc(sm_p + t * kTileBytes + (kk >> 2) * kPanelBytes + (kk & 3) * 32, 16, 1024),
-                                make_smem_desc(sm_v + kk * 2048, kPanelBytes, 1024), p.idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    tc_commit(bar_odone(t));
-                    if (j == num_kt - 1) tc_commit(bar_ofinal(t));
-                }
-                if (ok) tc_commit(bar_vempty);
-            }
-        }
-    } else {
-        // ------------------------------------------------------------------ softmax warps (thread = row)
-        const int t = warp >> 2;
-        const int wq = warp & 3;
-        const int row = wq * 32 + lane;
-        const uint32_t t_s = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + t * 128;
-        const uint32_t t_o = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + 256 + t * 128;
-        const int lim = min(shift + q0 + row + 1, k_len);
-        unsigned char* p_panels = smem_gen + kOff4P + t * kTileBytes;
-        const uint32_t sread = bar_sread(t);
-        float m_ref = -INFINITY, l_run = 0.0f;
-        bool alive = true;
-        for (int j = 0; j < num_kt; ++j) {
-            alive = warp_mbar_wait(bar_sfull(t), j & 1, abort_flag, 31);
-            if (!alive) break;
-            tc_fence_after();
-            const int key0 = j * kBN;
-            const bool need_mask = key0 + kBN > min(shift + q0 + 1, k_len);
-            alive = softmax_row_to_smem<T>(t_s, t_o, p_panels, row, need_mask, key0, lim, p.scale_log2, j == 0, m_ref, l_run,
-                                           bar_odone(t), (j - 1) & 1, abort_flag, [&] {
-                                               tc_fence_before();
-                                               __syncwarp();
-                                               if (lane == 0) mbar_arrive(sread);   // the score columns may be overwritten
-                                           });
-            if (!alive) break;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_pfull(t));
-        }
-        if (alive) alive = warp_mbar_wait(bar_ofinal(t), 0, abort_flag, 32);
-        tc_fence_after();
-        if (alive) {
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            unsigned char* stage = smem_gen + kOff4Q + t * kTileBytes;   // Q_t is dead: every S MMA has completed
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(t_o + c * 32, r);
-                tc_wait_ld(); reg_fence32(r);
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint4 v;
-                    v.x = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv);
-                    v.y = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv);
-                    v.z = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv);
-                    v.w = ElemTraits<T>::pack2(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv);
-                    const int chunk = c * 4 + q4;
-                    *reinterpret_cast<uint4*>(stage + row * 256 + ((chunk ^ (row & 15)) << 4)) = v;
-                }
-            }
-            __syncwarp();
-            T* o0 = static_cast<T*>(p.out) + (static_cast<size_t>(qb + q0) * p.num_heads + head0 + t) * kHeadDim;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int r = wq * 32 + 2 * i + (lane >> 4), chunk = lane & 15;
-                if (r < rows_here) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4));
-                    *reinterpret_cast<uint4*>(o0 + r * out_stride + chunk * 8) = v;
-                }
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 8) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols2) : "memory");
-    }
-}
-
 // =================================================================================================
-// Version 5: version 4 made persistent.  One block per SM takes (query tile, head pair) items from a
+// The persistent head-pair kernel.  One block per SM takes (query tile, head pair) items from a
 // ticket counter, heaviest query tiles first, and keeps TMEM, barriers and the three warp roles alive
 // across items: while the softmax warps write one item's output (staged in the P buffer, which the
 // last P.V has finished with), the producer has already fetched the next item's Q and first K tiles and
@@ -971,16 +684,10 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // and last item of a block do.  All barrier phases are counted cumulatively over items.
 // =================================================================================================
 constexpr int kTicketSlots = 64;
-#ifndef NVK_TC5_ISSUERS
-#define NVK_TC5_ISSUERS 2
-#endif
-constexpr int kIssuers5 = NVK_TC5_ISSUERS;   // issuing warps: 1, or 2 (one per query tile)
-#ifndef NVK_TC5_REGS
-#define NVK_TC5_REGS 1
-#define NVK_TC5_REGS_LOW 56
-#define NVK_TC5_REGS_HIGH 224
-#endif
-constexpr int kThreads5 = NVK_TC5_REGS ? 384 : 320;   // three warpgroups (register reallocation works on whole warpgroups)
+constexpr int kIssuers5 = 2;        // issuing warps, one per query tile
+constexpr int kThreads5 = 384;      // three warpgroups (register reallocation works on whole warpgroups)
+constexpr int kRegsLow5 = 56;       // registers per thread of the third warpgroup after setmaxnreg.dec
+constexpr int kRegsHigh5 = 224;     // registers per thread of the two softmax warpgroups after setmaxnreg.inc
 __device__ unsigned int g_prefill_ticket[kTicketSlots];
 __device__ unsigned int g_prefill_done[kTicketSlots];
 
@@ -1045,8 +752,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     __shared__ Tc5Item s_ring[4];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    unsigned long long dbg_t0 = 0;
-    if (p.dbg_clk != nullptr && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(dbg_t0));
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t sm_q = smem_base + kOff4Q, sm_k = smem_base + kOff4K, sm_v = smem_base + kOff4V, sm_p = smem_base + kOff4P;
@@ -1090,9 +795,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // probabilities and the step's state without spilling.
 
     if (warp >= 8) {
-#if NVK_TC5_REGS
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(NVK_TC5_REGS_LOW));
-#endif
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsLow5));
     if (warp == 9) {
         // ------------------------------------------------------------------ ticket taker + TMA producer
         int n = 0;            // items published so far (all of them carry work)
@@ -1144,12 +847,12 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (!kind) break;
             const int head0 = 2 * pair;
             const int kvh = head0 * p.num_kv_heads / p.num_heads;
-            const int32_t* table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : nullptr;
+            const IndexArray table = p.block_tables ? p.block_tables + static_cast<int64_t>(seq) * p.max_blocks : IndexArray();
             auto key_row = [&](int key0) -> int {
                 if (table) {
-                    const int id = table[key0 / p.block_size];
+                    const int64_t id = table[key0 / p.block_size];
                     if (id < 0 || id >= p.num_cache_blocks) return static_cast<int>(p.key_rows);
-                    return id * p.block_size + key0 % p.block_size;
+                    return static_cast<int>(id) * p.block_size + key0 % p.block_size;
                 }
                 return static_cast<int>(g.kb) + key0;
             };
@@ -1277,9 +980,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
     }
     } else {
-#if NVK_TC5_REGS
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(NVK_TC5_REGS_HIGH));
-#endif
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kRegsHigh5));
         // ------------------------------------------------------------------ softmax warps (thread = row)
         const int t = warp >> 2;
         const int wq = warp & 3;
@@ -1355,14 +1056,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             }
             G += g.num_kt; ++n;
         }
-        if (p.dbg_clk != nullptr && tid == 0) {
-            unsigned long long t1;
-            unsigned int smid;
-            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
-            asm volatile("mov.u32 %0, %%smid;\n" : "=r"(smid));
-            p.dbg_clk[blockIdx.x * 4 + 0] = smid; p.dbg_clk[blockIdx.x * 4 + 1] = n;
-            p.dbg_clk[blockIdx.x * 4 + 2] = static_cast<long long>(dbg_t0); p.dbg_clk[blockIdx.x * 4 + 3] = static_cast<long long>(t1);
-        }
     }
     tc_fence_before();
     __syncthreads();
@@ -1417,21 +1110,6 @@ uint32_t make_idesc(bool bf16, bool b_mn_major) {
            (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-// Head-pair kernel used when the GQA group is even: the persistent one ("Version 5") unless NVK_PREFILL_IMPL=tc4
-// asks for its one-block-per-item form; NVK_PREFILL_IMPL=tc1 selects the single-tile kernel for every shape
-// (A/B comparisons; tests/test_gpu_parity.py runs the parity cases once under each setting).
-int tc_version() {
-    static const int v = [] {
-        const char* e = std::getenv("NVK_PREFILL_IMPL");
-        if (e != nullptr && e[0] == 't' && e[1] == 'c' && (e[2] == '1' || e[2] == '4')) return e[2] - '0';
-        return 5;
-    }();
-    return v;
-}
-
-float* g_debug_dump = nullptr;
-long long* g_debug_clock = nullptr;
-
 template <typename T>
 int launch_typed(const PrefillArgs& a, bool bf16) {
     static bool attr_done[64] = {};
@@ -1450,7 +1128,7 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
         !make_map(&tv, paged ? a.v_cache : a.v, key_rows, a.num_kv_heads, bf16))
         return fail(NVK_ERR_CUDA, "prefill attention (tcgen05): cuTensorMapEncodeTiled failed");
     TcParams p{};
-    p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.block_tables = a.block_tables; p.out = a.out; p.dbg = g_debug_dump; p.dbg_clk = g_debug_clock;
+    p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.block_tables = a.block_tables; p.out = a.out;
     p.num_seqs = a.cu_q ? a.num_seqs : 1; p.total_q = a.total_q; p.total_k = a.total_k; p.max_blocks = a.max_blocks;
     p.key_rows = key_rows; p.num_cache_blocks = a.num_cache_blocks;
     p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.block_size = paged ? a.block_size : 1;
@@ -1460,7 +1138,7 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
     const int64_t tiles = (a.total_q + kBM - 1) / kBM + (a.cu_q ? a.num_seqs : 0);
     if (tiles > 65535) return fail(NVK_ERR_UNSUPPORTED, "prefill attention (tcgen05): too many query tiles");
     const int group = a.num_heads / a.num_kv_heads;
-    if (group % 2 == 0 && tc_version() == 5) {   // persistent blocks, one per SM, items from a ticket counter
+    if (group % 2 == 0) {   // pairs of query heads that share a KV head: persistent blocks, one per SM, items from a ticket counter
         static bool attr5_done[64] = {};
         static int sm_count[64] = {};
         static std::atomic<unsigned int> launch_seq{0};
@@ -1483,17 +1161,7 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
         prefill_tc5_kernel<T><<<blocks, kThreads5, kSmemBytes4, a.stream>>>(tq, tk, tv, pp);
         return check_launch("prefill_tc5_kernel launch");
     }
-    if (group % 2 == 0 && tc_version() == 4) {   // pairs of query heads that share a KV head, P through shared memory
-        static bool attr4_done[64] = {};
-        if (device >= 0 && device < 64 && !attr4_done[device]) {
-            const cudaError_t e = cudaFuncSetAttribute(prefill_tc4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes4);
-            if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill attention (tcgen05 v4): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            attr4_done[device] = true;
-        }
-        const dim3 grid4(a.num_heads / 2, static_cast<unsigned>(tiles));
-        prefill_tc4_kernel<T><<<grid4, kThreads4, kSmemBytes4, a.stream>>>(tq, tk, tv, p);
-        return check_launch("prefill_tc4_kernel launch");
-    }
+    // odd group sizes: one block per (query tile, head)
     const dim3 grid(a.num_heads, static_cast<unsigned>(tiles));
     prefill_tc_kernel<T><<<grid, kThreads, kSmemBytes, a.stream>>>(tq, tk, tv, p);
     return check_launch("prefill_tc_kernel launch");
@@ -1502,11 +1170,6 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
 }  // namespace
 
 bool prefill_tc_supported(const PrefillArgs& a) {
-    static const int mode = [] {   // NVK_PREFILL_IMPL=mma keeps the mma.sync kernel (A/B comparisons)
-        const char* e = std::getenv("NVK_PREFILL_IMPL");
-        return (e != nullptr && e[0] == 'm') ? 0 : 1;
-    }();
-    if (mode == 0) return false;
     if (a.dtype != NVK_F16 && a.dtype != NVK_BF16) return false;
     if (a.head_dim != kHeadDim) return false;
     if (!aligned_to(a.q, 16) || !aligned_to(a.out, 16)) return false;
@@ -1528,13 +1191,19 @@ int launch_prefill_tc(const PrefillArgs& a) {
 
 }  // namespace nvk
 
-// Debug hooks (declared in csrc/nvk_debug.h, not part of the product ABI).
-extern "C" void nvk_debug_set_prefill_dump(float* device_buffer) { nvk::g_debug_dump = device_buffer; }
-extern "C" void nvk_debug_set_prefill_clock(long long* device_buffer) { nvk::g_debug_clock = device_buffer; }
-extern "C" int nvk_debug_take_device_error(void) {
-    int v = 0;
-    cudaMemcpyFromSymbol(&v, nvk::g_tc_error, sizeof(int));
-    const int zero = 0;
-    cudaMemcpyToSymbol(nvk::g_tc_error, &zero, sizeof(int));
-    return v;
+extern "C" int nvk_prefill_status(void* stream, int* status) {
+    using namespace nvk;
+    if (!status) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill status: null argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int word = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(&word, g_tc_error, sizeof(int), 0, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess && word != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbolAsync(g_tc_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    }
+    if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill status: %s", cudaGetErrorString(e));
+    *status = word;
+    return NVK_OK;
 }

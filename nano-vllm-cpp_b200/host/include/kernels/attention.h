@@ -15,7 +15,11 @@ void launch_prefill_attention_paged(const Tensor& query, const Tensor* cu_seqlen
                                     cudaStream_t stream = nullptr);
 
 // No allocator in this signature: split-K scratch comes from the library's built-in array
-// (nvk_decode_attention_paged_static) when the problem fits it, otherwise the call runs unsplit.
+// (nvk_decode_attention_paged_static) when the problem fits nvk_decode_attention_static_scratch_bytes(), otherwise the
+// call runs unsplit.  Two rules follow from sharing that array, neither of which the reference's function has:
+// calls whose kernels may overlap on one device (different streams) race on it and must be serialised by the caller,
+// and the first call on a device looks the array's address up, which must not happen inside a stream capture -- make
+// one call (or construct an Attention layer and run a warm-up step, as a graph runner does anyway) before capturing.
 void launch_decode_attention_paged(const Tensor& query, const Tensor& k_cache, const Tensor& v_cache,
                                    const Tensor& context_lens, const Tensor& block_tables, int num_kv_heads,
                                    int head_dim, int block_size, float scale, Tensor& output,
@@ -26,5 +30,10 @@ void launch_decode_attention_paged_int8(const Tensor& query, const Tensor& k_cac
                                         const Tensor& k_scale, const Tensor& v_scale, const Tensor& context_lens,
                                         const Tensor& block_tables, int num_kv_heads, int head_dim, int block_size,
                                         float scale, Tensor& output, cudaStream_t stream = nullptr);
+
+// The tensor-core prefill kernel bounds every internal wait; a launch whose wait ran out leaves rows unwritten and
+// records the fact on the device.  This call synchronises `stream`, and throws std::runtime_error if any prefill launch
+// since the previous call gave up (call it where the engine synchronises anyway, e.g. after a prefill step).
+void throw_if_prefill_error(cudaStream_t stream = nullptr);
 
 }  // namespace nano_vllm

@@ -50,6 +50,31 @@ private:
     std::map<std::pair<int, size_t>, std::vector<void*>> free_lists_;
 };
 
+// Bump allocator over one device range reserved up front: nothing it hands out is ever freed individually, reset()
+// rewinds it.  A CUDA graph is captured with one of these in place of the caching allocator, so that no cudaMalloc runs
+// under capture and a warm-up pass and the capture pass receive identical addresses (the role of ScratchAllocator in
+// src/engine/model_runner.cpp:57-100 of the reference).  Copies and memsets are forwarded to `delegate`.
+class ArenaAllocator final : public DeviceAllocator {
+public:
+    ArenaAllocator(size_t capacity, Device device, DeviceAllocator& delegate);
+
+    Memory::Ptr allocate(size_t bytes, Device device) override;   // 256-byte aligned; throws std::runtime_error when full
+    void memset_async(void* ptr, int value, size_t bytes, cudaStream_t stream) const override;
+    void copy_to_device_async(void* dst, const void* src, size_t bytes, cudaStream_t stream) const override;
+    void copy_to_host_async(void* dst, const void* src, size_t bytes, cudaStream_t stream) const override;
+    void synchronize_stream(cudaStream_t stream) const override;
+
+    void reset() { offset_ = 0; }
+    size_t used() const { return offset_; }
+    size_t high_water() const { return high_water_; }
+
+private:
+    Memory::Ptr arena_;
+    Device device_;
+    DeviceAllocator& delegate_;
+    size_t offset_ = 0, high_water_ = 0;
+};
+
 // Page-locked host staging buffer (metadata upload, src/engine/model_runner.cpp:805-831).
 class PinnedHostBuffer {
 public:

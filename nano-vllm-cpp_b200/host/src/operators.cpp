@@ -72,10 +72,18 @@ int code(ScalarType t) { return static_cast<int>(t); }
 
 const int32_t* int32_data(const char* name, const Tensor& t) {
     ensure_cuda_tensor(name, t);
-    if (t.dtype() == ScalarType::kInt64)
-        throw std::invalid_argument(std::string(name) + " must be int32 (the engine produces int32 metadata)");
-    if (t.dtype() != ScalarType::kInt32) throw std::invalid_argument(std::string(name) + " must be int32 or int64");
+    if (t.dtype() != ScalarType::kInt32) throw std::invalid_argument(std::string(name) + " must be int32");
     return t.data_as<int32_t>();
+}
+
+// An index tensor of either width (the reference's attention kernels take int32 or int64 for each of cu_seqlens_q,
+// cu_seqlens_k, context_lens and block_tables on its own, src/kernels/attention.cu:644-660, :708-735).
+struct IndexRef { const void* ptr; int dtype; };
+IndexRef index_data(const char* name, const Tensor& t) {
+    ensure_cuda_tensor(name, t);
+    if (t.dtype() != ScalarType::kInt32 && t.dtype() != ScalarType::kInt64)
+        throw std::invalid_argument(std::string(name) + " must be int32 or int64");
+    return {t.data(), code(t.dtype())};
 }
 
 int64_t cache_blocks(const Tensor& cache, int block_size, int num_kv_heads, int head_dim) {
@@ -194,8 +202,8 @@ void decode_common(const Tensor& query, const Tensor& k_cache, const Tensor& v_c
     ensure_cuda_tensor("v_cache", v_cache);
     ensure_same_dtype("query", query, "k_cache", k_cache);
     ensure_same_dtype("query", query, "v_cache", v_cache);
-    const int32_t* lens = int32_data("context_lens", context_lens);
-    const int32_t* tables = int32_data("block_tables", block_tables);
+    const IndexRef lens = index_data("context_lens", context_lens);
+    const IndexRef tables = index_data("block_tables", block_tables);
     if (block_tables.dim() != 2) throw std::invalid_argument("block_tables must be [batch, max_blocks]");
     const int64_t batch = query.sizes()[0];
     const int heads = static_cast<int>(query.sizes()[1]);
@@ -204,22 +212,24 @@ void decode_common(const Tensor& query, const Tensor& k_cache, const Tensor& v_c
     if (allocator != nullptr) {
         const size_t need = nvk_decode_attention_workspace_bytes(batch, heads, num_kv_heads, head_dim, max_blocks, block_size);
         Memory::Ptr scratch = need > 0 ? allocator->allocate(need, query.device()) : nullptr;
-        throw_on_nvk_status(nvk_decode_attention_paged(query.data(), k_cache.data(), v_cache.data(), lens, tables, batch,
-                                                       max_blocks, blocks, heads, num_kv_heads, head_dim, block_size,
-                                                       scale, output.data(), code(query.dtype()),
-                                                       scratch ? scratch->data() : nullptr, need, stream));
+        throw_on_nvk_status(nvk_decode_attention_paged(query.data(), k_cache.data(), v_cache.data(), lens.ptr, lens.dtype,
+                                                       tables.ptr, tables.dtype, batch, max_blocks, blocks, heads,
+                                                       num_kv_heads, head_dim, block_size, scale, output.data(),
+                                                       code(query.dtype()), scratch ? scratch->data() : nullptr, need, stream));
         return;   // the scratch block returns to the allocator's cache; stream order keeps it valid for this launch
     }
     const size_t need = nvk_decode_attention_workspace_bytes(batch, heads, num_kv_heads, head_dim, max_blocks, block_size);
-    if (need > 0 && need <= (size_t(32) << 20)) {
-        throw_on_nvk_status(nvk_decode_attention_paged_static(query.data(), k_cache.data(), v_cache.data(), lens, tables,
-                                                              batch, max_blocks, blocks, heads, num_kv_heads, head_dim,
-                                                              block_size, scale, output.data(), code(query.dtype()), stream));
+    if (need > 0 && need <= nvk_decode_attention_static_scratch_bytes()) {
+        throw_on_nvk_status(nvk_decode_attention_paged_static(query.data(), k_cache.data(), v_cache.data(), lens.ptr,
+                                                              lens.dtype, tables.ptr, tables.dtype, batch, max_blocks,
+                                                              blocks, heads, num_kv_heads, head_dim, block_size, scale,
+                                                              output.data(), code(query.dtype()), stream));
         return;
     }
-    throw_on_nvk_status(nvk_decode_attention_paged(query.data(), k_cache.data(), v_cache.data(), lens, tables, batch,
-                                                   max_blocks, blocks, heads, num_kv_heads, head_dim, block_size, scale,
-                                                   output.data(), code(query.dtype()), nullptr, 0, stream));
+    throw_on_nvk_status(nvk_decode_attention_paged(query.data(), k_cache.data(), v_cache.data(), lens.ptr, lens.dtype,
+                                                   tables.ptr, tables.dtype, batch, max_blocks, blocks, heads, num_kv_heads,
+                                                   head_dim, block_size, scale, output.data(), code(query.dtype()), nullptr,
+                                                   0, stream));
 }
 
 }  // namespace
@@ -255,8 +265,8 @@ void launch_decode_attention_paged_int8(const Tensor& query, const Tensor& k_cac
         throw std::invalid_argument("int8 decode attention requires int8 caches");
     if (k_scale.dtype() != ScalarType::kFloat16 || v_scale.dtype() != ScalarType::kFloat16)
         throw std::invalid_argument("int8 decode attention requires float16 scales");
-    if (context_lens.dtype() != ScalarType::kInt32 || block_tables.dtype() != ScalarType::kInt32)
-        throw std::invalid_argument("context_lens and block_tables must be int32");
+    const IndexRef lens = index_data("context_lens", context_lens);
+    const IndexRef tables = index_data("block_tables", block_tables);
     if (block_tables.dim() != 2 || block_tables.sizes()[0] != query.sizes()[0])
         throw std::invalid_argument("block_tables must be [batch, max_blocks]");
     if (static_cast<int64_t>(context_lens.numel()) != query.sizes()[0])
@@ -273,9 +283,8 @@ void launch_decode_attention_paged_int8(const Tensor& query, const Tensor& k_cac
         throw std::invalid_argument("k_scale and v_scale must hold one value per cache row and KV head");
     // no allocator in this signature (as in the reference): the call runs without split-K scratch
     throw_on_nvk_status(nvk_decode_attention_paged_int8(
-        query.data(), k_cache.data(), v_cache.data(), k_scale.data(), v_scale.data(),
-        static_cast<const int32_t*>(context_lens.data()), static_cast<const int32_t*>(block_tables.data()), batch, max_blocks,
-        blocks, heads, num_kv_heads, head_dim, block_size, scale, output.data(), code(query.dtype()), nullptr, 0, stream));
+        query.data(), k_cache.data(), v_cache.data(), k_scale.data(), v_scale.data(), lens.ptr, lens.dtype, tables.ptr,
+        tables.dtype, batch, max_blocks, blocks, heads, num_kv_heads, head_dim, block_size, scale, output.data(), code(query.dtype()), nullptr, 0, stream));
 }
 
 // ---- prefill ------------------------------------------------------------------------------------------
@@ -288,11 +297,12 @@ void launch_prefill_attention_dense(const Tensor& query, const Tensor* cu_seqlen
     ensure_same_dtype("query", query, "key", key);
     ensure_same_dtype("query", query, "value", value);
     const bool varlen = cu_seqlens_q != nullptr && cu_seqlens_k != nullptr;   // either missing: one sequence
-    const int32_t* cq = varlen ? int32_data("cu_seqlens_q", *cu_seqlens_q) : nullptr;
-    const int32_t* ck = varlen ? int32_data("cu_seqlens_k", *cu_seqlens_k) : nullptr;
+    const IndexRef cq = varlen ? index_data("cu_seqlens_q", *cu_seqlens_q) : IndexRef{nullptr, NVK_I32};
+    const IndexRef ck = varlen ? index_data("cu_seqlens_k", *cu_seqlens_k) : IndexRef{nullptr, NVK_I32};
     const int64_t seqs = varlen ? static_cast<int64_t>(cu_seqlens_q->numel()) - 1 : 1;
-    throw_on_nvk_status(nvk_prefill_attention_varlen(query.data(), key.data(), value.data(), nullptr, nullptr, cq, ck,
-                                                     nullptr, seqs, query.sizes()[0], key.sizes()[0], 0, 0, 0,
+    throw_on_nvk_status(nvk_prefill_attention_varlen(query.data(), key.data(), value.data(), nullptr, nullptr, cq.ptr,
+                                                     cq.dtype, ck.ptr, ck.dtype, nullptr, NVK_I32, seqs, query.sizes()[0],
+                                                     key.sizes()[0], 0, 0, 0,
                                                      static_cast<int>(query.sizes()[1]), num_kv_heads, head_dim, 1, scale,
                                                      output.data(), code(query.dtype()), stream));
 }
@@ -309,13 +319,22 @@ void launch_prefill_attention_paged(const Tensor& query, const Tensor* cu_seqlen
     ensure_same_dtype("query", query, "k_cache", k_cache);
     if (block_tables.defined() && block_tables.dim() != 2)
         throw std::invalid_argument("block_tables must be [num_seqs, max_blocks]");
-    const int32_t* tables = int32_data("block_tables", block_tables);
+    const IndexRef tables = index_data("block_tables", block_tables);
+    const IndexRef cq = index_data("cu_seqlens_q", *cu_seqlens_q), ck = index_data("cu_seqlens_k", *cu_seqlens_k);
     throw_on_nvk_status(nvk_prefill_attention_varlen(
-        query.data(), nullptr, nullptr, k_cache.data(), v_cache.data(), int32_data("cu_seqlens_q", *cu_seqlens_q),
-        int32_data("cu_seqlens_k", *cu_seqlens_k), tables, static_cast<int64_t>(cu_seqlens_q->numel()) - 1,
+        query.data(), nullptr, nullptr, k_cache.data(), v_cache.data(), cq.ptr, cq.dtype, ck.ptr, ck.dtype, tables.ptr,
+        tables.dtype, static_cast<int64_t>(cu_seqlens_q->numel()) - 1,
         query.sizes()[0], 0, block_tables.sizes()[1], cache_blocks(k_cache, block_size, num_kv_heads, head_dim), 0,
         static_cast<int>(query.sizes()[1]), num_kv_heads, head_dim, block_size, scale, output.data(),
         code(query.dtype()), stream));
+}
+
+void throw_if_prefill_error(cudaStream_t stream) {
+    int word = 0;
+    throw_on_nvk_status(nvk_prefill_status(stream, &word));
+    if (word != 0)
+        throw std::runtime_error("prefill attention: a bounded wait inside the tensor-core kernel ran out (code " +
+                                 std::to_string(word) + "); output rows of that launch are incomplete");
 }
 
 bool flash_attn_available() { return true; }

@@ -102,6 +102,33 @@ void CudaAllocator::synchronize_stream(cudaStream_t stream) const {
     throw_if_cuda_error(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
 }
 
+// ---- ArenaAllocator -------------------------------------------------------------------------------
+ArenaAllocator::ArenaAllocator(size_t capacity, Device device, DeviceAllocator& delegate)
+    : arena_(delegate.allocate(capacity, device)), device_(device), delegate_(delegate) {}
+
+Memory::Ptr ArenaAllocator::allocate(size_t bytes, Device device) {
+    if (device != device_) throw std::invalid_argument("ArenaAllocator serves one device only");
+    const size_t rounded = (bytes + 255) / 256 * 256;
+    if (offset_ + rounded > arena_->bytes())
+        throw std::runtime_error("ArenaAllocator: " + std::to_string(offset_ + rounded) + " bytes needed, " +
+                                 std::to_string(arena_->bytes()) + " reserved");
+    void* ptr = static_cast<char*>(arena_->data()) + offset_;
+    offset_ += rounded;
+    if (offset_ > high_water_) high_water_ = offset_;
+    return Memory::make_borrowed(ptr, bytes, device_);
+}
+
+void ArenaAllocator::memset_async(void* ptr, int value, size_t bytes, cudaStream_t stream) const {
+    delegate_.memset_async(ptr, value, bytes, stream);
+}
+void ArenaAllocator::copy_to_device_async(void* dst, const void* src, size_t bytes, cudaStream_t stream) const {
+    delegate_.copy_to_device_async(dst, src, bytes, stream);
+}
+void ArenaAllocator::copy_to_host_async(void* dst, const void* src, size_t bytes, cudaStream_t stream) const {
+    delegate_.copy_to_host_async(dst, src, bytes, stream);
+}
+void ArenaAllocator::synchronize_stream(cudaStream_t stream) const { delegate_.synchronize_stream(stream); }
+
 // ---- PinnedHostBuffer -----------------------------------------------------------------------------
 PinnedHostBuffer::PinnedHostBuffer(size_t bytes) : bytes_(bytes) {
     if (bytes_ > 0) throw_if_cuda_error(cudaMallocHost(&data_, bytes_), "cudaMallocHost");

@@ -6,7 +6,7 @@ reference's unmodified attention.cu / kvcache.cu / split_qkv.cu compiled for sm_
 
     python tests/golden/make_golden.py [output_dir]
 
-Inputs are regenerated from seeds by ``nano-vllm-cpp_b200/workloads.py`` (the ``CASES`` table below is the
+Inputs are regenerated from seeds by ``benchmarks/workloads.py`` (the ``CASES`` table below is the
 single source of truth, imported by the tests), so a fixture stores only the reference's outputs plus a
 checksum of the inputs it was produced from.  Every case is small: the whole directory is a few hundred KB.
 """
@@ -49,7 +49,7 @@ def workloads():
     import __graft_entry__ as entry
     import importlib
     entry.load_package()
-    return importlib.import_module(entry.PKG_NAME + ".workloads")
+    return importlib.import_module("benchmarks.workloads")
 
 
 def make_inputs(name):

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol(built):
 
 def test_abi_version_and_error_channel(built):
     lib = built.lib()
-    assert lib.nvk_abi_version() == 1
+    assert lib.nvk_abi_version() == 2
     # invalid arguments are rejected on the host, before any CUDA call
     rc = lib.nvk_store_kvcache(None, None, None, None, None, 3, ctypes.c_int64(1), ctypes.c_int64(4),
                                ctypes.c_int64(4), 2, None)
@@ -46,10 +46,22 @@ def test_abi_version_and_error_channel(built):
     rc = lib.nvk_store_kvcache(one, one, one, one, one, 2, ctypes.c_int64(1), ctypes.c_int64(4),
                                ctypes.c_int64(4), 2, None)
     assert rc == built.ERR_INVALID_ARGUMENT and b"int32 or int64" in lib.nvk_last_error()
-    rc = lib.nvk_decode_attention_paged(one, one, one, one, one, ctypes.c_int64(1), ctypes.c_int64(1),
+    rc = lib.nvk_decode_attention_paged(one, one, one, one, 3, one, 3, ctypes.c_int64(1), ctypes.c_int64(1),
                                         ctypes.c_int64(1), 3, 2, 128, 256, ctypes.c_float(1.0), one, 1, None,
                                         ctypes.c_size_t(0), None)
     assert rc == built.ERR_INVALID_ARGUMENT and b"divisible" in lib.nvk_last_error()
+    # index tensors carry a dtype code each: int32 (3) or int64 (4), nothing else
+    rc = lib.nvk_decode_attention_paged(one, one, one, one, 3, one, 2, ctypes.c_int64(1), ctypes.c_int64(1),
+                                        ctypes.c_int64(1), 4, 2, 128, 256, ctypes.c_float(1.0), one, 1, None,
+                                        ctypes.c_size_t(0), None)
+    assert rc == built.ERR_INVALID_ARGUMENT and b"int32 or int64" in lib.nvk_last_error()
+    rc = lib.nvk_prefill_attention_varlen(one, None, None, one, one, one, 4, one, 5, one, 3, ctypes.c_int64(1),
+                                          ctypes.c_int64(1), ctypes.c_int64(0), ctypes.c_int64(1), ctypes.c_int64(1), 0,
+                                          4, 2, 128, 256, ctypes.c_float(1.0), one, 1, None)
+    assert rc == built.ERR_INVALID_ARGUMENT and b"int32 or int64" in lib.nvk_last_error()
+    rc = lib.nvk_prefill_status(None, None)
+    assert rc == built.ERR_INVALID_ARGUMENT
+    assert built.decode_attention_static_scratch_bytes() == 32 << 20
 
 
 def test_workspace_size_depends_only_on_host_known_sizes(built):

@@ -17,7 +17,7 @@ def mods():
     import torch
     nvk = entry.load_package()
     nvk.lib()
-    get = lambda n: importlib.import_module(entry.PKG_NAME + "." + n)  # noqa: E731
+    get = lambda n: importlib.import_module("benchmarks." + n)  # noqa: E731
     return torch, nvk, get("e2e_model"), get("e2e_schedule"), get("e2e_bench")
 
 

@@ -11,7 +11,7 @@ import __graft_entry__ as entry
 @pytest.fixture(scope="module")
 def sch():
     entry.load_package()
-    return importlib.import_module(entry.PKG_NAME + ".e2e_schedule")
+    return importlib.import_module("benchmarks.e2e_schedule")
 
 
 def test_requests_are_seeded_and_in_range(sch):

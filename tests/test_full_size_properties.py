@@ -27,7 +27,7 @@ def _close(a, b):
 def decode_full():
     import torch
     entry.load_package()
-    wl = importlib.import_module(entry.PKG_NAME + ".workloads")
+    wl = importlib.import_module("benchmarks.workloads")
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(77)
     ctx = rng.integers(1024, 8193, size=256).astype(np.int32)
@@ -151,7 +151,7 @@ def test_int8_cache_agrees_with_the_16_bit_cache_at_full_size(decode_full):
 def prefill_full():
     import torch
     entry.load_package()
-    kb = importlib.import_module(entry.PKG_NAME + ".kernel_bench")
+    kb = importlib.import_module("benchmarks.kernel_bench")
     dev = torch.device("cuda:0")
     w = kb.make_prefill_inputs(torch, dev, 2025)
     lib = nvk()

@@ -368,16 +368,145 @@ def test_fused_split_norm_rope_store_matches_oracle(num_q_heads, num_kv_heads, h
         assert (got == ref).mean() > 0.98
 
 
-@pytest.mark.gpu
-@pytest.mark.parametrize("impl", ["tc4", "tc1"])
-def test_prefill_parity_under_the_other_tensor_core_kernels(impl):
-    """The library picks its prefill kernel once per process (NVK_PREFILL_IMPL): re-run this file's prefill cases in
-    a child process under each alternative, so the one-block-per-item and the single-tile kernels stay covered."""
-    import os
-    import subprocess
-    import sys
-    env = dict(os.environ, NVK_PREFILL_IMPL=impl)
-    res = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-m", "gpu", "-x", "-k",
-                          "prefill and not under_the_other"], env=env, capture_output=True, text=True, timeout=600,
-                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+# ------------------------------------------------------- the kernels the library picks by shape
+
+@pytest.mark.parametrize("num_heads,num_kv_heads", [(3, 3), (6, 2), (5, 1)])
+def test_prefill_odd_gqa_groups_take_the_single_tile_tensor_core_kernel(num_heads, num_kv_heads):
+    """Query-head groups of odd size (1, 3, 5) cannot be split into head pairs: the one-block-per-(tile, head)
+    tcgen05 kernel serves them, paged with prefixes and dense."""
+    wl = workloads()
+    p = wl.make_prefill_workload([140, 1, 260, 129], [256, 512, 0, 0], num_heads, num_kv_heads, 128, 256, seed=31)
+    got, ref = _run_prefill(p, "bf16", num_kv_heads, 128, 256, paged=True, store_first=True)
+    assert not np.isnan(got).any()
+    assert_attention_close(got, ref)
+    d = wl.make_prefill_workload([70, 200, 1], [0, 0, 0], num_heads, num_kv_heads, 128, 256, seed=32, paged=False)
+    got, ref = _run_prefill(d, "f16" if num_heads == 5 else "bf16", num_kv_heads, 128, 256, paged=False)
+    assert_attention_close(got, ref)
+
+
+@pytest.mark.parametrize("block_size", [64, 192])
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_prefill_small_cache_blocks_take_the_mma_sync_kernel(block_size, dtype):
+    """A 128-key TMA tile must not straddle a cache block, so caches whose block size is a multiple of 64 but not of
+    128 go to the mma.sync kernel (64-key tiles): prefix hits, a chunk that starts mid-block, a one-token sequence."""
+    wl = workloads()
+    p = wl.make_prefill_workload([150, 1, 64, 333], [block_size, 3 * block_size, 37, 0], 8, 2, 128, block_size, seed=33)
+    if dtype == "f16":
+        for k in ("q", "k_cache", "v_cache", "k_new", "v_new"):
+            p[k] = round_f16(p[k])
+    got, ref = _run_prefill(p, dtype, 2, 128, block_size, paged=True, store_first=True)
+    assert not np.isnan(got).any()
+    assert_attention_close(got, ref)
+
+
+# -------------------------------------------------------------------------------- int64 index tensors
+
+def test_int64_index_tensors_give_the_same_bits_as_int32():
+    """The reference's kernels take int32 or int64 for each of cu_seqlens_q, cu_seqlens_k, context_lens and
+    block_tables on its own (src/kernels/attention.cu:644-660, :708-735); so does the C ABI.  Mixed widths, every
+    kernel family: tensor-core decode (split and unsplit), the general decode path, int8 decode, tcgen05 prefill
+    (head pairs and single tile), the mma.sync prefill and the general prefill path."""
+    wl = workloads()
+    bf = torch.bfloat16
+    L = torch.int64
+    # decode: tensor-core path with and without workspace, general path (fp32)
+    for dtype, hq, hkv, d, bs in (("bf16", 8, 2, 128, 256), ("f32", 4, 2, 64, 16)):
+        w = wl.make_decode_workload(6, hq, hkv, d, bs, 1, 900, seed=41, rounded=(dtype == "bf16"))
+        td = _dt(dtype)
+        q, kc, vc = to_dev(w["q"], td), to_dev(w["k_cache"], td), to_dev(w["v_cache"], td)
+        ctx, bt = to_dev(w["context_lens"]), to_dev(w["block_tables"])
+        ws_bytes = nvk().decode_attention_workspace_bytes(6, hq, hkv, d, bt.shape[1], bs)
+        for ws in (None, torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device="cuda")):
+            outs = []
+            for c, t in ((ctx, bt), (ctx.to(L), bt), (ctx, bt.to(L)), (ctx.to(L), bt.to(L))):
+                out = torch.full_like(q, float("nan"))
+                nvk().launch_decode_attention_paged(q, kc, vc, c, t, hkv, d, bs, w["scale"], out, ws)
+                outs.append(out)
+            torch.cuda.synchronize()
+            assert all(torch.equal(outs[0], o) for o in outs[1:])
+    # prefill: head pairs (8/2), single tile (3/3), mma.sync (block 64), general path (head_dim 64)
+    for hq, hkv, d, bs in ((8, 2, 128, 256), (3, 3, 128, 256), (8, 2, 128, 64), (4, 2, 64, 16)):
+        p = wl.make_prefill_workload([130, 1, 70], [bs, 2 * bs, 0], hq, hkv, d, bs, seed=42)
+        q, kc, vc = to_dev(p["q"], bf), to_dev(p["k_cache"], bf), to_dev(p["v_cache"], bf)
+        cq, ck, bt = to_dev(p["cu_q"]), to_dev(p["cu_k"]), to_dev(p["block_tables"])
+        outs = []
+        for a, b, t in ((cq, ck, bt), (cq.to(L), ck, bt), (cq, ck.to(L), bt.to(L)), (cq.to(L), ck.to(L), bt.to(L))):
+            out = torch.full_like(q, float("nan"))
+            nvk().launch_prefill_attention_paged(q, a, kc, vc, b, t, hkv, d, bs, p["scale"], out)
+            outs.append(out)
+        torch.cuda.synchronize()
+        assert not torch.isnan(outs[0].float()).any()
+        assert all(torch.equal(outs[0], o) for o in outs[1:])
+    with pytest.raises(ValueError):
+        nvk().launch_decode_attention_paged(q, kc, vc, ctx.to(torch.int16), bt, 2, 64, 16, 1.0, torch.empty_like(q))
+
+
+def test_decode_context_longer_than_the_block_table_is_clamped():
+    """context_lens[b] beyond max_blocks * block_size cannot be addressed by the table row: the kernels clamp it
+    (no read past the row, no read of another row's partial results) and the output equals the clamped result."""
+    wl = workloads()
+    bf = torch.bfloat16
+    w = wl.make_decode_workload(4, 8, 2, 128, 256, 700, 1000, seed=43)
+    cap = w["block_tables"].shape[1] * 256
+    q, kc, vc, bt = to_dev(w["q"], bf), to_dev(w["k_cache"], bf), to_dev(w["v_cache"], bf), to_dev(w["block_tables"])
+    clamped = w["context_lens"].copy()
+    clamped[1] = cap
+    wild = clamped.copy()
+    wild[1] = cap + 5000
+    ws = torch.empty(max(16, nvk().decode_attention_workspace_bytes(4, 8, 2, 128, bt.shape[1], 256)), dtype=torch.uint8, device="cuda")
+    for workspace in (None, ws):
+        a, b = torch.full_like(q, float("nan")), torch.full_like(q, float("nan"))
+        nvk().launch_decode_attention_paged(q, kc, vc, to_dev(clamped), bt, 2, 128, 256, w["scale"], a, workspace)
+        nvk().launch_decode_attention_paged(q, kc, vc, to_dev(wild), bt, 2, 128, 256, w["scale"], b, workspace)
+        torch.cuda.synchronize()
+        assert torch.isfinite(b.float()).all()
+        assert torch.equal(a, b)
+
+
+def test_prefill_status_is_zero_after_normal_launches():
+    """Every tensor-core prefill launch above completed inside its bounded waits: the per-device error word is clear,
+    and reading it clears it (plumbing check; a time-out itself is never provoked on a GPU)."""
+    assert nvk().prefill_status() == 0
+    assert nvk().prefill_status() == 0
+
+
+# -------------------------------------------- the two forms of the prologue used by the unfused route
+
+@pytest.mark.parametrize("num_q_heads,num_kv_heads,head_dim", [(32, 8, 128), (4, 1, 128), (6, 2, 64)])
+def test_prologue_identity_slots_and_no_norm(num_q_heads, num_kv_heads, head_dim):
+    """slot_mapping = None writes k / v of row r to row r of plain [rows, Hkv, D] tensors -- bit-identical to the fused
+    form with slots 0 .. rows-1; norm weights = None skips the RMSNorm -- bit-identical to the oracle with unit weights
+    and the head's own rms multiplied back ... which is not expressible, so it is checked against a torch fp32 RoPE."""
+    wl = workloads()
+    rows, max_pos = 45, 200
+    w = wl.make_prologue_workload(rows, num_q_heads, num_kv_heads, head_dim, rows, max_pos, seed=14)
+    table = to_dev(oracle.build_cos_sin_cache(max_pos, head_dim, w["rope_base"]))
+    bf = torch.bfloat16
+    qkv, pos = to_dev(w["qkv"], bf), to_dev(w["positions"])
+    qw, kw = to_dev(w["q_norm_weight"], bf), to_dev(w["k_norm_weight"], bf)
+    outs = []
+    for slots in (to_dev(np.arange(rows, dtype=np.int32)), None):
+        k = torch.zeros(rows, num_kv_heads, head_dim, dtype=bf, device="cuda")
+        v = torch.zeros_like(k)
+        q = torch.empty(rows, num_q_heads, head_dim, dtype=bf, device="cuda")
+        nvk().fused_split_norm_rope_store(qkv, pos, qw, kw, w["eps"], table, slots, k, v, num_q_heads, num_kv_heads, head_dim, q)
+        outs.append((q, k, v))
+    torch.cuda.synchronize()
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+    # no norm: plain neox RoPE of the bf16 inputs, computed in fp32 and rounded once
+    k = torch.zeros(rows, num_kv_heads, head_dim, dtype=bf, device="cuda")
+    v = torch.zeros_like(k)
+    q = torch.empty(rows, num_q_heads, head_dim, dtype=bf, device="cuda")
+    nvk().fused_split_norm_rope_store(qkv, pos, None, None, w["eps"], table, None, k, v, num_q_heads, num_kv_heads, head_dim, q)
+    torch.cuda.synchronize()
+    x = qkv.float().view(rows, num_q_heads + 2 * num_kv_heads, head_dim)
+    cs = table[pos.long()]                                     # [rows, D] = [cos | sin]
+    cos, sin = cs[:, None, :head_dim // 2], cs[:, None, head_dim // 2:]
+    lo, hi = x[..., :head_dim // 2], x[..., head_dim // 2:]
+    rot = torch.cat([lo * cos - hi * sin, hi * cos + lo * sin], dim=-1)
+    want_q, want_k = rot[:, :num_q_heads], rot[:, num_q_heads:num_q_heads + num_kv_heads]
+    for got, want in ((q, want_q), (k, want_k)):
+        err = (got.float() - want).abs()
+        assert (err <= want.abs().clamp_min(1e-3) * 2.0 ** -7).all()
+    assert torch.equal(v, qkv.view(rows, -1, head_dim)[:, num_q_heads + num_kv_heads:])

@@ -9,7 +9,7 @@ from util import entry, nvk
 
 def _module():
     nvk()                                   # registers the package under its importable name
-    return importlib.import_module(entry.PKG_NAME + ".tp_comm")
+    return importlib.import_module("benchmarks.tp_comm")
 
 
 def test_module_imports_without_cuda():

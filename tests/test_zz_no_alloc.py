@@ -5,13 +5,16 @@ Some users of the decode kernel cannot give it a workspace: a wrapper that keeps
 pledged all free HBM to its KV cache (or that bans ``cudaMalloc`` after start-up) has nothing left to
 hand over.  For them the library keeps the split-K scratch in a fixed 32 MiB device array.  This file
 checks, through the C ABI, that the allocation-free entry point returns what the workspace-taking one
-returns, twice in a row (the second call finds the first call's leftovers in the shared array), and that
-problems too large for the array are refused.  It is named so that pytest collects it last.
+returns -- the same bits, since both run the same kernels with the same split -- twice in a row (the second
+call finds the first call's leftovers in the shared array), that the result is also right (against the CPU
+oracle, within the tolerance of every bf16 attention test), and that problems too large for the array are
+refused.  It is named so that pytest collects it last.
 """
 import numpy as np
 import pytest
 
-from util import MAX_ABS_TOL, MEAN_ABS_TOL, nvk, to_dev, to_np, workloads
+import oracle
+from util import assert_attention_close, nvk, to_dev, to_np, workloads
 
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
@@ -30,7 +33,7 @@ def _both(w, num_kv_heads):
     got = torch.full_like(q, float("nan"))
     nvk().launch_decode_attention_paged_static(q, kc, vc, ctx, bt, num_kv_heads, 128, 256, w["scale"], got)
     torch.cuda.synchronize()
-    return to_np(got), to_np(expected)
+    return got, expected
 
 
 def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
@@ -39,9 +42,11 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
     second = wl.make_decode_workload(3, 16, 8, 128, 256, 200, 4000, seed=72, pad_blocks_to=20)
     for w, hkv in ((first, 8), (second, 8)):
         got, expected = _both(w, hkv)
-        assert not np.isnan(got).any()
-        err = np.abs(got - expected)
-        assert err.max() <= MAX_ABS_TOL and err.mean() <= MEAN_ABS_TOL
+        assert not torch.isnan(got.float()).any()
+        assert torch.equal(got, expected)
+    ref = oracle.decode_attention_paged(second["q"], second["k_cache"], second["v_cache"], second["context_lens"],
+                                        second["block_tables"], 8, 128, 256, second["scale"])
+    assert_attention_close(to_np(got), ref)
 
 
 def test_static_scratch_entry_point_rejects_problems_beyond_its_array():

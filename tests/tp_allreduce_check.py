@@ -22,7 +22,7 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     nvk = entry.load_package()
     nvk.lib()
-    tc = importlib.import_module(entry.PKG_NAME + ".tp_comm")
+    tc = importlib.import_module("benchmarks.tp_comm")
     rows, cols = 256, 4096
     comm = tc.PeerAllReduce(nvk, torch, dist, dev, rank, world, rows * cols, torch.bfloat16)
     addend, result = comm.buffers(rows, cols)

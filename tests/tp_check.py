@@ -21,8 +21,8 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     nvk = entry.load_package()
     nvk.lib()
-    em = importlib.import_module(entry.PKG_NAME + ".e2e_model")
-    es = importlib.import_module(entry.PKG_NAME + ".e2e_schedule")
+    em = importlib.import_module("benchmarks.e2e_model")
+    es = importlib.import_module("benchmarks.e2e_schedule")
     cfg = em.DecoderConfig(layers=2, hidden=512, num_heads=8, num_kv_heads=4, head_dim=128, ffn=1024, vocab=1000,
                            max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=2048)
     rng = np.random.default_rng(9)
@@ -47,7 +47,7 @@ def main():
 
     comm = None
     if os.environ.get("TP_CHECK_PEER") == "1":   # decode-step all-reduces through the peer-memory kernel
-        tc = importlib.import_module(entry.PKG_NAME + ".tp_comm")
+        tc = importlib.import_module("benchmarks.tp_comm")
         comm = tc.PeerAllReduce(nvk, torch, dist, dev, rank, world, 8 * cfg.hidden, torch.bfloat16)
     sharded = run(em.Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=16, seed=4, peer_comm=comm))
     if comm is not None:

@@ -25,7 +25,7 @@ def nvk():
 def workloads():
     import importlib
     entry.load_package()
-    return importlib.import_module(entry.PKG_NAME + ".workloads")
+    return importlib.import_module("benchmarks.workloads")
 
 
 def to_dev(a, dtype=None, device="cuda"):
