@@ -17,11 +17,11 @@ from __future__ import annotations
 
 import argparse
 import ctypes
+import datetime
 import json
 import math
 import os
 import sys
-import threading
 import time
 
 import numpy as np
@@ -33,9 +33,16 @@ import __graft_entry__ as entry  # noqa: E402
 METRIC = "paged_decode_attention_hbm_bandwidth"
 UNIT = "GB/s"
 CFG = dict(batch=256, num_heads=32, num_kv_heads=8, head_dim=128, block_size=256, ctx_lo=1024, ctx_hi=8192)
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_split_kernel launch, from the ncu capture
-# summarised in profiles/decode_split_kernel_batch32_full.md (batch-32 case; traffic scales with KV bytes).
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_split_kernel launch divided by its algorithmic bytes, from
+# an ncu capture of a batch-32 case of this workload (a full batch is too large to capture; traffic scales with KV bytes).
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.010
+
+
+def workload_name():
+    """The same string in both arms' ``config.workload``."""
+    return (f"paged decode attention + store_kvcache, Qwen3-8B shape: batch {CFG['batch']} per GPU, "
+            f"{CFG['num_heads']}/{CFG['num_kv_heads']} heads per GPU, head_dim {CFG['head_dim']}, block_size {CFG['block_size']}, "
+            f"context U[{CFG['ctx_lo']},{CFG['ctx_hi']}], random-permutation block tables")
 
 
 def measured_peaks():
@@ -46,62 +53,7 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
-
-    def __init__(self, index):
-        super().__init__(daemon=True)
-        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
-        self._stop_evt = threading.Event()
-        self.ok = False
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
-            self.ok = True
-        except Exception:
-            self.ok = False
-
-    def run(self):
-        if not self.ok:
-            return
-        nv = self.nv
-        names = {
-            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
-            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
-            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
-            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
-        }
-        while not self._stop_evt.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
-                for bit, name in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            time.sleep(0.01)
-
-    def finish(self):
-        self._stop_evt.set()
-        if self.is_alive():
-            self.join(timeout=2)
-        med = float(np.median(self.samples)) if self.samples else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
-
-
-def physical_gpu_index(local_rank):
-    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
-    if vis:
-        try:
-            return int(vis.split(",")[local_rank])
-        except Exception:
-            return local_rank
-    return local_rank
+from benchmarks.clocks import ClockSampler, physical_gpu_index  # noqa: E402
 
 
 def make_workload(torch, dev, seed):
@@ -190,7 +142,35 @@ def cpu_baseline(torch, w, budget_s=12.0):
         reps += 1
     return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
             "sample": f"first {n} of {CFG['batch']} sequences, all {CFG['num_heads']} heads, {reps} passes of the fp32 "
-                      f"oracle in {dt:.1f} s; bytes counted at the workload's bf16 element size"}
+                      f"oracle in {dt:.1f} s; bytes counted at the workload's bf16 element size",
+            "qwen3_0p6b_decode_fp32": cpu_reference_config(oracle)}
+
+
+def cpu_reference_config(oracle, budget_s=4.0):
+    """The CPU-runnable configuration, timed on the host cores: single-layer paged decode at the Qwen3-0.6B shape -- 16
+    query heads, 8 KV heads, head_dim 128, fp32, batch 8, block_size 256, contexts U[64,1024], q pre-scaled by
+    1/sqrt(128) (softmax scale 1), block tables from a seeded permutation of a 64-block pool, the new token stored
+    first.  One thread and all threads; bytes are the fp32 K and V actually read."""
+    from benchmarks import workloads as wl
+    ctx = np.random.default_rng(1234).integers(64, 1025, size=8)
+    need = int(((ctx + 255) // 256).sum())
+    w = wl.make_decode_workload(batch=8, num_heads=16, num_kv_heads=8, head_dim=128, block_size=256, ctx_lo=64, ctx_hi=1024,
+                                seed=1234, value_scale=0.5, prescale_q=True, rounded=False, extra_pool_blocks=64 - need,
+                                context_lens=ctx)
+    kc, vc = w["k_cache"].copy(), w["v_cache"].copy()
+    nbytes = int(w["context_lens"].astype(np.int64).sum()) * 2 * 8 * 128 * 4
+    out = {"workload": "16/8 heads, head_dim 128, fp32, batch 8, block_size 256, context U[64,1024], 64-block pool",
+           "algorithmic_bytes_per_step": nbytes, "unit": UNIT, "host_threads_available": oracle.default_threads()}
+    for label, threads in (("single_thread", 1), ("all_threads", oracle.default_threads())):
+        best, spent = float("inf"), 0.0
+        while spent < budget_s / 2:
+            t0 = time.perf_counter()
+            oracle.store_kvcache(w["k_new"], w["v_new"], kc, vc, w["slot_mapping"])
+            oracle.decode_attention_paged(w["q"], kc, vc, w["context_lens"], w["block_tables"], 8, 128, 256, w["scale"], threads=threads)
+            dt = time.perf_counter() - t0
+            best, spent = min(best, dt), spent + dt
+        out[label] = {"threads": threads, "ms_per_step": best * 1e3, "value": nbytes / best / 1e9}
+    return out
 
 
 def rank_plan(rank, world, shard):
@@ -347,18 +327,21 @@ def run_ours(args, torch, dist, rank, world, dev):
         if not torch.equal(host_out[(args.steps - 1) & 1], out_host):
             raise RuntimeError("pipelined end-to-end step produced a different result than the serial one")
 
+    per_rank = gather_per_rank(torch, dist, world, dev, {
+        "ms_per_step": total_ms / args.steps, "decode_ms_per_launch": decode_ms, "bytes_per_step": float(ab["total"]),
+        "context_tokens": float(w["context_lens_np"].astype(np.int64).sum()), "sm_mhz": float(clocks["sm_mhz"] or 0.0)})
+    own_decode_ms = decode_ms
     (total_ms, e2e_ms, decode_ms, serial_ms), (bytes_all, launches) = combine_ranks(
         torch, dist, world, dev, [total_ms, e2e_ms, decode_ms, serial_ms], [float(ab["total"]), float(launches)])
     launches = int(launches)
 
     peak, peak_kind = measured_peaks()
-    achieved = ab["decode"] / (decode_ms * 1e-3) / 1e9
+    achieved = ab["decode"] / (own_decode_ms * 1e-3) / 1e9      # rank 0's own bytes over rank 0's own launch time
     line = {
         "metric": METRIC, "value": bytes_all * args.steps / (total_ms * 1e-3) / 1e9, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
         "higher_is_better": True, "scaling": plan["scaling"], "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"paged decode attention + store_kvcache, Qwen3-8B shape: batch {CFG['batch']} per GPU, {CFG['num_heads']}/{CFG['num_kv_heads']} heads per GPU, "
-                               "head_dim 128, block_size 256, context U[1024,8192], random-permutation block tables",
+        "config": {"workload": workload_name(),
                    "bytes_per_step_per_gpu": ab["total"], "kv_pool_blocks": w["pool"],
                    "l2": "inputs (about 4.8 GB of KV per step) exceed the 126 MB L2; no flush needed",
                    "parallelism": plan["parallelism"]},
@@ -370,32 +353,82 @@ def run_ours(args, torch, dist, rank, world, dev):
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": "decode_split_kernel (+ decode_merge_kernel)", "achieved": achieved,
                      "peak": peak, "peak_source": f"{peak_kind} copy bandwidth", "unit": UNIT, "frac": achieved / peak,
-                     "frac_of_nominal_8TBs": achieved / 8000.0, "ms_per_launch": decode_ms,
+                     "frac_of_nominal_8TBs": achieved / 8000.0, "ms_per_launch": own_decode_ms,
                      "algorithmic_bytes_per_launch": ab["decode"],
                      "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * ab["decode"]
                                  if NCU_TRAFFIC_PER_ALGORITHMIC_BYTE else None)},
         "clocks": clocks,
     }
+    if world > 1:
+        # every rank's own figures: ranks draw different context lengths (seed 2024 + rank), so bytes differ by a few per
+        # cent; `value` divides the sum of bytes by the slowest rank's time, `sum_of_rank_rates` adds bytes_r / t_r
+        line["per_rank"] = per_rank
+        line["sum_of_rank_rates"] = sum(b / (t * 1e-3) / 1e9 for b, t in zip(per_rank["bytes_per_step"], per_rank["ms_per_step"]))
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(torch, w)
+    # free the decode workload before anything else is measured in this process
+    del dev_in, dev_out, host_out, host, out_host, ws
+    w.clear()
+    torch.cuda.empty_cache()
+    if world == 1 and not args.no_other_kernels:
+        from benchmarks import kernel_bench as kb
+        line["other_kernels"] = kb.other_kernels(nvk, torch, dev)
+        line["gpu_launches_other_kernels"] = "not counted in gpu_launches (outside the timed region)"
+    if world > 1 and not args.no_tp_e2e:
+        line["tp_e2e"] = tp_e2e(args, nvk, torch, dist, rank, world, dev)
     return line
 
 
-def run_reference(args, torch, dev):
-    """Reference arm: the reference's own CUDA kernels (store_kvcache + decode_paged_attention_kernel,
-    compiled unmodified for sm_100a into oracle/_ref) on the same workload.  The reference has no CPU
-    implementation of this path; if the compiled reference is absent the CPU oracle port is timed."""
-    w = make_workload(torch, dev, seed=2024)
+def tp_e2e(args, nvk, torch, dist, rank, world, dev):
+    """The second half of the metric: output tokens per second of the end-to-end Qwen3-8B-shaped decoder, tensor-parallel
+    over the N GPUs of this run (KV-head shards; all-reduce after o_proj / down_proj through this library's peer-memory
+    kernel in the decode steps).  Returns the figures of benchmarks/e2e_bench.run_e2e, or the error that stopped it."""
+    from benchmarks import e2e_bench as eb, e2e_model as em
+    sampler = ClockSampler(physical_gpu_index(int(os.environ.get("LOCAL_RANK", 0))))
+    sampler.start()
+    try:
+        full = eb.run_e2e(nvk, torch, dist, rank, world, dev, em.DecoderConfig(layers=args.e2e_layers), num_seqs=args.e2e_seqs,
+                          len_lo=min(100, args.e2e_maxlen), len_hi=args.e2e_maxlen, use_graph=True, kv_dtype="bf16",
+                          allreduce=args.e2e_allreduce)
+    except Exception as exc:   # reported, not fatal: the decode figures of this line stand on their own
+        sampler.finish()
+        return {"error": f"{type(exc).__name__}: {exc}"}
+    keep = ("metric", "value", "unit", "ms_per_step", "scaling", "output_tokens", "prompt_tokens", "total_s", "prefill_s", "decode_s",
+            "attention_ms_per_decode_step", "peer_allreduce_status", "prefill_status", "gpu_launches")
+    out = {k: full.get(k) for k in keep}
+    out["config"] = full["config"]
+    out["clocks"] = sampler.finish()
+    return out
+
+
+def gather_per_rank(torch, dist, world, device, values: dict) -> dict:
+    """{name: [value of rank 0, value of rank 1, ...]} for a dict of floats."""
+    names = sorted(values)
+    mine = torch.tensor([float(values[k]) for k in names], device=device, dtype=torch.float64)
+    if world <= 1:
+        return {k: [float(v)] for k, v in zip(names, mine.tolist())}
+    rows = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(rows, mine)
+    return {k: [float(r[i]) for r in rows] for i, k in enumerate(names)}
+
+
+def run_reference(args, torch, dist, rank, world, dev):
+    """Reference arm: the reference's own CUDA kernels (store_kvcache + decode_paged_attention_kernel, compiled
+    unmodified for sm_100a into oracle/_ref) on the same workload, one rank per GPU with the aggregation of the other arm
+    (every rank its own batch, seed 2024 + rank; slowest rank's time, sum of bytes).  The reference has no CPU
+    implementation of this path; if the compiled reference is absent the CPU oracle port is timed on rank 0."""
+    w = make_workload(torch, dev, seed=2024 + rank)
     ab = algorithmic_bytes(w["context_lens_np"], w["block_tables_np"])
     ref_path = os.path.join(ROOT, "oracle", "_ref", "libnvk_ref.so")
-    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+    steps = min(args.steps, 50)   # the reference kernel is two orders of magnitude slower per step
+    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "data": "synthetic",
-            "config": {"workload": "paged decode attention + store_kvcache, Qwen3-8B shape: batch 256, 32/8 heads, "
-                                   "head_dim 128, block_size 256, context U[1024,8192]"}}
+            "data": "synthetic", "config": {"workload": workload_name(), "parallelism": f"{world} independent batches, one per GPU, no collective"}}
     if not os.path.exists(ref_path):
+        if rank != 0:
+            return None
         cb = cpu_baseline(torch, w, budget_s=20.0)
-        base.update({"value": cb["value"], "ms_per_step": None, "dtype": "f32", "cpu_baseline": cb,
+        base.update({"value": cb["value"], "ms_per_step": None, "dtype": "f32", "cpu_baseline": cb, "n_gpus": 0,
                      "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
         return base
     ref = ctypes.CDLL(ref_path)
@@ -416,20 +449,26 @@ def run_reference(args, torch, dev):
         if rc:
             raise RuntimeError(ref.nvkref_last_error().decode())
 
-    steps = min(args.steps, 50)   # the reference kernel is two orders of magnitude slower per step
-    for _ in range(min(args.warmup, 3)):
+    for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(physical_gpu_index(int(os.environ.get("LOCAL_RANK", 0))))
+    sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(steps):
         step()
     ev1.record()
     torch.cuda.synchronize()
-    ms = ev0.elapsed_time(ev1)
-    value = ab["total"] * steps / (ms * 1e-3) / 1e9
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.finish()
+    (ms,), (bytes_all,) = combine_ranks(torch, dist, world, dev, [ev0.elapsed_time(ev1)], [float(ab["total"])])
+    value = bytes_all * steps / (ms * 1e-3) / 1e9
     base.update({
-        "value": value, "steps": steps, "ms_per_step": ms / steps, "dtype": "bf16", "gpu_launches": 2 * steps,
+        "value": value, "ms_per_step": ms / steps, "dtype": "bf16", "gpu_launches": 2 * steps * world, "clocks": clocks,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 0, "kind": "reference",
                          "sample": "full workload; the reference implements this path only as CUDA kernels, so its "
                                    "own kernels (compiled for sm_100a) run on the GPU, not on host cores"},
@@ -445,6 +484,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--no-other-kernels", action="store_true", help="N = 1: skip the short runs of the kernels beside paged decode")
+    ap.add_argument("--no-tp-e2e", action="store_true", help="N > 1: skip the tensor-parallel end-to-end decoder run")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e", "decode_int8"],
                     help="decode is the benchmark; prefill / store / prologue / mixed / decode_int8 time the remaining kernels of the path "
                          "(1 GPU); e2e reports output tokens per second of the whole decoder, tensor-parallel over --gpus")
@@ -475,10 +516,16 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
 
     if args.impl == "reference":
-        if rank != 0:
-            return 0
-        torch.cuda.set_device(0)
-        print(json.dumps(run_reference(args, torch, torch.device("cuda:0"))), flush=True)
+        dist = None
+        torch.cuda.set_device(local_rank)
+        if world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"), timeout=datetime.timedelta(seconds=300))
+        line = run_reference(args, torch, dist, rank, world, torch.device(f"cuda:{local_rank}"))
+        if rank == 0 and line is not None:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
         return 0
 
     if args.workload == "e2e":
@@ -558,7 +605,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"), timeout=datetime.timedelta(seconds=300))
     else:
         torch.cuda.set_device(local_rank)
     dev = torch.device(f"cuda:{local_rank}")

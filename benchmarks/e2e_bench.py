@@ -136,6 +136,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
         attn_ms = a0.elapsed_time(a1) / 10
 
     comm_status = comm.status() if comm is not None else 0
+    prefill_status = nvk.prefill_status()     # non-zero: a tensor-core prefill launch gave up a bounded wait (rows incomplete)
     times = torch.tensor([total_ms, prefill_ms, decode_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -160,7 +161,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
         "mean_active_rows": active_rows / max(steps, 1),
         "attention_ms_per_decode_step": attn_ms,
         "attention_share_of_decode_step": (attn_ms / (decode_ms / max(steps, 1))) if attn_ms else None,
-        "model_build_s": build_s, "peer_allreduce_status": comm_status,
+        "model_build_s": build_s, "peer_allreduce_status": comm_status, "prefill_status": prefill_status,
         "gpu_launches": our_launches, "gpu_launches_issued_eagerly": eager_launches,
         "e2e": {"value": out_tokens / (total_ms / 1e3), "unit": "tok/s",
                 "h2d_bytes_per_step": num_seqs * width * 4, "d2h_bytes_per_step": 0,

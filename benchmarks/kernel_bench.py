@@ -1,6 +1,8 @@
 """Single-GPU measurements of the kernels beside paged decode: varlen prefill, store_kvcache at
-prefill size and the fused decode prologue.  ``bench.py --workload {prefill,store,prologue}`` prints
-one JSON line per run in the same layout as the decode benchmark (metric / value / roofline).
+prefill size, the fused decode prologue, int8-cache decode and the mixed step.  ``bench.py --workload
+{prefill,store,prologue,decode_int8,mixed}`` prints one JSON line per run in the same layout as the decode
+benchmark (metric / value / roofline / clocks); ``other_kernels`` runs short versions of all of them for the
+default benchmark line.
 
 Every workload is seeded synthetic data in the shapes of the Qwen3-8B configurations: 32 query
 heads, 8 KV heads, head_dim 128, bf16, 256-token cache blocks.
@@ -26,11 +28,27 @@ def _peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+def _sustained_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh).get("bf16_tflops_sustained", 0.0)) or None
+    return 1400.0
+
+
+LAST_CLOCKS = None   # clock record of the most recent _time() call: every line below carries it
+
+
 def _time(torch, fn, steps, warmup, flush=None):
+    """Mean and median CUDA-event time of ``fn`` in ms; SM clock and throttle reasons are sampled while it runs."""
+    global LAST_CLOCKS
+    from .clocks import sampler_for_local_rank
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    sampler = sampler_for_local_rank()
+    sampler.start()
     for a, b in evs:
         if flush is not None:
             flush()
@@ -38,6 +56,7 @@ def _time(torch, fn, steps, warmup, flush=None):
         fn()
         b.record()
     torch.cuda.synchronize()
+    LAST_CLOCKS = sampler.finish()
     times = sorted(a.elapsed_time(b) for a, b in evs)
     return float(np.mean(times)), float(times[len(times) // 2])
 
@@ -88,8 +107,8 @@ def make_prefill_inputs(torch, dev, seed, num_seqs=16, q_lo=512, q_hi=4096, pref
     return w
 
 
-def bench_prefill(nvk, torch, dev, steps, warmup, num_seqs=16, q_lo=512, q_hi=4096):
-    w = make_prefill_inputs(torch, dev, 2025, num_seqs, q_lo, q_hi)
+def bench_prefill(nvk, torch, dev, steps, warmup, num_seqs=16, q_lo=512, q_hi=4096, prefix_frac=0.5):
+    w = make_prefill_inputs(torch, dev, 2025, num_seqs, q_lo, q_hi, prefix_frac)
     nvk.store_kvcache(w["k_new"], w["v_new"], w["k_cache"], w["v_cache"], w["slot_mapping"])
 
     def attn():
@@ -100,6 +119,7 @@ def bench_prefill(nvk, torch, dev, steps, warmup, num_seqs=16, q_lo=512, q_hi=40
         nvk.store_kvcache(w["k_new"], w["v_new"], w["k_cache"], w["v_cache"], w["slot_mapping"])
 
     mean_ms, med_ms = _time(torch, attn, steps, warmup)
+    attn_clocks = LAST_CLOCKS
     st_mean, _ = _time(torch, store, steps, warmup)
     hbm, tf, kind = _peaks()
     achieved = w["flops"] / (mean_ms * 1e-3) / 1e12
@@ -110,15 +130,16 @@ def bench_prefill(nvk, torch, dev, steps, warmup, num_seqs=16, q_lo=512, q_hi=40
         "steps": steps, "warmup": warmup, "ms_per_step": mean_ms, "median_ms": med_ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"varlen causal prefill, Qwen3-8B shape: {num_seqs} sequences of U[{q_lo},{q_hi}] new tokens, "
-                               "half with a 256-1024-token paged prefix, keys read through block_tables",
+                               f"{'half' if prefix_frac == 0.5 else str(prefix_frac) + ' of them'} with a 256-1024-token paged prefix, keys read through block_tables",
                    "total_q": total_q, "flops_per_step": w["flops"],
                    "l2": "q/out (2 x %.0f MB) exceed the 126 MB L2" % (total_q * HQ * D * 2 / 1e6)},
         "roofline": {"bound": "tensor", "kernel": "prefill kernel", "achieved": achieved, "peak": tf,
                      "peak_source": f"{kind} cuBLAS bf16 burst", "unit": "TFLOP/s", "frac": achieved / tf,
-                     "frac_of_nominal_2250": achieved / 2250.0, "traffic": None},
+                     "frac_of_nominal_2250": achieved / 2250.0,
+                     "frac_of_sustained": (achieved / _sustained_tflops()) if _sustained_tflops() else None, "traffic": None},
         "store_kvcache": {"ms": st_mean, "bytes": store_bytes, "GBps": store_bytes / (st_mean * 1e-3) / 1e9,
                           "frac_of_" + kind + "_hbm": store_bytes / (st_mean * 1e-3) / 1e9 / hbm},
-        "gpu_launches": 2 * steps,
+        "gpu_launches": 2 * steps, "clocks": attn_clocks,
     }
 
 
@@ -145,7 +166,7 @@ def bench_store(nvk, torch, dev, steps, warmup, tokens=36864):
                        "l2": "a 256 MB buffer is written between timed iterations"},
             "roofline": {"bound": "hbm", "kernel": "store_rows_kernel", "achieved": ach, "peak": hbm,
                          "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
-            "gpu_launches": steps}
+            "gpu_launches": steps, "clocks": LAST_CLOCKS}
 
 
 def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ctx_hi=8192):
@@ -176,6 +197,7 @@ def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ct
     dec8 = lambda: nvk.launch_decode_attention_paged_int8(q, kc8, vc8, ks, vs, ctx_dev, tab_dev, HKV, D, BS, scale, out8, ws)  # noqa: E731
     dec16 = lambda: nvk.launch_decode_attention_paged(q, kc16, vc16, ctx_dev, tab_dev, HKV, D, BS, scale, out16, ws)  # noqa: E731
     mean8, med8 = _time(torch, dec8, steps, warmup)
+    clocks8 = LAST_CLOCKS
     mean16, _ = _time(torch, dec16, steps, warmup)
     err = (out8.float() - out16.float()).abs()
     tokens = int(ctx.astype(np.int64).sum())
@@ -197,7 +219,7 @@ def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ct
             "max_abs_diff_vs_bf16_cache": float(err.max()), "mean_abs_diff_vs_bf16_cache": float(err.mean()),
             "store_kvcache_int8": {"ms": store_ms, "tokens": rows, "bytes": store_bytes, "GBps": store_bytes / (store_ms * 1e-3) / 1e9,
                                    "frac_of_measured_hbm": store_bytes / (store_ms * 1e-3) / 1e9 / hbm},
-            "gpu_launches": steps * 2}
+            "gpu_launches": steps * 2, "clocks": clocks8}
 
 
 def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
@@ -234,7 +256,7 @@ def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
                              else "a 256 MB buffer is written between timed iterations"},
             "roofline": {"bound": "hbm", "kernel": "fused_prologue_kernel", "achieved": ach, "peak": hbm,
                          "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
-            "gpu_launches": steps}
+            "gpu_launches": steps, "clocks": LAST_CLOCKS}
 
 
 def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_lo=512, ctx_hi=16384, prefill_seqs=4,
@@ -341,7 +363,43 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
                        "note": "logical layers are mapped round-robin onto the physical caches that fit in HBM",
                        "bytes_per_layer": bytes_layer, "prefill_flops_per_layer": flops_layer,
                        "l2": "each layer cache (GiB) exceeds the 126 MB L2"},
-            "roofline": {"bound": "hbm", "kernel": ("prefill_tc5_kernel" if single_launch else "decode_split_kernel (dominant; prefill_tc5_kernel second)"), "achieved": ach,
+            "roofline": {"bound": "hbm", "kernel": ("prefill kernel" if single_launch else "decode_split_kernel (dominant; the prefill kernel second)"), "achieved": ach,
                          "peak": hbm, "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm,
                          "ideal_ms_per_step": ideal_ms, "frac_of_ideal_time": ideal_ms / mean_ms, "traffic": None},
-            "gpu_launches": steps * layers * (2 if single_launch else 5)}
+            "gpu_launches": steps * layers * (2 if single_launch else 5), "clocks": LAST_CLOCKS}
+
+
+def other_kernels(nvk, torch, dev, steps=20, warmup=3):
+    """Short runs of the kernels beside paged decode, for the default benchmark line: the prefill configuration
+    (tensor roofline), store_kvcache at prefill size, the fused prologue at decode and prefill row counts, decode over
+    the int8 cache.  Each entry: ms per launch, algorithmic bytes or flops, fraction of the measured peak, clocks."""
+    out = {}
+
+    def brief(line, extra=()):
+        r = line["roofline"]
+        e = {"ms": line["ms_per_step"], "median_ms": line.get("median_ms"), "achieved": r["achieved"], "unit": r["unit"],
+             "peak": r["peak"], "frac": r["frac"], "bound": r["bound"], "workload": line["config"]["workload"],
+             "clocks": line.get("clocks")}
+        for k in extra:
+            e[k] = line[k] if k in line else r.get(k)
+        return e
+
+    line = bench_prefill(nvk, torch, dev, steps, warmup)
+    out["prefill"] = brief(line)
+    out["prefill"].update({"flops": line["config"]["flops_per_step"], "frac_of_sustained": line["roofline"]["frac_of_sustained"],
+                           "frac_of_nominal_2250": line["roofline"]["frac_of_nominal_2250"]})
+    torch.cuda.empty_cache()
+    line = bench_prefill(nvk, torch, dev, steps, warmup, num_seqs=32, q_lo=512, q_hi=512, prefix_frac=0.0)
+    out["prefill_32x512"] = brief(line)
+    out["prefill_32x512"]["flops"] = line["config"]["flops_per_step"]
+    torch.cuda.empty_cache()
+    line = bench_store(nvk, torch, dev, steps, warmup)
+    out["store_kvcache_36864_tokens"] = brief(line)
+    for rows in (256, 16384):
+        line = bench_prologue(nvk, torch, dev, steps, warmup, rows=rows)
+        out[f"fused_prologue_{rows}_rows"] = brief(line)
+    torch.cuda.empty_cache()
+    line = bench_decode_int8(nvk, torch, dev, steps, warmup)
+    out["decode_int8_kv"] = brief(line, extra=("bf16_cache_same_shape", "store_kvcache_int8"))
+    torch.cuda.empty_cache()
+    return out

@@ -1,29 +1,31 @@
 """Peer-memory all-reduce for the tensor-parallel decoder (plumbing around ``nvk_tp_allreduce``).
 
-One process per GPU.  Every rank allocates an addend buffer, a result buffer and a flag area with ``cudaMalloc``
-(through cuda-python), publishes their CUDA IPC handles over the existing ``torch.distributed`` group and maps the
-peers' buffers with ``cudaIpcOpenMemHandle`` (plain peer mappings over NVLink; no multicast object is created).  The
-row-parallel GEMMs write straight into the addend buffer (``torch.matmul(..., out=...)``), the kernel leaves the sum in
-the result buffer of every rank.  Replaces ``NcclTensorParallelCommunicator::all_reduce_sum``
-(src/utils/tensor_parallel.cpp:331-353 of the reference) for messages of up to ``max_elems`` 16-bit elements.
+One process per GPU.  Every rank allocates a staging area and a flag area with ``cudaMalloc`` (through cuda-python),
+publishes the staging area's CUDA IPC handle over the existing ``torch.distributed`` group and maps the peers' staging
+areas with ``cudaIpcOpenMemHandle`` (plain peer mappings over NVLink; no multicast object is created).  Addend, result
+and norm buffers are ordinary torch tensors of the owning rank: peers never touch them, the row-parallel GEMMs write
+straight into the addend (``torch.matmul(..., out=...)``) and the kernel leaves the sum in the result buffer.
+Replaces ``NcclTensorParallelCommunicator::all_reduce_sum`` (src/utils/tensor_parallel.cpp:331-353 of the reference)
+for messages of up to ``max_elems`` 16-bit elements.
 """
 from __future__ import annotations
 
 import ctypes
 
 
-class _DeviceBlock:
-    """A cudaMalloc'ed range exposed to torch through the CUDA array interface (as int16 elements)."""
-
-    def __init__(self, ptr: int, nbytes: int):
-        self.ptr, self.nbytes = ptr, nbytes
-        self.__cuda_array_interface__ = {"shape": (nbytes // 2,), "typestr": "<i2", "data": (ptr, False), "version": 2}
-
-
 def _check(err, what):
     code = int(err)
     if code != 0:
         raise RuntimeError(f"{what} failed with CUDA error {code}")
+
+
+def declare(lib) -> None:
+    """ctypes signatures of the all-reduce entry points (include/nvk.h)."""
+    lib.nvk_tp_allreduce_flag_bytes.restype = ctypes.c_size_t
+    lib.nvk_tp_allreduce_stage_bytes.restype = ctypes.c_size_t
+    lib.nvk_tp_allreduce_stage_bytes.argtypes = [ctypes.c_int64]
+    lib.nvk_tp_allreduce_set_wait_limit_ms.restype = None
+    lib.nvk_tp_allreduce_set_wait_limit_ms.argtypes = [ctypes.c_int]
 
 
 class PeerAllReduce:
@@ -33,47 +35,39 @@ class PeerAllReduce:
         self.rank, self.world, self.max_elems, self.dtype = rank, world, int(max_elems), dtype
         self._cudart = cudart
         lib = nvk.lib()
-        lib.nvk_tp_allreduce_flag_bytes.restype = ctypes.c_size_t
-        flag_bytes = int(lib.nvk_tp_allreduce_flag_bytes())
-        sizes = {"in": self.max_elems * 2, "out": self.max_elems * 2, "norm": self.max_elems * 2,
-                 "flags": (flag_bytes + 255) // 256 * 256}
-        self._own, handles = {}, {}
-        for name, nbytes in sizes.items():
+        declare(lib)
+        self.stage_bytes = int(lib.nvk_tp_allreduce_stage_bytes(self.max_elems))
+        flag_bytes = (int(lib.nvk_tp_allreduce_flag_bytes()) + 255) // 256 * 256
+        self._own = {}
+        for name, nbytes in (("stage", self.stage_bytes), ("flags", flag_bytes)):
             err, ptr = cudart.cudaMalloc(nbytes)
             _check(err, "cudaMalloc")
             _check(cudart.cudaMemset(ptr, 0, nbytes)[0], "cudaMemset")
-            err, handle = cudart.cudaIpcGetMemHandle(ptr)
-            _check(err, "cudaIpcGetMemHandle")
             self._own[name] = (int(ptr), nbytes)
-            handles[name] = bytes(handle.reserved)
+        err, handle = cudart.cudaIpcGetMemHandle(self._own["stage"][0])
+        _check(err, "cudaIpcGetMemHandle")
         _check(cudart.cudaDeviceSynchronize()[0], "cudaDeviceSynchronize")
         gathered = [None] * world
-        dist.all_gather_object(gathered, handles)
+        dist.all_gather_object(gathered, bytes(handle.reserved))
         self._opened = []
-        self._ptrs = {name: [0] * world for name in sizes}
+        stage = [0] * world
         for r in range(world):
-            for name in sizes:
-                if r == rank:
-                    self._ptrs[name][r] = self._own[name][0]
-                    continue
-                handle = cudart.cudaIpcMemHandle_t()
-                handle.reserved = gathered[r][name]
-                err, ptr = cudart.cudaIpcOpenMemHandle(handle, cudart.cudaIpcMemLazyEnablePeerAccess)
-                _check(err, "cudaIpcOpenMemHandle")
-                self._opened.append(int(ptr))
-                self._ptrs[name][r] = int(ptr)
-        arr = ctypes.c_void_p * world
-        self._in_tab = arr(*self._ptrs["in"])
-        self._out_tab = arr(*self._ptrs["out"])
-        self._flag_tab = arr(*self._ptrs["flags"])
-        self._norm_tab = arr(*self._ptrs["norm"])
-        self._norm_block = _DeviceBlock(*self._own["norm"])
-        self._in_block = _DeviceBlock(*self._own["in"])
-        self._out_block = _DeviceBlock(*self._own["out"])
-        self.addend = torch.as_tensor(self._in_block, device=dev).view(dtype)    # [max_elems], this rank's addend
-        self.result = torch.as_tensor(self._out_block, device=dev).view(dtype)   # [max_elems], the sum
-        self.normed = torch.as_tensor(self._norm_block, device=dev).view(dtype)  # [max_elems], rmsnorm of (residual + sum)
-        dist.barrier()   # every rank has mapped every buffer before anyone launches
+            if r == rank:
+                stage[r] = self._own["stage"][0]
+                continue
+            h = cudart.cudaIpcMemHandle_t()
+            h.reserved = gathered[r]
+            err, ptr = cudart.cudaIpcOpenMemHandle(h, cudart.cudaIpcMemLazyEnablePeerAccess)
+            _check(err, "cudaIpcOpenMemHandle")
+            self._opened.append(int(ptr))
+            stage[r] = int(ptr)
+        self._stage_tab = (ctypes.c_void_p * world)(*stage)
+        self._flags = ctypes.c_void_p(self._own["flags"][0])
+        self.addend = torch.zeros(self.max_elems, device=dev, dtype=dtype)   # this rank's addend
+        self.result = torch.zeros(self.max_elems, device=dev, dtype=dtype)   # the sum
+        self.normed = torch.zeros(self.max_elems, device=dev, dtype=dtype)   # rmsnorm of (residual + sum)
+        torch.cuda.synchronize()
+        dist.barrier()   # every rank has mapped every staging area before anyone launches
 
     def buffers(self, rows: int, cols: int):
         """Views of the addend and result buffers shaped [rows, cols]."""
@@ -88,9 +82,10 @@ class PeerAllReduce:
         if count % (8 * self.world) != 0 or count > self.max_elems:
             raise ValueError("count must be a multiple of 8 * world and fit the peer buffers")
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        nvk._check(nvk.lib().nvk_tp_allreduce(self._in_tab, self._out_tab, self._flag_tab, ctypes.c_int(self.rank),
-                                              ctypes.c_int(self.world), ctypes.c_int64(count),
-                                              ctypes.c_int(nvk._dtype_code(self.addend)), stream))
+        nvk._check(nvk.lib().nvk_tp_allreduce(
+            ctypes.c_void_p(self.addend.data_ptr()), ctypes.c_void_p(self.result.data_ptr()), self._stage_tab,
+            ctypes.c_size_t(self.stage_bytes), self._flags, ctypes.c_int(self.rank), ctypes.c_int(self.world),
+            ctypes.c_int64(count), ctypes.c_int(nvk._dtype_code(self.addend)), stream))
         nvk.launch_count += 1
 
     def all_reduce_add_rmsnorm(self, residual, weight, eps: float, rows: int, cols: int):
@@ -102,17 +97,19 @@ class PeerAllReduce:
             raise ValueError("rows must be a multiple of world and the message must fit the peer buffers")
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         nvk._check(nvk.lib().nvk_tp_allreduce_add_rmsnorm(
-            self._in_tab, self._out_tab, self._norm_tab, self._flag_tab, ctypes.c_void_p(residual.data_ptr()),
-            ctypes.c_void_p(weight.data_ptr()), ctypes.c_float(eps), ctypes.c_int(self.rank), ctypes.c_int(self.world),
-            ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(nvk._dtype_code(self.addend)), stream))
+            ctypes.c_void_p(self.addend.data_ptr()), ctypes.c_void_p(self.result.data_ptr()),
+            ctypes.c_void_p(self.normed.data_ptr()), self._stage_tab, ctypes.c_size_t(self.stage_bytes), self._flags,
+            ctypes.c_void_p(residual.data_ptr()), ctypes.c_void_p(weight.data_ptr()), ctypes.c_float(eps),
+            ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(rows), ctypes.c_int(cols),
+            ctypes.c_int(nvk._dtype_code(self.addend)), stream))
         nvk.launch_count += 1
         return self.result[:n].view(rows, cols), self.normed[:n].view(rows, cols)
 
     def status(self) -> int:
-        """0 when every wait on the peers completed; 1 / 2 when a peer never arrived (synchronises the stream)."""
+        """0 when every wait on the peers completed; 1 / 2 when a peer's data never arrived (synchronises the stream)."""
         out = ctypes.c_int(0)
         stream = ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)
-        self.nvk._check(self.nvk.lib().nvk_tp_allreduce_status(ctypes.c_void_p(self._own["flags"][0]), stream, ctypes.byref(out)))
+        self.nvk._check(self.nvk.lib().nvk_tp_allreduce_status(self._flags, stream, ctypes.byref(out)))
         return int(out.value)
 
     def close(self) -> None:
@@ -126,3 +123,38 @@ class PeerAllReduce:
         for ptr, _ in self._own.values():
             cudart.cudaFree(ptr)
         self._own = {}
+
+
+class InProcessAllReduce:
+    """``world`` ranks on ONE device (``nvk_tp_allreduce_inprocess``): a buffer set per rank, one cooperative launch per
+    collective.  The counterpart of the reference's in-process communicator (src/utils/tensor_parallel.cpp:165-277)."""
+
+    def __init__(self, nvk, torch, dev, world: int, max_elems: int, dtype):
+        self.nvk, self.torch, self.world, self.max_elems, self.dtype = nvk, torch, world, int(max_elems), dtype
+        lib = nvk.lib()
+        declare(lib)
+        self.stage_bytes = int(lib.nvk_tp_allreduce_stage_bytes(self.max_elems))
+        flag_words = int(lib.nvk_tp_allreduce_flag_bytes()) // 4
+        mk = lambda: [torch.zeros(self.max_elems, device=dev, dtype=dtype) for _ in range(world)]  # noqa: E731
+        self.addend, self.result, self.normed = mk(), mk(), mk()
+        self.stage = [torch.zeros(self.stage_bytes, device=dev, dtype=torch.uint8) for _ in range(world)]
+        self.flags = [torch.zeros(flag_words, device=dev, dtype=torch.int32) for _ in range(world)]
+        self._tab = lambda ts: (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])  # noqa: E731
+
+    def launch(self, rows: int, cols: int, residuals=None, weight=None, eps: float = 1e-6) -> None:
+        """Plain sum when ``residuals`` is None, else the fused form with one residual tensor per rank."""
+        nvk, torch = self.nvk, self.torch
+        fused = residuals is not None
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nvk._check(nvk.lib().nvk_tp_allreduce_inprocess(
+            self._tab(self.addend), self._tab(self.result), self._tab(self.normed) if fused else None, self._tab(self.stage),
+            ctypes.c_size_t(self.stage_bytes), self._tab(self.flags), self._tab(residuals) if fused else None,
+            ctypes.c_void_p(weight.data_ptr()) if fused else None, ctypes.c_float(eps), ctypes.c_int(self.world),
+            ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(nvk._dtype_code(self.addend[0])), stream))
+        nvk.launch_count += 1
+
+    def status(self, rank: int = 0) -> int:
+        out = ctypes.c_int(0)
+        stream = ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+        self.nvk._check(self.nvk.lib().nvk_tp_allreduce_status(ctypes.c_void_p(self.flags[rank].data_ptr()), stream, ctypes.byref(out)))
+        return int(out.value)

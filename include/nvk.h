@@ -174,31 +174,56 @@ int nvk_decode_attention_paged_static(const void* query, const void* k_cache, co
  * Tensor-parallel all-reduce (sum, F16 / BF16) over NVLink peer memory for the latency-bound messages of a decode
  * step.  Replaces, for that case, NcclTensorParallelCommunicator::all_reduce_sum
  * (src/utils/tensor_parallel.cpp:331-353), called after o_proj and down_proj (src/layers/linear.cpp:315-318).
- * One process per GPU; every rank owns an addend buffer, a result buffer and a flag area of
- * nvk_tp_allreduce_flag_bytes() bytes (zeroed once), all mapped into every process (cudaIpc* or equivalent; plain peer
- * mappings, no multicast).  in_ptrs / out_ptrs / flag_ptrs are HOST arrays of `world` device pointers as mapped in the
- * calling process, index = rank.  Every rank calls with the same count (a multiple of 8 * world elements) in the same
- * order; the result, identical on all ranks, is in the caller's own out buffer when the launch completes.  The launch
- * may be captured in a CUDA graph.  Waits on peers are bounded (about one second); nvk_tp_allreduce_status copies the
- * error word of the caller's flag area to the host (synchronises the stream): 0 = ok, 1 / 2 = a peer never arrived.
+ *
+ * One process per GPU.  Every rank owns a STAGING area of at least nvk_tp_allreduce_stage_bytes(largest count) bytes
+ * and a FLAG area of nvk_tp_allreduce_flag_bytes() bytes, both zeroed once.  The staging areas are mapped into every
+ * process (cudaIpc* or equivalent; plain peer mappings, no multicast); stage_ptrs is a HOST array of `world` device
+ * pointers as mapped in the calling process, index = rank, and stage_bytes the size every one of them has (the same
+ * on all ranks).  The addend `in`, the result `out` and the flag area are ordinary device memory of the calling
+ * rank: peers never access them, so a GEMM may write `in` and read `out` in place.  Every rank calls with the same
+ * count (a multiple of 8 * world elements) in the same order; the result, identical on all ranks, is in `out` when the
+ * launch completes.  The launch may be captured in a CUDA graph.
+ *
+ * Failure contract.  A kernel waits only for data, and every wait is bounded (nvk_tp_allreduce_set_wait_limit_ms;
+ * 10 s unless set -- far above any skew between healthy ranks, since a rank that is merely late must not be taken
+ * for dead).  When a wait runs out the rank's error word becomes non-zero and STAYS so: every later launch of that
+ * rank returns at once without touching data, and its peers run into one time-out themselves.  nvk_tp_allreduce_status
+ * copies the word to the host (synchronises the stream): 0 = ok, 1 = an addend slice never arrived, 2 = a result slice
+ * never arrived.  A non-zero status means that the group is out of step and that every result since the last zero
+ * status is invalid.  To reuse the buffers all ranks must, under a host-side barrier and with no launch in flight,
+ * zero their staging areas and call nvk_tp_allreduce_reset (zeroes the flag area: error word and launch counter).
  */
 #define NVK_TP_MAX_RANKS 8
 size_t nvk_tp_allreduce_flag_bytes(void);
-int nvk_tp_allreduce(const void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank, int world,
-                     int64_t count, int dtype, void* stream);
-int nvk_tp_allreduce_status(const void* own_flags, void* stream, int* status);
+size_t nvk_tp_allreduce_stage_bytes(int64_t max_count);
+void nvk_tp_allreduce_set_wait_limit_ms(int ms);   /* process-wide; applies to launches made (or captured) afterwards */
+int nvk_tp_allreduce(const void* in, void* out, void* const* stage_ptrs, size_t stage_bytes, void* flags, int rank,
+                     int world, int64_t count, int dtype, void* stream);
+int nvk_tp_allreduce_status(const void* flags, void* stream, int* status);
+int nvk_tp_allreduce_reset(void* flags, void* stream);
 /*
  * The same all-reduce with the residual add and the RMSNorm that follow it in a decoder layer folded in:
- *   h_new = residual + bf16(sum over ranks of addend)   -> every rank's out buffer   [rows, cols]
- *   x     = rmsnorm(h_new, eps) * weight                -> every rank's norm buffer  [rows, cols]
+ *   h_new = residual + bf16(sum over ranks of addend)   -> out   [rows, cols]
+ *   x     = rmsnorm(h_new, eps) * weight                -> norm  [rows, cols]
  * rows must be a multiple of world (a rank reduces rows / world whole rows), cols a multiple of 8, at most 8192.
- * residual [rows, cols] is the caller's own copy (identical on all ranks), weight [cols]; both ordinary device memory.
+ * residual [rows, cols] is the caller's own copy (identical on all ranks; it may be `out` itself), weight [cols].
  * Rounding follows the unfused sequence (sum rounded to the 16-bit type, added to the residual in it, normalised from the
  * rounded h_new), so results agree with all-reduce + add + rms_norm to within one unit of the 16-bit type.
  */
-int nvk_tp_allreduce_add_rmsnorm(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
-                                 void* const* flag_ptrs, const void* residual, const void* weight, float eps,
-                                 int rank, int world, int rows, int cols, int dtype, void* stream);
+int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes,
+                                 void* flags, const void* residual, const void* weight, float eps, int rank, int world,
+                                 int rows, int cols, int dtype, void* stream);
+/*
+ * All `world` ranks of either form on ONE device in one cooperative launch: in_ptrs / out_ptrs / stage_ptrs /
+ * flag_ptrs (and, for the fused form, norm_ptrs / residual_ptrs; pass norm_ptrs == NULL for the plain sum) are host
+ * arrays of `world` pointers into the current device's memory, one buffer set per rank.  Same kernels, same protocol,
+ * same results as `world` processes; the counterpart of the reference's InProcessTensorParallelCommunicator
+ * (src/utils/tensor_parallel.cpp:165-277), for tests and single-GPU bring-up.
+ */
+int nvk_tp_allreduce_inprocess(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
+                               void* const* stage_ptrs, size_t stage_bytes, void* const* flag_ptrs,
+                               const void* const* residual_ptrs, const void* weight, float eps, int world, int rows,
+                               int cols, int dtype, void* stream);
 
 /*
  * Replaces nano_vllm::launch_prefill_attention_dense / launch_prefill_attention_paged

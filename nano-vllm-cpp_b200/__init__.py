@@ -27,7 +27,8 @@ EXPORTED_SYMBOLS = (
     "nvk_decode_attention_workspace_bytes", "nvk_decode_attention_paged",
     "nvk_prefill_attention_varlen", "nvk_decode_attention_paged_static",
     "nvk_store_kvcache_int8", "nvk_decode_attention_paged_int8",
-    "nvk_tp_allreduce_flag_bytes", "nvk_tp_allreduce", "nvk_tp_allreduce_status", "nvk_tp_allreduce_add_rmsnorm",
+    "nvk_tp_allreduce_flag_bytes", "nvk_tp_allreduce_stage_bytes", "nvk_tp_allreduce_set_wait_limit_ms", "nvk_tp_allreduce",
+    "nvk_tp_allreduce_status", "nvk_tp_allreduce_reset", "nvk_tp_allreduce_add_rmsnorm", "nvk_tp_allreduce_inprocess",
     "nvk_prefill_status", "nvk_decode_attention_static_scratch_bytes",
 )
 

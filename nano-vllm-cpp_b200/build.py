@@ -34,16 +34,20 @@ def sources() -> list[str]:
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
-def _deps_mtime() -> float:
-    files = sources() + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+def _headers() -> list[str]:
+    """Every header an object may depend on: csrc/*.cuh, csrc/*.h and the C ABI header."""
+    files = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     files.append(os.path.join(os.path.dirname(HERE), "include", "nvk.h"))
-    return max(os.path.getmtime(f) for f in files)
+    return files
+
+
+def _deps_mtime() -> float:
+    return max(os.path.getmtime(f) for f in sources() + _headers())
 
 
 def _compile(src: str, verbose: bool) -> str:
     obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
-    hdr_time = max(os.path.getmtime(os.path.join(CSRC, f)) for f in os.listdir(CSRC) if f.endswith(".cuh"))
-    hdr_time = max(hdr_time, os.path.getmtime(os.path.join(os.path.dirname(HERE), "include", "nvk.h")))
+    hdr_time = max(os.path.getmtime(f) for f in _headers())
     if os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_time):
         return obj
     cmd = [nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]

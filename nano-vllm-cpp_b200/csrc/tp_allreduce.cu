@@ -3,316 +3,486 @@
 // Replaces, for that case, NcclTensorParallelCommunicator::all_reduce_sum (src/utils/tensor_parallel.cpp:331-353 of the
 // reference), which the row-parallel linears call after o_proj and down_proj (src/layers/linear.cpp:315-318): 72
 // all-reduces of [rows, hidden] 16-bit per decode step, 2 MiB each at 256 rows -- far too small to be bandwidth bound.
+// The message crosses the wire in under 3 us; what such a collective costs is synchronisation, so this one has none
+// that is separate from the data: no flag exchange, no memory fence, no peer load.
 //
-// One process per GPU.  Every rank owns three buffers that all ranks have mapped (plain peer mappings, no multicast):
-// `in` (its addend), `out` (the result) and a small flag area.  One launch does a two-shot all-reduce:
-//   1. block c of rank r tells every peer "rank r has started" (flag A), i.e. its addend is complete, and waits for the
-//      same from every peer;
-//   2. it reduces slice c of chunk r (chunk = count / world) over all ranks' `in` buffers in fp32 -- peer loads -- and
-//      writes the rounded sums into slice c of chunk r of EVERY rank's `out` buffer -- peer stores;
-//   3. after a block barrier it tells every peer, with a system-scope release store, "slice c of chunk r has landed"
-//      (flag B) and waits for the same from every peer, so when the kernel ends the whole `out` buffer of this rank is
-//      complete.
-// Blocks never wait for other blocks of their own GPU, only for the block with the same index on the peers, so the
-// ranks' kernels need not be co-scheduled block for block.  Flags carry a launch counter (epoch) kept in device memory,
-// so a captured launch can be replayed.  Every wait is bounded (about one second): on a time-out the block raises an
-// error word in its own flag area, skips its remaining waits and returns; the host reads the word with
-// nvk_tp_allreduce_status.
+// One process per GPU.  Every rank owns a staging area that all ranks have mapped (plain peer mappings, no multicast);
+// addend, result, residual and norm buffers are ordinary memory of the rank that owns them -- peers never touch them.
+// Data crosses NVLink as self-validating words: a 16-byte vector of payload is stored as two 16-byte vectors
+// {w0, epoch, w1, epoch} {w2, epoch, w3, epoch}; each 8-byte half arrives atomically, so a receiver that sees `epoch`
+// in both tags of a vector holds its payload (the low-latency protocol NCCL uses for small messages).  The epoch is a
+// launch counter kept in device memory: the same on every rank, because all ranks run the same sequence of launches,
+// and different from whatever an earlier launch left in the slot.  One launch is a two-shot all-reduce, chunk r of
+// the message (count / world elements; whole rows in the fused form) being reduced by rank r:
+//   1. push    every rank stores the slices of its addend that belong to the other ranks' chunks into their staging
+//              areas (region A, indexed by source rank);
+//   2. reduce  it adds its own slice and the world - 1 slices arriving in its region A in fp32, in rank order, rounds
+//              once (the fused form then adds the residual row and computes the row's RMSNorm);
+//   3. push    it stores the result slice into every other rank's region B and into its own output buffers;
+//   4. gather  it copies the other chunks' results from its region B into its output buffers as they arrive (the fused
+//              form computes their RMSNorm on the way, so only one row per result crosses the wire).
+// Blocks only ever wait for data, and only for the data of the same-numbered block of the peers.  A staging slot is
+// never overwritten before it was read: a rank can only start launch L + 1 after every peer finished reducing launch L
+// (it holds their results), and it writes region B of launch L + 1 only after every peer pushed region A of L + 1,
+// which they do after finishing all of L.
+//
+// Every wait is bounded (nvk_tp_allreduce_set_wait_limit_ms, 10 s unless set).  A block whose wait runs out raises the
+// error word in its rank's flag area; from then on every launch of that rank returns at once (the error is sticky), so
+// a dead peer costs one time-out, not one per launch, and peers of a rank that gave up time out once themselves.
+// Results since the last zero status are invalid; see nvk_tp_allreduce_reset for re-arming.
+//
+// The same device code also runs `world` ranks on ONE device in one cooperative launch
+// (nvk_tp_allreduce_inprocess): the counterpart of the reference's in-process communicator
+// (src/utils/tensor_parallel.cpp:165-277), used to test the protocol where only one GPU is present.
 #include "nvk_internal.cuh"
+
+#include <atomic>
 
 namespace nvk {
 namespace {
 
-constexpr int kArBlocks = 128;           // most blocks a launch uses = flag slots per phase
-constexpr int kArUnroll = 2;             // vectors a thread has in flight
+constexpr int kArBlocks = 128;           // most blocks per rank
 constexpr int kArThreads = 256;
-constexpr long long kArWaitCycles = 2000000000LL;
+constexpr int kMaxVecs = 4;              // 16-byte vectors of a row per thread (fused form): cols <= 256 * 4 * 8 = 8192
+constexpr int kFlagWords = 64;           // flag area: [0] epoch of the last completed launch, [1] blocks finished, [2] error word
+
+std::atomic<long long> g_wait_cycles{20000000000LL};   // about 10 s at 2 GHz
 
 struct ArParams {
-    const void* in[NVK_TP_MAX_RANKS];    // every rank's addend (index = rank), as mapped in this process
-    void* out[NVK_TP_MAX_RANKS];         // every rank's result buffer
-    uint32_t* flags[NVK_TP_MAX_RANKS];   // every rank's flag area
-    int rank, world;
-    int64_t count;                       // elements; a multiple of 8 * world
+    const void* in;                          // this rank's addend
+    void* out;                               // this rank's result buffer (h_new in the fused form)
+    void* norm;                              // fused form: this rank's buffer for x
+    const void* residual;                    // fused form: [rows, cols], this rank's copy (identical on all ranks)
+    const void* weight;                      // fused form: [cols]
+    uint4* stage[NVK_TP_MAX_RANKS];          // every rank's staging area as mapped in this process (index = rank)
+    uint32_t* flags;                         // this rank's flag area
+    int64_t region_b;                        // offset of region B inside a staging area, in uint4
+    int64_t chunk_vecs;                      // 16-byte payload vectors per rank chunk
+    int64_t seg_vecs;                        // payload vectors per block segment (fused form: one row)
+    long long wait_cycles;
+    float eps;
+    int rank, world, cols;
 };
+struct ArGroup { ArParams r[NVK_TP_MAX_RANKS]; };   // in-process form: one parameter set per rank
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_tagged(uint4* slot, const uint4& v, uint32_t ep) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(slot), "r"(v.x), "r"(ep), "r"(v.y), "r"(ep) : "memory");
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(slot + 1), "r"(v.z), "r"(ep), "r"(v.w), "r"(ep) : "memory");
 }
-__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint4 ld_peer16(const void* p) {
+__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
     uint4 v;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
-// Flag area layout (uint32): [0] epoch of the last completed launch, [1] blocks finished in the current launch,
-// [2] error word, [3] unused, then phase A slots [block][rank], then phase B slots [block][rank].
-__device__ __forceinline__ uint32_t* flag_slot(uint32_t* base, int phase, int block, int rank) {
-    return base + 4 + (phase * kArBlocks + block) * NVK_TP_MAX_RANKS + rank;
-}
-
-// Thread r < world of the block: publish `epoch` in slot [phase][block][my rank] of rank r's flags, then wait until rank r
-// has published it in mine.  Returns false (whole block) when a wait ran out.
-//
-// Phase 0 publishes with a relaxed store: what it announces (this rank's addend) was written by earlier kernels of the
-// stream into this GPU's own memory and is complete at the kernel boundary, and nothing this kernel wrote precedes it.
-// A release store there costs about 4 us for nothing.  Phase 1 publishes with a release store after the block's
-// __syncthreads(): the barrier orders every thread's peer stores before the publishing thread, and its release makes
-// them visible system-wide before the flag (no per-thread system fence, which cost another 7 us).
-__device__ __forceinline__ bool exchange(const ArParams& p, int phase, uint32_t epoch, int* timed_out) {
-    const int r = threadIdx.x;
-    if (r < p.world) {
-        if (phase == 0) st_relaxed_sys(flag_slot(p.flags[r], phase, blockIdx.x, p.rank), epoch);
-        else st_release_sys(flag_slot(p.flags[r], phase, blockIdx.x, p.rank), epoch);
-        const uint32_t* mine = flag_slot(p.flags[p.rank], phase, blockIdx.x, r);
-        const long long start = clock64();
-        while (ld_acquire_sys(mine) != epoch) {
-            if (clock64() - start > kArWaitCycles) {
-                atomicExch(reinterpret_cast<unsigned int*>(p.flags[p.rank] + 2), 1u + static_cast<unsigned int>(phase));
-                *timed_out = 1;
-                break;
+// Waits until the tagged vectors slot[k] (k < n, k != skip; at most NVK_TP_MAX_RANKS) all carry `ep`, returns their
+// payloads.  All loads of a round are issued before any tag is looked at, so the round costs one memory latency.
+// Every index is a compile-time constant after unrolling (the arrays stay in registers).  Gives up (payload
+// undefined) when the limit runs out or another thread of the block already gave up.
+struct Waiter {
+    const ArParams& p;
+    int* gave_up;          // shared: set by the first thread whose wait ran out
+    int code;
+    __device__ __forceinline__ void poll(const uint4* const (&slot)[NVK_TP_MAX_RANKS], int n, int skip, uint32_t ep,
+                                         uint4 (&payload)[NVK_TP_MAX_RANKS]) const {
+        long long start = 0;
+        while (true) {
+            uint4 a[NVK_TP_MAX_RANKS], b[NVK_TP_MAX_RANKS];
+#pragma unroll
+            for (int k = 0; k < NVK_TP_MAX_RANKS; ++k)
+                if (k < n && k != skip) { a[k] = ld_volatile16(slot[k]); b[k] = ld_volatile16(slot[k] + 1); }
+            bool ready = true;
+#pragma unroll
+            for (int k = 0; k < NVK_TP_MAX_RANKS; ++k)
+                if (k < n && k != skip) {
+                    ready = ready && a[k].y == ep && a[k].w == ep && b[k].y == ep && b[k].w == ep;
+                    payload[k] = make_uint4(a[k].x, a[k].z, b[k].x, b[k].z);
+                }
+            if (ready) return;
+            if (*reinterpret_cast<volatile int*>(gave_up)) return;
+            if (start == 0) start = clock64();
+            else if (clock64() - start > p.wait_cycles) {
+                *reinterpret_cast<volatile int*>(gave_up) = 1;
+                atomicCAS(reinterpret_cast<unsigned int*>(p.flags + 2), 0u, static_cast<unsigned int>(code));
+                return;
             }
         }
     }
-    __syncthreads();
-    return *timed_out == 0;
-}
+};
 
 template <typename T>
-__global__ void __launch_bounds__(kArThreads) allreduce_two_shot_kernel(const ArParams p) {
-    __shared__ int s_timed_out;
-    if (threadIdx.x == 0) s_timed_out = 0;
+__device__ __forceinline__ void accumulate(float (&acc)[8], const uint4& v) {
+    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += ElemTraits<T>::to_float(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 round_pack(const float (&acc)[8]) {
+    uint4 r;
+    r.x = ElemTraits<T>::pack2(acc[0], acc[1]); r.y = ElemTraits<T>::pack2(acc[2], acc[3]);
+    r.z = ElemTraits<T>::pack2(acc[4], acc[5]); r.w = ElemTraits<T>::pack2(acc[6], acc[7]);
+    return r;
+}
+
+// Block-wide sum of one float per thread (every thread gets the total).  `scratch` holds kArThreads / 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();   // scratch of the previous use has been read by everyone
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
     __syncthreads();
-    uint32_t* my_flags = p.flags[p.rank];
-    const uint32_t epoch = my_flags[0] + 1u;   // the same on every rank: all ranks run the same sequence of launches
-
-    bool ok = exchange(p, 0, epoch, &s_timed_out);   // every addend is complete
-
-    if (ok) {
-        const int64_t chunk_vecs = p.count / p.world / 8;          // 16-byte vectors in one rank's chunk
-        const int64_t per_block = (chunk_vecs + gridDim.x - 1) / gridDim.x;
-        const int64_t v0 = static_cast<int64_t>(blockIdx.x) * per_block;
-        const int64_t v1 = v0 + per_block < chunk_vecs ? v0 + per_block : chunk_vecs;
-        const int64_t base = static_cast<int64_t>(p.rank) * chunk_vecs;   // this rank reduces chunk `rank`
-        for (int64_t vb = v0 + threadIdx.x; vb < v1; vb += kArThreads * kArUnroll) {
-            uint4 part[kArUnroll][NVK_TP_MAX_RANKS];
+    float total = 0.0f;
 #pragma unroll
-            for (int u = 0; u < kArUnroll; ++u) {   // every load of this round first: peer latency is paid once
-                const int64_t v = vb + u * kArThreads;
+    for (int w = 0; w < kArThreads / 32; ++w) total += scratch[w];
+    return total;
+}
+
+// x = h * rsqrt(mean(h^2) + eps) * weight for this thread's vectors of one row; h as rounded to T.
+template <typename T>
+__device__ __forceinline__ void norm_row(const ArParams& p, const uint4 (&h)[kMaxVecs], int row_vecs, int64_t row_base,
+                                         float* scratch) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kMaxVecs; ++u) {
+        if (static_cast<int>(threadIdx.x) + u * kArThreads < row_vecs) {
+            const T* e = reinterpret_cast<const T*>(&h[u]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { const float f = ElemTraits<T>::to_float(e[i]); ss += f * f; }
+        }
+    }
+    const float inv_rms = rsqrtf(block_sum(ss, scratch) / static_cast<float>(p.cols) + p.eps);
+#pragma unroll
+    for (int u = 0; u < kMaxVecs; ++u) {
+        const int v = static_cast<int>(threadIdx.x) + u * kArThreads;
+        if (v < row_vecs) {
+            const uint4 wv = __ldg(static_cast<const uint4*>(p.weight) + v);
+            const T* we = reinterpret_cast<const T*>(&wv);
+            const T* e = reinterpret_cast<const T*>(&h[u]);
+            float x[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = ElemTraits<T>::to_float(e[i]) * inv_rms * ElemTraits<T>::to_float(we[i]);
+            static_cast<uint4*>(p.norm)[row_base + v] = round_pack<T>(x);
+        }
+    }
+}
+
+// One rank's part of one launch, as block `block` of `blocks`.
+template <typename T, bool FUSED>
+__device__ __forceinline__ void allreduce_body(const ArParams& p, int block, int blocks) {
+    __shared__ int s_gave_up;
+    __shared__ float s_scratch[kArThreads / 32];
+    if (threadIdx.x == 0) s_gave_up = 0;
+    __syncthreads();
+    const uint32_t last = *reinterpret_cast<volatile uint32_t*>(p.flags);
+    const uint32_t epoch = last + 1u == 0u ? 1u : last + 1u;     // never 0: staging areas start zeroed
+    const bool poisoned = *reinterpret_cast<volatile uint32_t*>(p.flags + 2) != 0u;
+    const int tid = threadIdx.x;
+    const uint4* in = static_cast<const uint4*>(p.in);
+    uint4* out = static_cast<uint4*>(p.out);
+    const int64_t segs = (p.chunk_vecs + p.seg_vecs - 1) / p.seg_vecs;      // segments per chunk
+    const int seg_len = static_cast<int>(p.seg_vecs);
+
+    if (!poisoned) {
+        // ---- 1. push this rank's slices of the other ranks' chunks ---------------------------------------------
+        for (int64_t seg = block; seg < segs; seg += blocks) {
+            const int64_t v0 = seg * p.seg_vecs;
+            const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
+            for (int v = tid; v < n; v += kArThreads) {
+                uint4 mine[NVK_TP_MAX_RANKS];
 #pragma unroll
                 for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
-                    if (r < p.world && v < v1) part[u][r] = ld_peer16(static_cast<const uint4*>(p.in[r]) + base + v);
-            }
-#pragma unroll
-            for (int u = 0; u < kArUnroll; ++u) {
-                const int64_t v = vb + u * kArThreads;
-                if (v >= v1) break;
-                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) {
-                    if (r < p.world) {
-                        const T* e = reinterpret_cast<const T*>(&part[u][r]);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] += ElemTraits<T>::to_float(e[i]);
-                    }
-                }
-                uint4 sum;
-                sum.x = ElemTraits<T>::pack2(acc[0], acc[1]); sum.y = ElemTraits<T>::pack2(acc[2], acc[3]);
-                sum.z = ElemTraits<T>::pack2(acc[4], acc[5]); sum.w = ElemTraits<T>::pack2(acc[6], acc[7]);
+                    if (r < p.world && r != p.rank) mine[r] = in[r * p.chunk_vecs + v0 + v];
 #pragma unroll
                 for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
-                    if (r < p.world) static_cast<uint4*>(p.out[r])[base + v] = sum;
+                    if (r < p.world && r != p.rank) st_tagged(p.stage[r] + 2 * (p.rank * p.chunk_vecs + v0 + v), mine[r], epoch);
             }
         }
-        __syncthreads();          // every thread's peer stores precede the release store of the publishing threads
-        ok = exchange(p, 1, epoch, &s_timed_out);   // every rank's slice of every chunk has landed here
+        // ---- 2. reduce this rank's chunk, 3. push the results ---------------------------------------------------
+        const uint4* stage_a = p.stage[p.rank];
+        const Waiter waiter_a{p, &s_gave_up, 1};
+        for (int64_t seg = block; seg < segs; seg += blocks) {
+            const int64_t v0 = seg * p.seg_vecs;
+            const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
+            const int64_t base = p.rank * p.chunk_vecs + v0;            // position in the whole message
+            auto reduce_one = [&](int v) -> uint4 {
+                const uint4 own = in[base + v];
+                const uint4* slot[NVK_TP_MAX_RANKS];
+                uint4 got[NVK_TP_MAX_RANKS];
+#pragma unroll
+                for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) slot[r] = stage_a + 2 * (r * p.chunk_vecs + v0 + v);
+                waiter_a.poll(slot, p.world, p.rank, epoch, got);
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) {      // rank order, whoever does the adding
+                    if (r < p.world) {
+                        if (r == p.rank) accumulate<T>(acc, own);
+                        else accumulate<T>(acc, got[r]);
+                    }
+                }
+                if (FUSED) {
+                    // the sum is rounded to T first (what the all-reduce alone would deliver), then the residual is added in T
+                    const uint4 res = static_cast<const uint4*>(p.residual)[base + v];
+                    const T* e0 = reinterpret_cast<const T*>(&res);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        acc[i] = ElemTraits<T>::to_float(e0[i]) + ElemTraits<T>::to_float(ElemTraits<T>::from_float(acc[i]));
+                }
+                const uint4 h = round_pack<T>(acc);
+                // a rank that gave up publishes nothing more: a peer that is merely late must run into its own
+                // time-out instead of accepting a result made from slices that never arrived
+                if (*reinterpret_cast<volatile int*>(&s_gave_up)) return h;
+#pragma unroll
+                for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
+                    if (r < p.world && r != p.rank) st_tagged(p.stage[r] + 2 * (p.region_b + base + v), h, epoch);
+                out[base + v] = h;
+                return h;
+            };
+            if (FUSED) {                       // a segment is one row, at most kMaxVecs vectors per thread: keep them for the norm
+                uint4 h[kMaxVecs];
+#pragma unroll
+                for (int u = 0; u < kMaxVecs; ++u)
+                    if (tid + u * kArThreads < n) h[u] = reduce_one(tid + u * kArThreads);
+                norm_row<T>(p, h, n, base, s_scratch);
+            } else {
+                for (int v = tid; v < n; v += kArThreads) reduce_one(v);
+            }
+        }
+        // ---- 4. gather the other chunks' results ---------------------------------------------------------------
+        const uint4* stage_b = p.stage[p.rank] + 2 * p.region_b;
+        const Waiter waiter_b{p, &s_gave_up, 2};
+        for (int64_t seg = block; seg < segs; seg += blocks) {
+            const int64_t v0 = seg * p.seg_vecs;
+            const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
+            if (FUSED) {
+                for (int s = 0; s < p.world; ++s) {
+                    if (s == p.rank) continue;
+                    const int64_t base = s * p.chunk_vecs + v0;
+                    uint4 h[kMaxVecs];
+                    {
+                        const uint4* slot[NVK_TP_MAX_RANKS];
+                        uint4 got[NVK_TP_MAX_RANKS];
+                        const int mine = tid < n ? (n - tid + kArThreads - 1) / kArThreads : 0;   // this thread's vectors: u < mine
+#pragma unroll
+                        for (int u = 0; u < kMaxVecs; ++u) slot[u] = stage_b + 2 * (base + tid + u * kArThreads);
+                        waiter_b.poll(slot, mine, -1, epoch, got);
+                        const bool abandoned = *reinterpret_cast<volatile int*>(&s_gave_up) != 0;
+#pragma unroll
+                        for (int u = 0; u < kMaxVecs; ++u)
+                            if (u < mine) { h[u] = got[u]; if (!abandoned) out[base + tid + u * kArThreads] = got[u]; }
+                    }
+                    norm_row<T>(p, h, n, base, s_scratch);
+                }
+            } else {
+                for (int v = tid; v < n; v += kArThreads) {
+                    const uint4* slot[NVK_TP_MAX_RANKS];
+                    uint4 got[NVK_TP_MAX_RANKS];
+#pragma unroll
+                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) slot[r] = stage_b + 2 * (r * p.chunk_vecs + v0 + v);
+                    waiter_b.poll(slot, p.world, p.rank, epoch, got);
+                    if (*reinterpret_cast<volatile int*>(&s_gave_up)) break;
+#pragma unroll
+                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
+                        if (r < p.world && r != p.rank) out[r * p.chunk_vecs + v0 + v] = got[r];
+                }
+            }
+        }
     }
 
     // the last block of the launch publishes the epoch for the next launch
+    __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(reinterpret_cast<unsigned int*>(my_flags + 1), 1u) == gridDim.x - 1) {
-            my_flags[1] = 0u;
-            my_flags[0] = epoch;
+        if (atomicAdd(reinterpret_cast<unsigned int*>(p.flags + 1), 1u) == static_cast<unsigned int>(blocks) - 1u) {
+            p.flags[1] = 0u;
+            p.flags[0] = epoch;
             __threadfence();
         }
     }
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// The same all-reduce with the two element-wise kernels that follow it in a decoder layer folded in:
-//     h_new = residual + sum over ranks of addend          (src/layers/linear.cpp:315-318 then the residual add)
-//     x     = rmsnorm(h_new) * weight                      (the layer norm that consumes h_new next)
-// A rank's chunk of the [rows, cols] message is rows / world whole rows, so the rank that reduces a row also has all of
-// it for the mean of squares: it adds its (replicated) residual row, rounds to T, normalises the rounded values as the
-// separate kernel would, and pushes both rows into every rank's `out` (h_new) and `norm` (x) buffers.
-// ---------------------------------------------------------------------------------------------------------------
-constexpr int kNormMaxVecs = 4;   // 16-byte vectors of a row per thread: cols <= 256 * 4 * 8 = 8192
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(kArThreads) allreduce_ll_kernel(const ArParams p) {
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");             // the addend comes from the kernel before this one
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    allreduce_body<T, FUSED>(p, blockIdx.x, gridDim.x);
+}
 
-struct ArNormParams {
-    ArParams ar;
-    void* norm[NVK_TP_MAX_RANKS];     // every rank's buffer for x
-    const void* residual;             // [rows, cols], this rank's copy (identical on all ranks)
-    const void* weight;               // [cols]
-    float eps;
-    int rows, cols;
-};
+// `world` ranks on one device: blockIdx.y is the rank.  Launched cooperatively, so all blocks are resident and the
+// ranks can wait for one another's data.
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(kArThreads) allreduce_ll_inprocess_kernel(const ArGroup g) {
+    allreduce_body<T, FUSED>(g.r[blockIdx.y], blockIdx.x, gridDim.x);
+}
 
-template <typename T>
-__global__ void __launch_bounds__(kArThreads) allreduce_add_rmsnorm_kernel(const ArNormParams q) {
-    const ArParams& p = q.ar;
-    __shared__ int s_timed_out;
-    __shared__ float s_part[kArThreads / 32];
-    if (threadIdx.x == 0) s_timed_out = 0;
-    __syncthreads();
-    uint32_t* my_flags = p.flags[p.rank];
-    const uint32_t epoch = my_flags[0] + 1u;
+struct Plan { int64_t chunk_vecs, seg_vecs; int blocks; };
 
-    bool ok = exchange(p, 0, epoch, &s_timed_out);
+// Blocks per rank and segment size: the same on every rank (they depend on the message only).
+Plan plan_plain(int64_t count, int world) {
+    Plan pl{};
+    pl.chunk_vecs = count / world / 8;
+    int64_t blocks = (pl.chunk_vecs + kArThreads - 1) / kArThreads;    // about one vector per thread
+    if (blocks < 1) blocks = 1;
+    if (blocks > kArBlocks) blocks = kArBlocks;
+    pl.seg_vecs = (pl.chunk_vecs + blocks - 1) / blocks;
+    pl.blocks = static_cast<int>((pl.chunk_vecs + pl.seg_vecs - 1) / pl.seg_vecs);
+    return pl;
+}
+Plan plan_fused(int rows, int cols, int world) {
+    Plan pl{};
+    pl.seg_vecs = cols / 8;
+    pl.chunk_vecs = static_cast<int64_t>(rows / world) * pl.seg_vecs;
+    pl.blocks = rows / world < kArBlocks ? rows / world : kArBlocks;
+    return pl;
+}
 
-    if (ok) {
-        const int rows_per_rank = q.rows / p.world;
-        const int row_vecs = q.cols / 8;
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-        for (int lr = blockIdx.x; lr < rows_per_rank; lr += gridDim.x) {
-            const int64_t row = static_cast<int64_t>(p.rank) * rows_per_rank + lr;
-            const int64_t base = row * row_vecs;
-            uint4 part[kNormMaxVecs][NVK_TP_MAX_RANKS];
-            uint4 res[kNormMaxVecs];
-#pragma unroll
-            for (int u = 0; u < kNormMaxVecs; ++u) {   // every load first
-                const int v = threadIdx.x + u * kArThreads;
-                if (v < row_vecs) {
-                    res[u] = static_cast<const uint4*>(q.residual)[base + v];
-#pragma unroll
-                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
-                        if (r < p.world) part[u][r] = ld_peer16(static_cast<const uint4*>(p.in[r]) + base + v);
-                }
-            }
-            float hn[kNormMaxVecs][8];
-            uint4 hpack[kNormMaxVecs];
-            float ss = 0.0f;
-#pragma unroll
-            for (int u = 0; u < kNormMaxVecs; ++u) {
-                const int v = threadIdx.x + u * kArThreads;
-                if (v < row_vecs) {
-                    float acc[8];
-                    const T* e0 = reinterpret_cast<const T*>(&res[u]);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-#pragma unroll
-                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) {
-                        if (r < p.world) {
-                            const T* e = reinterpret_cast<const T*>(&part[u][r]);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) acc[i] += ElemTraits<T>::to_float(e[i]);
-                        }
-                    }
-                    // the sum is rounded to T first (what the all-reduce alone would deliver), then the residual is added in T
-                    T* hp = reinterpret_cast<T*>(&hpack[u]);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float s = ElemTraits<T>::to_float(ElemTraits<T>::from_float(acc[i]));
-                        hp[i] = ElemTraits<T>::from_float(ElemTraits<T>::to_float(e0[i]) + s);
-                        hn[u][i] = ElemTraits<T>::to_float(hp[i]);
-                        ss += hn[u][i] * hn[u][i];
-                    }
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            __syncthreads();   // s_part of the previous row has been read by everyone
-            if (lane == 0) s_part[warp] = ss;
-            __syncthreads();
-            float total = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kArThreads / 32; ++w) total += s_part[w];
-            const float inv_rms = rsqrtf(total / static_cast<float>(q.cols) + q.eps);
-#pragma unroll
-            for (int u = 0; u < kNormMaxVecs; ++u) {
-                const int v = threadIdx.x + u * kArThreads;
-                if (v < row_vecs) {
-                    const uint4 wv = static_cast<const uint4*>(q.weight)[v];
-                    const T* we = reinterpret_cast<const T*>(&wv);
-                    uint4 xpack;
-                    T* xp = reinterpret_cast<T*>(&xpack);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        xp[i] = ElemTraits<T>::from_float(hn[u][i] * inv_rms * ElemTraits<T>::to_float(we[i]));
-#pragma unroll
-                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r) {
-                        if (r < p.world) {
-                            static_cast<uint4*>(p.out[r])[base + v] = hpack[u];
-                            static_cast<uint4*>(q.norm[r])[base + v] = xpack;
-                        }
-                    }
-                }
-            }
-        }
-        __syncthreads();
-        ok = exchange(p, 1, epoch, &s_timed_out);
+int check_common(const char* what, void* const* stage_ptrs, const void* flags, int rank, int world, int dtype, size_t stage_bytes,
+                 int64_t count) {
+    if (!stage_ptrs || !flags) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: staging table and flag area must be defined", what);
+    if (world < 2 || world > NVK_TP_MAX_RANKS || rank < 0 || rank >= world)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "%s: world must be 2..%d and rank inside it", what, NVK_TP_MAX_RANKS);
+    if (dtype != NVK_F16 && dtype != NVK_BF16) return fail(NVK_ERR_UNSUPPORTED, "%s: dtype must be F16 or BF16", what);
+    if (count <= 0 || count % (8 * world) != 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "%s: count must be a positive multiple of 8 * world", what);
+    if (stage_bytes < nvk_tp_allreduce_stage_bytes(count))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "%s: staging areas of %zu bytes given, %zu needed for %lld elements", what, stage_bytes,
+                    nvk_tp_allreduce_stage_bytes(count), static_cast<long long>(count));
+    for (int r = 0; r < world; ++r) {
+        if (!stage_ptrs[r]) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: null staging area of rank %d", what, r);
+        if (!aligned_to(stage_ptrs[r], 16)) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: staging areas must be 16-byte aligned", what);
     }
+    if (!aligned_to(flags, 16)) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: the flag area must be 16-byte aligned", what);
+    return NVK_OK;
+}
 
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(reinterpret_cast<unsigned int*>(my_flags + 1), 1u) == gridDim.x - 1) {
-            my_flags[1] = 0u;
-            my_flags[0] = epoch;
-            __threadfence();
-        }
-    }
+void fill_common(ArParams& p, void* const* stage_ptrs, void* flags, int rank, int world, size_t stage_bytes, const Plan& pl) {
+    for (int r = 0; r < world; ++r) p.stage[r] = static_cast<uint4*>(stage_ptrs[r]);
+    p.flags = static_cast<uint32_t*>(flags);
+    p.region_b = static_cast<int64_t>(stage_bytes / 2 / 32);   // in payload vectors: two uint4 each
+    p.chunk_vecs = pl.chunk_vecs; p.seg_vecs = pl.seg_vecs;
+    p.wait_cycles = g_wait_cycles.load(std::memory_order_relaxed);
+    p.rank = rank; p.world = world;
+}
+
+template <bool FUSED>
+int launch(const ArParams& p, int blocks, int dtype, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(kArThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = dtype == NVK_BF16 ? cudaLaunchKernelEx(&cfg, allreduce_ll_kernel<__nv_bfloat16, FUSED>, p)
+                                             : cudaLaunchKernelEx(&cfg, allreduce_ll_kernel<__half, FUSED>, p);
+    if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "tp all-reduce launch: %s", cudaGetErrorString(e));
+    return check_launch("tp all-reduce launch");
 }
 
 }  // namespace
 }  // namespace nvk
 
-extern "C" size_t nvk_tp_allreduce_flag_bytes(void) {
-    return (4 + 2 * nvk::kArBlocks * NVK_TP_MAX_RANKS) * sizeof(uint32_t);
+extern "C" size_t nvk_tp_allreduce_flag_bytes(void) { return nvk::kFlagWords * sizeof(uint32_t); }
+
+// Two regions (incoming addend slices, incoming results), each holding the whole message as tagged vectors (2 x payload).
+extern "C" size_t nvk_tp_allreduce_stage_bytes(int64_t max_count) {
+    if (max_count <= 0) return 0;
+    const size_t region = (static_cast<size_t>(max_count) * 2 * 2 + 255) / 256 * 256;
+    return 2 * region;
 }
 
-extern "C" int nvk_tp_allreduce(const void* const* in_ptrs, void* const* out_ptrs, void* const* flag_ptrs, int rank, int world,
-                                int64_t count, int dtype, void* stream) {
+extern "C" void nvk_tp_allreduce_set_wait_limit_ms(int ms) {
+    if (ms < 1) ms = 1;
+    nvk::g_wait_cycles.store(static_cast<long long>(ms) * 2000000LL, std::memory_order_relaxed);   // cycles at 2 GHz
+}
+
+extern "C" int nvk_tp_allreduce(const void* in, void* out, void* const* stage_ptrs, size_t stage_bytes, void* flags, int rank,
+                                int world, int64_t count, int dtype, void* stream) {
     using namespace nvk;
-    if (!in_ptrs || !out_ptrs || !flag_ptrs) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce: pointer tables must be defined");
-    if (world < 2 || world > NVK_TP_MAX_RANKS || rank < 0 || rank >= world)
-        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce: world must be 2..%d and rank inside it", NVK_TP_MAX_RANKS);
-    if (dtype != NVK_F16 && dtype != NVK_BF16) return fail(NVK_ERR_UNSUPPORTED, "tp all-reduce: dtype must be F16 or BF16");
-    if (count <= 0 || count % (8 * world) != 0)
-        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce: count must be a positive multiple of 8 * world");
+    const int rc = check_common("tp all-reduce", stage_ptrs, flags, rank, world, dtype, stage_bytes, count);
+    if (rc != NVK_OK) return rc;
+    if (!in || !out) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce: addend and result must be defined");
+    if (!aligned_to(in, 16) || !aligned_to(out, 16)) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce: buffers must be 16-byte aligned");
+    const Plan pl = plan_plain(count, world);
     ArParams p{};
-    for (int r = 0; r < world; ++r) {
-        if (!in_ptrs[r] || !out_ptrs[r] || !flag_ptrs[r]) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce: null buffer of rank %d", r);
-        if (!aligned_to(in_ptrs[r], 16) || !aligned_to(out_ptrs[r], 16) || !aligned_to(flag_ptrs[r], 4))
-            return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce: buffers must be 16-byte aligned");
-        p.in[r] = in_ptrs[r]; p.out[r] = out_ptrs[r]; p.flags[r] = static_cast<uint32_t*>(flag_ptrs[r]);
-    }
-    p.rank = rank; p.world = world; p.count = count;
-    // blocks: about kArUnroll rounds of work per thread, the same number on every rank (it depends on count and world only)
-    const int64_t chunk_vecs = count / world / 8;
-    int64_t blocks = (chunk_vecs + kArThreads * kArUnroll - 1) / (kArThreads * kArUnroll);
-    if (blocks < 4) blocks = 4;
-    if (blocks > kArBlocks) blocks = kArBlocks;
-    const unsigned grid = static_cast<unsigned>(blocks);
-    if (dtype == NVK_BF16)
-        allreduce_two_shot_kernel<__nv_bfloat16><<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    else
-        allreduce_two_shot_kernel<__half><<<grid, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    return check_launch("allreduce_two_shot_kernel launch");
+    fill_common(p, stage_ptrs, flags, rank, world, stage_bytes, pl);
+    p.in = in; p.out = out;
+    return launch<false>(p, pl.blocks, dtype, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int nvk_tp_allreduce_status(const void* own_flags, void* stream, int* status) {
+extern "C" int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes,
+                                            void* flags, const void* residual, const void* weight, float eps, int rank, int world,
+                                            int rows, int cols, int dtype, void* stream) {
     using namespace nvk;
-    if (!own_flags || !status) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce status: null argument");
+    const char* what = "tp all-reduce + add + rmsnorm";
+    if (rows <= 0 || world <= 0 || rows % world != 0) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: rows must be a positive multiple of world", what);
+    if (cols <= 0 || cols % 8 != 0 || cols > kArThreads * kMaxVecs * 8)
+        return fail(NVK_ERR_UNSUPPORTED, "%s: cols must be a multiple of 8 and at most %d", what, kArThreads * kMaxVecs * 8);
+    const int rc = check_common(what, stage_ptrs, flags, rank, world, dtype, stage_bytes, static_cast<int64_t>(rows) * cols);
+    if (rc != NVK_OK) return rc;
+    if (!in || !out || !norm || !residual || !weight) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: every pointer must be defined", what);
+    if (!aligned_to(in, 16) || !aligned_to(out, 16) || !aligned_to(norm, 16) || !aligned_to(residual, 16) || !aligned_to(weight, 16))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "%s: buffers must be 16-byte aligned", what);
+    const Plan pl = plan_fused(rows, cols, world);
+    ArParams p{};
+    fill_common(p, stage_ptrs, flags, rank, world, stage_bytes, pl);
+    p.in = in; p.out = out; p.norm = norm; p.residual = residual; p.weight = weight; p.eps = eps; p.cols = cols;
+    return launch<true>(p, pl.blocks, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvk_tp_allreduce_inprocess(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
+                                          void* const* stage_ptrs, size_t stage_bytes, void* const* flag_ptrs,
+                                          const void* const* residual_ptrs, const void* weight, float eps, int world, int rows,
+                                          int cols, int dtype, void* stream) {
+    using namespace nvk;
+    const char* what = "tp all-reduce (in-process)";
+    const bool fused = norm_ptrs != nullptr;
+    if (!in_ptrs || !out_ptrs || !flag_ptrs) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: pointer tables must be defined", what);
+    if (rows <= 0 || cols <= 0 || cols % 8 != 0) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: rows and cols must be positive, cols a multiple of 8", what);
+    if (fused && (world <= 0 || rows % world != 0 || cols > kArThreads * kMaxVecs * 8 || !residual_ptrs || !weight))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "%s: the fused form needs rows %% world == 0, cols <= %d, residuals and a weight", what,
+                    kArThreads * kMaxVecs * 8);
+    const int64_t count = static_cast<int64_t>(rows) * cols;
+    if (world < 2 || world > NVK_TP_MAX_RANKS) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: world must be 2..%d", what, NVK_TP_MAX_RANKS);
+    ArGroup g{};
+    Plan pl{};
+    for (int r = 0; r < world; ++r) {
+        const int rc = check_common(what, stage_ptrs, flag_ptrs[r], r, world, dtype, stage_bytes, count);
+        if (rc != NVK_OK) return rc;
+        if (!in_ptrs[r] || !out_ptrs[r] || (fused && (!norm_ptrs[r] || !residual_ptrs[r])))
+            return fail(NVK_ERR_INVALID_ARGUMENT, "%s: null buffer of rank %d", what, r);
+        pl = fused ? plan_fused(rows, cols, world) : plan_plain(count, world);
+        fill_common(g.r[r], stage_ptrs, flag_ptrs[r], r, world, stage_bytes, pl);
+        g.r[r].in = in_ptrs[r]; g.r[r].out = out_ptrs[r];
+        if (fused) { g.r[r].norm = norm_ptrs[r]; g.r[r].residual = residual_ptrs[r]; g.r[r].weight = weight; g.r[r].eps = eps; g.r[r].cols = cols; }
+    }
+    // every block of every rank must be resident at once: ask the occupancy calculator, shrink the grid if needed
+    const void* fn = fused ? (dtype == NVK_BF16 ? reinterpret_cast<const void*>(allreduce_ll_inprocess_kernel<__nv_bfloat16, true>)
+                                                : reinterpret_cast<const void*>(allreduce_ll_inprocess_kernel<__half, true>))
+                           : (dtype == NVK_BF16 ? reinterpret_cast<const void*>(allreduce_ll_inprocess_kernel<__nv_bfloat16, false>)
+                                                : reinterpret_cast<const void*>(allreduce_ll_inprocess_kernel<__half, false>));
+    int device = 0, sms = 0, per_sm = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kArThreads, 0);
+    if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    int blocks = pl.blocks;
+    const int fit = sms * per_sm / world;
+    if (fit < 1) return fail(NVK_ERR_UNSUPPORTED, "%s: %d ranks do not fit on this device at once", what, world);
+    if (blocks > fit) blocks = fit;   // blocks stride over the segments, any count is valid
+    void* args[] = {&g};
+    e = cudaLaunchCooperativeKernel(fn, dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(world)), dim3(kArThreads), args, 0,
+                                    static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return check_launch("tp all-reduce (in-process) launch");
+}
+
+extern "C" int nvk_tp_allreduce_status(const void* flags, void* stream, int* status) {
+    using namespace nvk;
+    if (!flags || !status) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce status: null argument");
     uint32_t word = 0;
-    cudaError_t e = cudaMemcpyAsync(&word, static_cast<const uint32_t*>(own_flags) + 2, sizeof(word), cudaMemcpyDeviceToHost,
+    cudaError_t e = cudaMemcpyAsync(&word, static_cast<const uint32_t*>(flags) + 2, sizeof(word), cudaMemcpyDeviceToHost,
                                     static_cast<cudaStream_t>(stream));
     if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "tp all-reduce status: %s", cudaGetErrorString(e));
@@ -320,35 +490,11 @@ extern "C" int nvk_tp_allreduce_status(const void* own_flags, void* stream, int*
     return NVK_OK;
 }
 
-extern "C" int nvk_tp_allreduce_add_rmsnorm(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
-                                            void* const* flag_ptrs, const void* residual, const void* weight, float eps,
-                                            int rank, int world, int rows, int cols, int dtype, void* stream) {
+extern "C" int nvk_tp_allreduce_reset(void* flags, void* stream) {
     using namespace nvk;
-    if (!in_ptrs || !out_ptrs || !norm_ptrs || !flag_ptrs || !residual || !weight)
-        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: every pointer must be defined");
-    if (world < 2 || world > NVK_TP_MAX_RANKS || rank < 0 || rank >= world)
-        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: world must be 2..%d and rank inside it", NVK_TP_MAX_RANKS);
-    if (dtype != NVK_F16 && dtype != NVK_BF16) return fail(NVK_ERR_UNSUPPORTED, "tp all-reduce + add + rmsnorm: dtype must be F16 or BF16");
-    if (rows <= 0 || rows % world != 0) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: rows must be a positive multiple of world");
-    if (cols <= 0 || cols % 8 != 0 || cols > kArThreads * kNormMaxVecs * 8)
-        return fail(NVK_ERR_UNSUPPORTED, "tp all-reduce + add + rmsnorm: cols must be a multiple of 8 and at most %d", kArThreads * kNormMaxVecs * 8);
-    if (!aligned_to(residual, 16) || !aligned_to(weight, 16))
-        return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: residual and weight must be 16-byte aligned");
-    ArNormParams q{};
-    for (int r = 0; r < world; ++r) {
-        if (!in_ptrs[r] || !out_ptrs[r] || !norm_ptrs[r] || !flag_ptrs[r])
-            return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: null buffer of rank %d", r);
-        if (!aligned_to(in_ptrs[r], 16) || !aligned_to(out_ptrs[r], 16) || !aligned_to(norm_ptrs[r], 16) || !aligned_to(flag_ptrs[r], 4))
-            return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce + add + rmsnorm: buffers must be 16-byte aligned");
-        q.ar.in[r] = in_ptrs[r]; q.ar.out[r] = out_ptrs[r]; q.norm[r] = norm_ptrs[r]; q.ar.flags[r] = static_cast<uint32_t*>(flag_ptrs[r]);
-    }
-    q.ar.rank = rank; q.ar.world = world; q.ar.count = static_cast<int64_t>(rows) * cols;
-    q.residual = residual; q.weight = weight; q.eps = eps; q.rows = rows; q.cols = cols;
-    int blocks = rows / world;
-    if (blocks > kArBlocks) blocks = kArBlocks;
-    if (dtype == NVK_BF16)
-        allreduce_add_rmsnorm_kernel<__nv_bfloat16><<<blocks, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(q);
-    else
-        allreduce_add_rmsnorm_kernel<__half><<<blocks, kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(q);
-    return check_launch("allreduce_add_rmsnorm_kernel launch");
+    if (!flags) return fail(NVK_ERR_INVALID_ARGUMENT, "tp all-reduce reset: null argument");
+    cudaError_t e = cudaMemsetAsync(flags, 0, kFlagWords * sizeof(uint32_t), static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "tp all-reduce reset: %s", cudaGetErrorString(e));
+    return NVK_OK;
 }
