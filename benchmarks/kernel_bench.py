@@ -223,10 +223,13 @@ def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ct
 
 
 def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
+    """The fused prologue at ``rows`` token rows.  Prefill-sized inputs (larger than L2) are timed launch by launch.  At
+    decode sizes a launch lasts a few microseconds and in a decoder it follows the QKV GEMM that has just left its
+    packed rows in L2, inside a CUDA graph: so there the figure is the time per launch of a replayed graph of 64 launches
+    that rotate over 16 sets of buffers (48 MB of packed rows in total: L2-resident, as after the GEMM)."""
     gen = torch.Generator(device=dev)
     gen.manual_seed(9)
     bf = torch.bfloat16
-    qkv = torch.randn((rows, (HQ + 2 * HKV) * D), generator=gen, device=dev).to(bf)
     qw = torch.ones(D, device=dev, dtype=bf)
     kw = torch.ones(D, device=dev, dtype=bf)
     max_pos = 4096
@@ -235,28 +238,50 @@ def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
     table = torch.from_numpy(np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)).to(dev)
     pos = torch.randint(0, max_pos, (rows,), generator=gen, device=dev, dtype=torch.int32)
     pool = max(64, (rows + BS - 1) // BS)      # every row has its own cache slot
-    kc = torch.zeros((pool, BS, HKV, D), device=dev, dtype=bf)
-    vc = torch.zeros_like(kc)
     slots = torch.from_numpy(np.random.default_rng(9).permutation(pool * BS)[:rows].astype(np.int32)).to(dev)
-    q_out = torch.empty((rows, HQ, D), device=dev, dtype=bf)
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    fn = lambda: nvk.fused_split_norm_rope_store(qkv, pos, qw, kw, 1e-6, table, slots, kc, vc, HQ, HKV, D, q_out)  # noqa: E731
-    # inputs larger than L2 (126 MB) need no flush; below that a 256 MB buffer is written between timed iterations
-    # (its dirty lines are written back during the timed kernel, which costs a short kernel up to 20 us)
-    big = qkv.numel() * 2 > (128 << 20)
-    mean_ms, med_ms = _time(torch, fn, steps, warmup, flush=None if big else (lambda: flush_buf.fill_(1)))
     nbytes = 2 * rows * (HQ + 2 * HKV) * D * 2 + rows * (D * 4 + 8)
+    big = rows * (HQ + 2 * HKV) * D * 2 > (128 << 20)
+    sets = 1 if big else 16
+
+    def make_set():
+        kc = torch.zeros((pool, BS, HKV, D), device=dev, dtype=bf)
+        return (torch.randn((rows, (HQ + 2 * HKV) * D), generator=gen, device=dev).to(bf), kc, torch.zeros_like(kc),
+                torch.empty((rows, HQ, D), device=dev, dtype=bf))
+
+    bufs = [make_set() for _ in range(sets)]
+
+    def launch(i):
+        qkv, kc, vc, q_out = bufs[i % sets]
+        nvk.fused_split_norm_rope_store(qkv, pos, qw, kw, 1e-6, table, slots, kc, vc, HQ, HKV, D, q_out)
+
+    if big:
+        mean_ms, med_ms = _time(torch, lambda: launch(0), steps, warmup)
+        how = "the packed qkv input (%d MB) exceeds L2; CUDA events around every launch" % (rows * (HQ + 2 * HKV) * D * 2 >> 20)
+    else:
+        per_graph = 64
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(sets):
+                launch(i)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(per_graph):
+                launch(i)
+        mean_ms, med_ms = _time(torch, graph.replay, steps, warmup)
+        mean_ms, med_ms = mean_ms / per_graph, med_ms / per_graph
+        how = f"time per launch of a replayed CUDA graph of {per_graph} launches over {sets} buffer sets (L2-resident inputs, as after the QKV GEMM)"
     hbm, _, kind = _peaks()
     ach = nbytes / (mean_ms * 1e-3) / 1e9
     return {"metric": "fused_split_norm_rope_store_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1,
             "steps": steps, "warmup": warmup, "ms_per_step": mean_ms, "median_ms": med_ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"fused split + q/k RMSNorm + RoPE + KV store, {rows} rows of 48 heads x 128",
-                       "l2": ("the packed qkv input (%d MB) exceeds L2" % (qkv.numel() * 2 >> 20)) if big
-                             else "a 256 MB buffer is written between timed iterations"},
+            "config": {"workload": f"fused split + q/k RMSNorm + RoPE + KV store, {rows} rows of 48 heads x 128", "l2": how},
             "roofline": {"bound": "hbm", "kernel": "fused_prologue_kernel", "achieved": ach, "peak": hbm,
                          "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
-            "gpu_launches": steps, "clocks": LAST_CLOCKS}
+            "gpu_launches": steps * (1 if big else 64), "clocks": LAST_CLOCKS}
 
 
 def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_lo=512, ctx_hi=16384, prefill_seqs=4,

@@ -1090,25 +1090,26 @@ EncodeFn encode_fn() {
     return fn;
 }
 
-// [rows, heads, 128] 16-bit tensor -> boxes of 128 rows x 1 head x 64 elements, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, int64_t rows, int heads, bool bf16) {
+// [rows, heads, 128] 16-bit tensor -> boxes of `box_rows` rows x 1 head x 64 elements, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int heads, bool bf16, int box_rows = 128) {
     EncodeFn fn = encode_fn();
     if (fn == nullptr || rows <= 0) return false;
     const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kHeadDim) * 2, static_cast<cuuint64_t>(heads) * kHeadDim * 2};
-    const cuuint32_t box[3] = {64, 1, 128};
+    const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem[3] = {1, 1, 1};
     return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base),
               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// kind::f16 instruction descriptor: D = F32, A / B = F16 or BF16, M 128, N 128.
-uint32_t make_idesc(bool bf16, bool b_mn_major) {
+// kind::f16 instruction descriptor: D = F32, A / B = F16 or BF16, N 128, M 128 (one block) or 256 (a block pair).
+uint32_t make_idesc(bool bf16, bool b_mn_major, int m = kBM) {
     const uint32_t fmt = bf16 ? 1u : 0u;
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
-           (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+           (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
+
 
 template <typename T>
 int launch_typed(const PrefillArgs& a, bool bf16) {
