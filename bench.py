@@ -501,7 +501,8 @@ def main():
     ap.add_argument("--layers", type=int, default=36, help="mixed workload: layer caches per step")
     ap.add_argument("--rows", type=int, default=256, help="prologue workload: token rows")
     ap.add_argument("--mixed-single-launch", action="store_true",
-                    help="mixed workload: the whole step as one varlen paged-prefill launch per layer (decode rows as one-token sequences)")
+                    help="mixed workload: one attention launch per layer for prefill and decode rows together (nvk_attention_mixed_step)")
+    ap.add_argument("--mixed-prefill-blocks", type=int, default=0, help="mixed single launch: blocks that start on the prefill items (0 = from the sizes)")
     ap.add_argument("--seqs", type=int, default=16, help="prefill workload: number of sequences")
     ap.add_argument("--qmax", type=int, default=4096, help="prefill workload: longest new-token run")
     ap.add_argument("--batch", type=int, default=CFG["batch"],
@@ -595,7 +596,7 @@ def main():
             line = kb.bench_decode_int8(nvk, torch, dev, steps, args.warmup, batch=args.batch)
         elif args.workload == "mixed":
             line = kb.bench_mixed(nvk, torch, dev, min(steps, 10), min(args.warmup, 3), layers=args.layers,
-                                  single_launch=args.mixed_single_launch)
+                                  single_launch=args.mixed_single_launch, prefill_blocks_hint=args.mixed_prefill_blocks)
         else:
             line = kb.bench_prologue(nvk, torch, dev, steps, args.warmup, rows=args.rows)
         print(json.dumps(line), flush=True)

@@ -285,7 +285,7 @@ def bench_prologue(nvk, torch, dev, steps, warmup, rows=256):
 
 
 def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_lo=512, ctx_hi=16384, prefill_seqs=4,
-                prefill_len=2048, mem_fraction=0.80, hq=HQ, hkv=HKV, single_launch=False):
+                prefill_len=2048, mem_fraction=0.80, hq=HQ, hkv=HKV, single_launch=False, prefill_blocks_hint=0):
     """Config 4: one continuous-batching step of attention over ``layers`` layer caches -- per layer the store of the
     prefill tokens, the varlen prefill (no prefix), the store of the decode tokens and the paged decode attention,
     all on one stream (the reference never fuses prefill and decode into one launch, src/engine/scheduler.cpp:65-67).
@@ -293,9 +293,9 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
     caches as fit are allocated and the logical layers are mapped onto them round-robin; every physical cache has
     its own block-table permutation and each is far larger than L2, so the reuse brings no cache hits.
 
-    ``single_launch`` runs the same step as ONE store and ONE varlen paged-prefill launch per layer, the decode
-    sequences entering as sequences of one new token whose prefix is their context (the "true mixed step" the
-    reference lists as future work, docs/interview_star.md:54) -- for comparison with the two-kernel step."""
+    ``single_launch`` runs the same step with ONE attention launch per layer (``nvk_attention_mixed_step``: the
+    prefill kernel's persistent blocks also take the decode items; the "true mixed step" the reference lists as
+    future work, docs/interview_star.md:54) plus the merge of the decode splits."""
     from . import workloads as wl
     rng = np.random.default_rng(4040)
     ctx = rng.integers(ctx_lo, ctx_hi + 1, size=decode_seqs).astype(np.int32)
@@ -345,19 +345,19 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
     max_blocks = caches[0]["tables"].shape[1]
     ws = torch.empty(max(16, nvk.decode_attention_workspace_bytes(decode_seqs, hq, hkv, D, max_blocks, BS)), dtype=torch.uint8, device=dev)
 
-    # the same step as one varlen batch: prefill sequences first, then one-token sequences with their context as prefix
-    q_lens = np.concatenate([np.full(prefill_seqs, prefill_len, np.int64), np.ones(decode_seqs, np.int64)])
-    k_lens = np.concatenate([np.full(prefill_seqs, prefill_len, np.int64), ctx.astype(np.int64)])
-    cu_q_all = torch.from_numpy(np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)).to(dev)
-    cu_k_all = torch.from_numpy(np.concatenate([[0], np.cumsum(k_lens)]).astype(np.int32)).to(dev)
-    aq, ak, av = torch.cat([pq, dq]), torch.cat([pk, dk]), torch.cat([pv, dv])
-    aout = torch.empty_like(aq)
+    ak, av = torch.cat([pk, dk]), torch.cat([pv, dv])   # single launch: one store for the new K / V of both kinds of rows
+    flops_est = prefill_seqs * 4 * hq * D * (prefill_len * (prefill_len + 1) // 2)
+    bytes_est = int(ctx.astype(np.int64).sum()) * 2 * hkv * D * 2
+    t_p, t_d = flops_est / 0.55e15, bytes_est / 6.8e12   # what each half sustains on its share of the SMs
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    prefill_blocks = prefill_blocks_hint or max(1, int(round(sms * t_p / (t_p + t_d))))
 
     def step_single():
         for layer in range(layers):
             c = caches[layer % phys]
             nvk.store_kvcache(ak, av, c["k"], c["v"], c["all_slots"])
-            nvk.launch_prefill_attention_paged(aq, cu_q_all, c["k"], c["v"], cu_k_all, c["all_tables"], hkv, D, BS, scale, aout)
+            nvk.attention_mixed_step(pq, cu, pk, pv, cu, None, pout, dq, ctx_dev, c["tables"], dout, c["k"], c["v"], hkv, D, BS,
+                                     scale, ws, prefill_blocks)
 
     def step():
         for layer in range(layers):
@@ -382,16 +382,17 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
             "config": {"workload": f"mixed continuous-batching step, Qwen3-8B attention shape: {prefill_seqs} prefill sequences x "
                                    f"{prefill_len} new tokens + {decode_seqs} decode sequences with context U[{ctx_lo},{ctx_hi}], "
                                    f"{layers} layers per step",
-                       "launches": ("one store + one varlen paged-prefill launch per layer (decode sequences as one-token sequences)"
+                       "launches": (f"per layer: one store + one mixed prefill / decode launch ({prefill_blocks} of {sms} blocks start on the "
+                                    "prefill items) + the merge of the decode splits"
                                     if single_launch else "per layer: store + dense prefill + store + paged decode (split-K + merge)"),
                        "physical_layer_caches": phys, "bytes_per_layer_cache": bytes_per_layer,
                        "note": "logical layers are mapped round-robin onto the physical caches that fit in HBM",
                        "bytes_per_layer": bytes_layer, "prefill_flops_per_layer": flops_layer,
                        "l2": "each layer cache (GiB) exceeds the 126 MB L2"},
-            "roofline": {"bound": "hbm", "kernel": ("prefill kernel" if single_launch else "decode_split_kernel (dominant; the prefill kernel second)"), "achieved": ach,
+            "roofline": {"bound": "hbm", "kernel": ("prefill_tc5_kernel<T, true> (both halves)" if single_launch else "decode_split_kernel (dominant; the prefill kernel second)"), "achieved": ach,
                          "peak": hbm, "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm,
                          "ideal_ms_per_step": ideal_ms, "frac_of_ideal_time": ideal_ms / mean_ms, "traffic": None},
-            "gpu_launches": steps * layers * (2 if single_launch else 5), "clocks": LAST_CLOCKS}
+            "gpu_launches": steps * layers * (3 if single_launch else 5), "clocks": LAST_CLOCKS}
 
 
 def other_kernels(nvk, torch, dev, steps=20, warmup=3):

@@ -259,6 +259,35 @@ int nvk_prefill_attention_varlen(const void* query, const void* key, const void*
                                  int block_size, float scale, void* output, int dtype,
                                  void* stream);
 
+/*
+ * One continuous-batching step that holds BOTH prefill sequences and decode sequences, as one launch (plus the small
+ * merge of the decode splits).  The reference never mixes the two in a step (src/engine/scheduler.cpp:65-67, :103-106)
+ * and names the mixed step as its next one (docs/interview_star.md:54); with two launches the tensor-bound prefill
+ * part and the HBM-bound decode part run one after the other and every SM idles at the boundary.  Here the persistent
+ * blocks of the prefill kernel also take the decode kernel's (KV head, split, sequence) items from a second queue:
+ * `prefill_blocks` of them start with the prefill items, the rest with the decode items, every block finishes with
+ * what is left of the other kind.  Results are those of nvk_prefill_attention_varlen on the prefill rows and of
+ * nvk_decode_attention_paged (same split policy, so the same bits) on the decode rows.
+ *   prefill part   p_query / p_output [total_q, Hq, D]; keys dense (p_key, p_value [total_k, Hkv, D], p_block_tables
+ *                  NULL) or paged through p_block_tables [num_seqs, p_max_blocks]; cu_seqlens_* as in
+ *                  nvk_prefill_attention_varlen
+ *   decode part    d_query / d_output [batch, Hq, D], context_lens [batch], d_block_tables [batch, d_max_blocks]
+ *   both read      k_cache, v_cache [num_cache_blocks, block_size, Hkv, D] (new K / V already stored)
+ * workspace: nvk_decode_attention_workspace_bytes(batch, ...) bytes, required.  prefill_blocks: how many of the
+ * device's SMs start on the prefill part (the caller's scheduler knows both parts' sizes; about
+ * SMs * t_prefill / (t_prefill + t_decode)); 0 = the library's estimate from the sizes it is given.
+ * Supported where both single-purpose tensor-core paths are: F16 / BF16, head_dim 128, 2, 4, 6 or 8 query heads per KV
+ * head, paged block sizes that are multiples of 128; NVK_ERR_UNSUPPORTED otherwise (then make the two calls).
+ */
+int nvk_attention_mixed_step(const void* p_query, const void* p_key, const void* p_value, const void* k_cache, const void* v_cache,
+                             const void* cu_seqlens_q, int cu_seqlens_q_dtype, const void* cu_seqlens_k, int cu_seqlens_k_dtype,
+                             const void* p_block_tables, int p_block_tables_dtype, int64_t num_seqs, int64_t total_q,
+                             int64_t total_k, int64_t p_max_blocks, int max_seqlen_q, void* p_output, const void* d_query,
+                             const void* context_lens, int context_lens_dtype, const void* d_block_tables,
+                             int d_block_tables_dtype, int64_t batch, int64_t d_max_blocks, void* d_output,
+                             int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
+                             int dtype, void* workspace, size_t workspace_bytes, int prefill_blocks, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

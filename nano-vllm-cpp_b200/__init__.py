@@ -29,7 +29,7 @@ EXPORTED_SYMBOLS = (
     "nvk_store_kvcache_int8", "nvk_decode_attention_paged_int8",
     "nvk_tp_allreduce_flag_bytes", "nvk_tp_allreduce_stage_bytes", "nvk_tp_allreduce_set_wait_limit_ms", "nvk_tp_allreduce",
     "nvk_tp_allreduce_status", "nvk_tp_allreduce_reset", "nvk_tp_allreduce_add_rmsnorm", "nvk_tp_allreduce_inprocess",
-    "nvk_prefill_status", "nvk_decode_attention_static_scratch_bytes",
+    "nvk_prefill_status", "nvk_decode_attention_static_scratch_bytes", "nvk_attention_mixed_step",
 )
 
 _lib = None
@@ -290,3 +290,27 @@ def prefill_status() -> int:
 
 def decode_attention_static_scratch_bytes() -> int:
     return int(lib().nvk_decode_attention_static_scratch_bytes())
+
+
+def attention_mixed_step(p_query, cu_seqlens_q, p_key, p_value, cu_seqlens_k, p_block_tables, p_output, d_query, context_lens,
+                         d_block_tables, d_output, k_cache, v_cache, num_kv_heads, head_dim, block_size, scale, workspace,
+                         prefill_blocks=0) -> None:
+    """One launch for a step with prefill rows and decode rows (``nvk_attention_mixed_step``).  Dense prefill keys:
+    ``p_key`` / ``p_value`` given and ``p_block_tables`` None; paged: the other way round."""
+    global launch_count
+    for n, t in (("p_query", p_query), ("p_output", p_output), ("d_query", d_query), ("d_output", d_output), ("k_cache", k_cache),
+                 ("v_cache", v_cache), ("context_lens", context_lens), ("d_block_tables", d_block_tables), ("workspace", workspace)):
+        _require_cuda(n, t)
+    num_seqs = (cu_seqlens_q.numel() - 1) if cu_seqlens_q is not None else 1
+    ncb = k_cache.numel() // (block_size * num_kv_heads * head_dim)
+    _check(lib().nvk_attention_mixed_step(
+        _ptr(p_query), _ptr(p_key), _ptr(p_value), _ptr(k_cache), _ptr(v_cache), *_index("cu_seqlens_q", cu_seqlens_q),
+        *_index("cu_seqlens_k", cu_seqlens_k), *_index("p_block_tables", p_block_tables), ctypes.c_int64(num_seqs),
+        ctypes.c_int64(p_query.shape[0]), ctypes.c_int64(p_key.shape[0] if p_key is not None else 0),
+        ctypes.c_int64(p_block_tables.shape[1] if p_block_tables is not None else 0), ctypes.c_int(0), _ptr(p_output), _ptr(d_query),
+        *_index("context_lens", context_lens), *_index("d_block_tables", d_block_tables), ctypes.c_int64(d_query.shape[0]),
+        ctypes.c_int64(d_block_tables.shape[1]), _ptr(d_output), ctypes.c_int64(ncb), ctypes.c_int(p_query.shape[1]),
+        ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim), ctypes.c_int(block_size), ctypes.c_float(scale),
+        ctypes.c_int(_dtype_code(p_query)), _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
+        ctypes.c_int(prefill_blocks), _stream()))
+    launch_count += 2

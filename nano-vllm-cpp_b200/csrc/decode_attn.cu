@@ -20,234 +20,53 @@
 //     O^T = V^T P^T with V^T taken straight from the row-major V tile by ldmatrix.trans, so the
 //     probability fragment of S is already in the layout the second MMA wants (no shuffles, no
 //     shared-memory round trip); online softmax in the exp2 domain with warp shuffles.
-#include "nvk_internal.cuh"
+#include "decode_body.cuh"
 
 #include <atomic>
 #include <cmath>
+#include <utility>
 
 #include <cuda_fp16.h>
 
 namespace nvk {
 namespace {
 
-constexpr int kHeadDim = 128;
-constexpr int kWarps = 4;
-constexpr int kThreads = kWarps * 32;
-constexpr int kTileTokens = 16;                       // tokens per warp tile
-constexpr int kRowBytes = kHeadDim * 2;               // one head row of K or V
-constexpr int kTileBytes = kTileTokens * kRowBytes;   // 4 KiB (K) ; V follows
-constexpr int kStageBytes = 2 * kTileBytes;           // K + V
-constexpr int kStages = 3;
-constexpr int kMaxGroup = 8;                          // query heads per KV head
-constexpr int kMaxChunkBlocks = 128;                  // block-table entries cached per block
-constexpr int kSmemBytes = kWarps * kStages * kStageBytes;  // 96 KiB -> two blocks per SM
+using namespace dec;   // constants, DecodeParams and decode_split_body: decode_body.cuh
 
-struct DecodeParams {
-    const void* q; const void* k_cache; const void* v_cache;
-    IndexArray context_lens; IndexArray block_tables;
-    void* out; float* ws_o; float* ws_lse;
-    int64_t max_blocks, num_cache_blocks;
-    int num_heads, num_kv_heads, group, block_size, chunk_tokens, num_splits;
-    float scale_log2;
-};
+// The decode kernels are launched with the programmatic-stream-serialization attribute: a kernel's blocks may be
+// scheduled while its predecessor in the stream still runs, wait here until that predecessor has completed and its
+// writes are visible (the first thing every block does, so nothing is read early), and at once allow their own
+// successor the same head start.  In a decode graph of several hundred short kernels this hides launch latency.
+__device__ __forceinline__ void pdl_wait_then_release() {
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
 
-// context_lens[b], limited to what the block table can address (max_blocks * block_size): a longer value would make
-// the split kernels read block_tables past the row and the merge kernel read partial results of the next row.
-__device__ __forceinline__ int clamped_context(const DecodeParams& p, int64_t b) {
-    const int64_t ctx = p.context_lens[b];
-    const int64_t cap = p.max_blocks * p.block_size;
-    return static_cast<int>(ctx < cap ? ctx : cap);
+// <<<grid, block, smem, stream>>> with that attribute.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_blocks[kMaxChunkBlocks];
-
-    const int kvh = blockIdx.x;
-    const int split = blockIdx.y;
-    const int64_t b = blockIdx.z;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int G = p.group;
-
-    const int ctx = clamped_context(p, b);
-    const int t0 = split * p.chunk_tokens;
-    T* out = static_cast<T*>(p.out);
-    if (ctx <= 0) {
-        if (split == 0) {  // empty context: zero rows for the whole group
-            for (int i = tid; i < G * kHeadDim; i += kThreads)
-                out[(b * p.num_heads + kvh * G) * kHeadDim + i] = ElemTraits<T>::from_float(0.0f);
-        }
-        return;
-    }
-    if (t0 >= ctx) return;
-    const int t1 = min(ctx, t0 + p.chunk_tokens);
-    const int live_splits = (ctx + p.chunk_tokens - 1) / p.chunk_tokens;
-
-    // Physical block ids of this chunk (-1 = outside the cache: reads as zeros).
-    const int blk0 = t0 / p.block_size;
-    const int nblk = (t1 - 1) / p.block_size - blk0 + 1;
-    for (int i = tid; i < nblk; i += kThreads) {
-        const int64_t id = p.block_tables[b * p.max_blocks + blk0 + i];
-        s_blocks[i] = (id >= 0 && id < p.num_cache_blocks) ? static_cast<int>(id) : -1;
-    }
-    __syncthreads();
-
-    // Query fragments: rows g < G of the 16-row A tile, rows 8..15 are zero.
-    uint32_t qa[8][2];
-    {
-        const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
-            static_cast<const T*>(p.q) + (b * p.num_heads + kvh * G + (g < G ? g : 0)) * kHeadDim);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            qa[ks][0] = g < G ? qrow[ks * 8 + t] : 0u;
-            qa[ks][1] = g < G ? qrow[ks * 8 + 4 + t] : 0u;
-        }
-    }
-
-    unsigned char* ring = smem + warp * (kStages * kStageBytes);
-    const uint32_t ring_u32 = smem_u32(ring);
-    const int num_tiles = (t1 - t0 + kTileTokens - 1) / kTileTokens;
-    const int my_tiles = num_tiles > warp ? (num_tiles - warp + kWarps - 1) / kWarps : 0;
-    const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kRowBytes;  // bytes between tokens
-    const unsigned char* kc = static_cast<const unsigned char*>(p.k_cache) + static_cast<size_t>(kvh) * kRowBytes;
-    const unsigned char* vc = static_cast<const unsigned char*>(p.v_cache) + static_cast<size_t>(kvh) * kRowBytes;
-
-    // Lane's piece of a tile: 16-byte column c of rows r = 2 * i + (lane >> 4), i = 0..7.
-    const int c = lane & 15, rhalf = lane >> 4;
-
-    auto issue = [&](int j) {  // load this warp's j-th tile into stage j % kStages
-        if (j < my_tiles) {
-            const int tok0 = t0 + (warp + j * kWarps) * kTileTokens;
-            const int blk = tok0 / p.block_size;
-            const int phys = s_blocks[blk - blk0];
-            const int off = tok0 - blk * p.block_size;
-            const size_t base = (static_cast<size_t>(phys < 0 ? 0 : phys) * p.block_size + off) * row_stride + c * 16;
-            const uint32_t stage = ring_u32 + (j % kStages) * kStageBytes;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int r = 2 * i + rhalf;
-                const int bytes = (phys >= 0 && tok0 + r < t1) ? 16 : 0;
-                const size_t src = base + (bytes ? r * row_stride : 0);
-                const uint32_t dst = stage + r * kRowBytes + ((c ^ (r & 7)) << 4);
-                cp_async16(dst, kc + src, bytes);
-                cp_async16(dst + kTileBytes, vc + src, bytes);
-            }
-        }
-        cp_async_commit();
-    };
-
-    float o[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    float m_run = -INFINITY, l_run = 0.0f;  // per head g (replicated over the 4 lanes of a row)
-
-#pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) issue(s);
-
-    // ldmatrix lane addressing.  K (non-transposed): matrices (tok 0-7, d lo), (tok 0-7, d hi),
-    // (tok 8-15, d lo), (tok 8-15, d hi) of one 16-wide k-step.  V (transposed): matrices
-    // (tok 0-7, d lo), (tok 0-7, d hi), (tok 8-15, d lo), (tok 8-15, d hi) of one 16-wide d-tile.
-    const int k_row = ((lane >> 4) << 3) + (lane & 7);
-    const int k_sel = (lane >> 3) & 1;
-    const int v_row = (((lane >> 3) >> 1) << 3) + (lane & 7);
-    const int v_sel = (lane >> 3) & 1;
-
-    for (int j = 0; j < my_tiles; ++j) {
-        issue(j + kStages - 1);
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
-        const uint32_t stage = ring_u32 + (j % kStages) * kStageBytes;
-        const int tok0 = t0 + (warp + j * kWarps) * kTileTokens;
-
-        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            uint32_t b0, b1, b2, b3;
-            const int chunk = 2 * ks + k_sel;
-            ldmatrix_x4(b0, b1, b2, b3, stage + k_row * kRowBytes + ((chunk ^ (k_row & 7)) << 4));
-            mma_16816<T>(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-            mma_16816<T>(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
-        }
-        // scores of head g: tokens tok0 + {2t, 2t+1, 8+2t, 9+2t}
-        float sc[4];
-        sc[0] = s0[0] * p.scale_log2; sc[1] = s0[1] * p.scale_log2;
-        sc[2] = s1[0] * p.scale_log2; sc[3] = s1[1] * p.scale_log2;
-        const int tk = tok0 + 2 * t;
-        if (tk >= t1) sc[0] = -INFINITY;
-        if (tk + 1 >= t1) sc[1] = -INFINITY;
-        if (tk + 8 >= t1) sc[2] = -INFINITY;
-        if (tk + 9 >= t1) sc[3] = -INFINITY;
-        float m_tile = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-        m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
-        m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
-        const float m_new = fmaxf(m_run, m_tile);   // finite: token tok0 is always valid
-        const float corr = fast_exp2(m_run - m_new);
-        const float p0 = fast_exp2(sc[0] - m_new), p1 = fast_exp2(sc[1] - m_new);
-        const float p2 = fast_exp2(sc[2] - m_new), p3 = fast_exp2(sc[3] - m_new);
-        l_run = l_run * corr + ((p0 + p1) + (p2 + p3));
-        m_run = m_new;
-        const uint32_t pb0 = ElemTraits<T>::pack2(p0, p1);
-        const uint32_t pb1 = ElemTraits<T>::pack2(p2, p3);
-        // accumulator columns of this lane are heads 2t and 2t+1
-        const float c0 = __shfl_sync(0xffffffffu, corr, 8 * t);
-        const float c1 = __shfl_sync(0xffffffffu, corr, 8 * t + 4);
-#pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            uint32_t a0, a1, a2, a3;
-            const int chunk = 2 * mt + v_sel;
-            ldmatrix_x4_trans(a0, a1, a2, a3, stage + kTileBytes + v_row * kRowBytes + ((chunk ^ (v_row & 7)) << 4));
-            o[mt][0] *= c0; o[mt][1] *= c1; o[mt][2] *= c0; o[mt][3] *= c1;
-            mma_16816<T>(o[mt], a0, a1, a2, a3, pb0, pb1);
-        }
-        __syncwarp();
-    }
-    cp_async_wait<0>();
-    __syncthreads();  // every ring is idle from here on: reuse it for the cross-warp merge
-
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-
-    float* sm_o = reinterpret_cast<float*>(smem);                    // [warp][head][128]
-    float* sm_m = sm_o + kWarps * kMaxGroup * kHeadDim;              // [warp][head]
-    float* sm_l = sm_m + kWarps * kMaxGroup;
-    if (t == 0) { sm_m[warp * kMaxGroup + g] = m_run; sm_l[warp * kMaxGroup + g] = l_run; }
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt) {
-        const int d = mt * 16 + g;
-        float* dst = sm_o + (warp * kMaxGroup + 2 * t) * kHeadDim + d;
-        dst[0] = o[mt][0]; dst[kHeadDim] = o[mt][1]; dst[8] = o[mt][2]; dst[kHeadDim + 8] = o[mt][3];
-    }
-    __syncthreads();
-
-    // thread d merges column d of every head of the group over the four warps
-    const int d = tid;
-    for (int h = 0; h < G; ++h) {
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, sm_m[w * kMaxGroup + h]);
-        float acc = 0.0f, lsum = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const float f = fast_exp2(sm_m[w * kMaxGroup + h] - mx);
-            acc += f * sm_o[(w * kMaxGroup + h) * kHeadDim + d];
-            lsum += f * sm_l[w * kMaxGroup + h];
-        }
-        const float val = acc / lsum;
-        const int64_t head = b * p.num_heads + kvh * G + h;
-        if (live_splits == 1) {
-            out[head * kHeadDim + d] = ElemTraits<T>::from_float(val);
-        } else {
-            p.ws_o[(head * p.num_splits + split) * kHeadDim + d] = val;
-            if (d == 0) p.ws_lse[head * p.num_splits + split] = mx + log2f(lsum);
-        }
-    }
+    pdl_wait_then_release();
+    decode_split_body<T>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, s_blocks, threadIdx.x, 1);
 }
 
 // One warp per (sequence, query head): merges the live splits' (O, lse) pairs.
 template <typename T>
 __global__ void __launch_bounds__(128) decode_merge_kernel(const DecodeParams p, int64_t num_rows) {
+    pdl_wait_then_release();
     const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
     if (row >= num_rows) return;
     const int lane = threadIdx.x & 31;
@@ -324,6 +143,7 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
     const DecodeParams& p = pp.base;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_blocks[kMaxChunkBlocks];
+    pdl_wait_then_release();
 
     const int kvh = blockIdx.x;
     const int split = blockIdx.y;
@@ -577,16 +397,10 @@ int choose_chunk_tokens(int64_t batch, int num_kv_heads, int64_t max_blocks, int
     return static_cast<int>(chunk);
 }
 
-template <typename T>
-int launch_typed(const DecodeArgs& a) {
-    static bool attr_done[64] = {};  // per device; the attribute call is idempotent
-    int device = 0;
-    cudaGetDevice(&device);
-    if (device >= 0 && device < 64 && !attr_done[device]) {
-        const cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "decode attention: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr_done[device] = true;
-    }
+}  // namespace
+
+// Kernel parameters of a split-K decode call from host-known sizes only: chunk length, split count, scratch layout.
+int decode_plan(const DecodeArgs& a, dec::DecodeParams* out) {
     DecodeParams p{};
     p.q = a.q; p.k_cache = a.k_cache; p.v_cache = a.v_cache;
     p.context_lens = a.context_lens; p.block_tables = a.block_tables; p.out = a.out;
@@ -611,13 +425,45 @@ int launch_typed(const DecodeArgs& a) {
         p.ws_o = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + lse_bytes);
     }
     if (a.batch > 65535 || p.num_splits > 65535) return fail(NVK_ERR_UNSUPPORTED, "decode attention: batch or split count exceeds grid limits");
+    *out = p;
+    return NVK_OK;
+}
+
+// The merge of the live splits' partial results (nothing to do when the plan has a single split).
+int launch_decode_merge(const dec::DecodeParams& p, int64_t batch, int dtype, cudaStream_t stream) {
+    if (p.num_splits <= 1) return NVK_OK;
+    const int64_t rows = batch * p.num_heads;
+    const cudaError_t le = dtype == NVK_BF16
+        ? launch_pdl(decode_merge_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0, stream, p, rows)
+        : launch_pdl(decode_merge_kernel<__half>, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0, stream, p, rows);
+    if (le != cudaSuccess) return fail(NVK_ERR_CUDA, "decode_merge_kernel launch: %s", cudaGetErrorString(le));
+    return check_launch("decode_merge_kernel launch");
+}
+
+namespace {
+
+template <typename T>
+int launch_typed(const DecodeArgs& a) {
+    static bool attr_done[64] = {};  // per device; the attribute call is idempotent
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 0 && device < 64 && !attr_done[device]) {
+        const cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "decode attention: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_done[device] = true;
+    }
+    DecodeParams p{};
+    int rc0 = decode_plan(a, &p);
+    if (rc0 != NVK_OK) return rc0;
     const dim3 grid(a.num_kv_heads, p.num_splits, static_cast<unsigned>(a.batch));
-    decode_split_kernel<T><<<grid, kThreads, kSmemBytes, a.stream>>>(p);
+    cudaError_t le = launch_pdl(decode_split_kernel<T>, grid, dim3(kThreads), kSmemBytes, a.stream, p);
+    if (le != cudaSuccess) return fail(NVK_ERR_CUDA, "decode_split_kernel launch: %s", cudaGetErrorString(le));
     int rc = check_launch("decode_split_kernel launch");
     if (rc != NVK_OK) return rc;
     if (p.num_splits > 1) {
         const int64_t rows = a.batch * a.num_heads;
-        decode_merge_kernel<T><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, a.stream>>>(p, rows);
+        le = launch_pdl(decode_merge_kernel<T>, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0, a.stream, p, rows);
+        if (le != cudaSuccess) return fail(NVK_ERR_CUDA, "decode_merge_kernel launch: %s", cudaGetErrorString(le));
         rc = check_launch("decode_merge_kernel launch");
     }
     return rc;
@@ -659,12 +505,14 @@ int launch_int8_typed(const DecodeInt8Args& x) {
     }
     if (a.batch > 65535 || p.num_splits > 65535) return fail(NVK_ERR_UNSUPPORTED, "decode attention (int8): batch or split count exceeds grid limits");
     const dim3 grid(a.num_kv_heads, p.num_splits, static_cast<unsigned>(a.batch));
-    decode_split_int8_kernel<T><<<grid, kThreads, kSmemBytesI8, a.stream>>>(pp);
+    cudaError_t le = launch_pdl(decode_split_int8_kernel<T>, grid, dim3(kThreads), kSmemBytesI8, a.stream, pp);
+    if (le != cudaSuccess) return fail(NVK_ERR_CUDA, "decode_split_int8_kernel launch: %s", cudaGetErrorString(le));
     int rc = check_launch("decode_split_int8_kernel launch");
     if (rc != NVK_OK) return rc;
     if (p.num_splits > 1) {
         const int64_t rows = a.batch * a.num_heads;
-        decode_merge_kernel<T><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, a.stream>>>(p, rows);
+        le = launch_pdl(decode_merge_kernel<T>, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0, a.stream, p, rows);
+        if (le != cudaSuccess) return fail(NVK_ERR_CUDA, "decode_merge_kernel launch: %s", cudaGetErrorString(le));
         rc = check_launch("decode_merge_kernel launch");
     }
     return rc;

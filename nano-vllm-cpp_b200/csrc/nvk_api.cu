@@ -212,4 +212,44 @@ int nvk_prefill_attention_varlen(const void* query, const void* key, const void*
     return launch_rowwise_prefill(a);
 }
 
+int nvk_attention_mixed_step(const void* p_query, const void* p_key, const void* p_value, const void* k_cache, const void* v_cache,
+                             const void* cu_seqlens_q, int cu_seqlens_q_dtype, const void* cu_seqlens_k, int cu_seqlens_k_dtype,
+                             const void* p_block_tables, int p_block_tables_dtype, int64_t num_seqs, int64_t total_q,
+                             int64_t total_k, int64_t p_max_blocks, int max_seqlen_q, void* p_output, const void* d_query,
+                             const void* context_lens, int context_lens_dtype, const void* d_block_tables,
+                             int d_block_tables_dtype, int64_t batch, int64_t d_max_blocks, void* d_output,
+                             int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
+                             int dtype, void* workspace, size_t workspace_bytes, int prefill_blocks, void* stream) {
+    if (!p_query || !p_output || !d_query || !d_output || !k_cache || !v_cache || !context_lens || !d_block_tables)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "mixed step: queries, outputs, the KV cache, context_lens and the decode block tables must be defined");
+    if (!is_index_dtype(context_lens_dtype) || !is_index_dtype(d_block_tables_dtype) || (cu_seqlens_q && !is_index_dtype(cu_seqlens_q_dtype)) ||
+        (cu_seqlens_k && !is_index_dtype(cu_seqlens_k_dtype)) || (p_block_tables && !is_index_dtype(p_block_tables_dtype)))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "mixed step: index tensors must be int32 or int64");
+    if (num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || block_size <= 0 || num_cache_blocks <= 0 || total_q <= 0 || batch <= 0 ||
+        d_max_blocks <= 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "mixed step: sizes must be positive (a step without prefill rows or without decode rows takes the single-purpose entry point)");
+    if (num_heads % num_kv_heads != 0) return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
+    const bool paged = p_block_tables != nullptr;
+    if (paged && (!cu_seqlens_q || !cu_seqlens_k || p_max_blocks <= 0))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "paged prefill attention requires cu_seqlens_q and cu_seqlens_k");
+    if (!paged && (!p_key || !p_value)) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill attention: key and value must be defined");
+    if ((cu_seqlens_q == nullptr) != (cu_seqlens_k == nullptr)) { cu_seqlens_q = nullptr; cu_seqlens_k = nullptr; }
+    if (cu_seqlens_q && num_seqs <= 0) return fail(NVK_ERR_INVALID_ARGUMENT, "prefill attention: num_seqs must be positive");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    PrefillArgs pa{p_query, p_key, p_value, k_cache, v_cache, index_array(cu_seqlens_q, cu_seqlens_q_dtype),
+                   index_array(cu_seqlens_k, cu_seqlens_k_dtype), index_array(p_block_tables, p_block_tables_dtype), p_output, num_seqs,
+                   total_q, total_k, p_max_blocks, num_cache_blocks, max_seqlen_q, num_heads, num_kv_heads, head_dim, block_size, scale,
+                   dtype, st};
+    DecodeArgs da{d_query, k_cache, v_cache, index_array(context_lens, context_lens_dtype), index_array(d_block_tables, d_block_tables_dtype),
+                  d_output, batch, d_max_blocks, num_cache_blocks, num_heads, num_kv_heads, head_dim, block_size, scale, dtype, workspace,
+                  workspace_bytes, st};
+    const size_t need = decode_mma_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, d_max_blocks, block_size);
+    if (workspace == nullptr || workspace_bytes < need || !aligned_to(workspace, 16))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "mixed step: a 16-byte aligned workspace of %zu bytes is needed (nvk_decode_attention_workspace_bytes)", need);
+    if (!mixed_step_supported(pa, da))
+        return fail(NVK_ERR_UNSUPPORTED, "mixed step: needs F16 / BF16, head_dim 128, an even number of query heads per KV head, at most 8, and "
+                                         "paged block sizes that are multiples of 128; call the prefill and decode entry points instead");
+    return launch_mixed_step(pa, da, prefill_blocks);
+}
+
 }  // extern "C"

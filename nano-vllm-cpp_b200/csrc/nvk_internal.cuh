@@ -98,6 +98,12 @@ bool decode_mma_supported(const DecodeArgs& a);
 size_t decode_mma_workspace_bytes(int64_t batch, int num_heads, int num_kv_heads, int head_dim,
                                   int64_t max_blocks, int block_size);
 int launch_decode_mma(const DecodeArgs& a);
+namespace dec { struct DecodeParams; }
+int decode_plan(const DecodeArgs& a, dec::DecodeParams* out);
+int launch_decode_merge(const dec::DecodeParams& p, int64_t batch, int dtype, cudaStream_t stream);
+// One launch for a step that holds prefill sequences and decode sequences (prefill_attn_tc.cu), then the split merge.
+bool mixed_step_supported(const PrefillArgs& p, const DecodeArgs& d);
+int launch_mixed_step(const PrefillArgs& p, const DecodeArgs& d, int prefill_blocks);
 // int8 KV cache (kv_int8.cu; tensor-core decode in decode_attn.cu)
 int launch_store_int8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
                       const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,

@@ -27,7 +27,7 @@
 //     softmax overlaps the other's MMAs.  Every mbarrier wait is bounded; on a time-out the block
 //     raises an error word, stops waiting, frees its TMEM and returns.
 //   * No cluster launch and no multicast anywhere.
-#include "nvk_internal.cuh"
+#include "decode_body.cuh"
 
 #include <cuda.h>
 
@@ -741,19 +741,57 @@ __device__ __forceinline__ bool tc5_locate(const TcParams& p, int64_t want, int&
     return false;
 }
 
-template <typename T>
+// The decode half of a mixed step (prefill_tc5_kernel<T, true>): the split-K decode items of decode_split_kernel, taken
+// from a second ticket counter by the same persistent blocks.  A block runs the two halves one after the other --
+// blocks [0, prefill_blocks) the prefill items first, the others the decode items first -- so while some SMs are busy
+// on the tensor pipe the rest stream the KV cache, and no SM idles between the two parts of the step as it does at the
+// boundary of two launches.  In the decode half the eight softmax warps form two groups of four warps, each with its
+// own 96 KiB of the block's shared memory, i.e. what two resident blocks of decode_split_kernel have per SM.
+struct MixedDecode {
+    dec::DecodeParams dp;
+    unsigned int items;       // KV heads x splits x sequences
+    int prefill_blocks;
+};
+__device__ unsigned int g_decode_ticket[kTicketSlots];
+
+template <typename T, bool MIXED>
 __global__ void __launch_bounds__(kThreads5, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const Tc5Params pp) {
+                   const __grid_constant__ CUtensorMap tm_v, const Tc5Params pp, const MixedDecode md) {
     const TcParams& p = pp.base;
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ Tc5Item s_ring[4];
+    __shared__ int s_dec_blocks[MIXED ? 2 : 1][MIXED ? dec::kMaxChunkBlocks : 1];
+    __shared__ unsigned int s_dec_item[2];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // decode half: warps 0-3 and 4-7 are two independent groups, each taking (KV head, split, sequence) items
+    auto decode_half = [&]() {
+        if (MIXED && warp < 8) {
+            const int group = warp >> 2, gtid = tid & 127, bar = 1 + group;
+            unsigned char* gsmem = smem_gen + group * dec::kSmemBytes;
+            const unsigned int hkv = static_cast<unsigned int>(md.dp.num_kv_heads), splits = static_cast<unsigned int>(md.dp.num_splits);
+            while (true) {
+                if (gtid == 0) s_dec_item[group] = atomicAdd(&g_decode_ticket[pp.slot], 1u);
+                dec::group_sync(bar);
+                const unsigned int item = s_dec_item[group];
+                dec::group_sync(bar);   // everyone holds the item before the next ticket overwrites it
+                if (item >= md.items) break;
+                dec::decode_split_body<T>(md.dp, static_cast<int>(item % hkv), static_cast<int>((item / hkv) % splits),
+                                          static_cast<int64_t>(item / (hkv * splits)), gsmem, s_dec_blocks[MIXED ? group : 0], gtid, bar);
+                dec::group_sync(bar);   // the group's shared memory is free for its next item
+            }
+        }
+    };
+    const bool decode_first = MIXED && static_cast<int>(blockIdx.x) >= md.prefill_blocks;
+    if (decode_first) {
+        decode_half();
+        __syncthreads();
+    }
     const uint32_t sm_q = smem_base + kOff4Q, sm_k = smem_base + kOff4K, sm_v = smem_base + kOff4V, sm_p = smem_base + kOff4P;
     const uint32_t bars = smem_base + kOff4Bar;
     const uint32_t bar_qfull = bars, bar_vfix = bars + 8, bar_vfull = bars + 16, bar_vempty = bars + 24, bar_qempty = bars + 144;
@@ -1062,10 +1100,13 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (warp == 8) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols2) : "memory");
     }
-    if (tid == 0) {   // the last block to finish re-arms the ticket counter for the next launch that uses this slot
+    if (MIXED && !decode_first) decode_half();
+    if (MIXED) __syncthreads();
+    if (tid == 0) {   // the last block to finish re-arms the ticket counters for the next launch that uses this slot
         __threadfence();
         if (atomicAdd(&g_prefill_done[pp.slot], 1u) == gridDim.x - 1) {
             g_prefill_ticket[pp.slot] = 0u;
+            g_decode_ticket[pp.slot] = 0u;
             g_prefill_done[pp.slot] = 0u;
             __threadfence();
         }
@@ -1111,6 +1152,55 @@ uint32_t make_idesc(bool bf16, bool b_mn_major, int m = kBM) {
 }
 
 
+// Launches that may run at the same time on one device need different ticket counters; 64 of them rotate.
+std::atomic<unsigned int> g_launch_seq{0};
+
+// Tensor maps and kernel parameters of a prefill call.
+struct TcLaunch {
+    CUtensorMap tq, tk, tv;
+    TcParams p;
+    int64_t tiles;
+};
+int prepare_tc_launch(const PrefillArgs& a, bool bf16, TcLaunch* out) {
+    const bool paged = a.block_tables != nullptr;
+    const int64_t key_rows = paged ? a.num_cache_blocks * a.block_size : a.total_k;
+    if (!make_map(&out->tq, a.q, a.total_q, a.num_heads, bf16) ||
+        !make_map(&out->tk, paged ? a.k_cache : a.k, key_rows, a.num_kv_heads, bf16) ||
+        !make_map(&out->tv, paged ? a.v_cache : a.v, key_rows, a.num_kv_heads, bf16))
+        return fail(NVK_ERR_CUDA, "prefill attention (tcgen05): cuTensorMapEncodeTiled failed");
+    TcParams p{};
+    p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.block_tables = a.block_tables; p.out = a.out;
+    p.num_seqs = a.cu_q ? a.num_seqs : 1; p.total_q = a.total_q; p.total_k = a.total_k; p.max_blocks = a.max_blocks;
+    p.key_rows = key_rows; p.num_cache_blocks = a.num_cache_blocks;
+    p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.block_size = paged ? a.block_size : 1;
+    p.scale_log2 = a.scale * kLog2e;
+    p.idesc_s = make_idesc(bf16, false);
+    p.idesc_pv = make_idesc(bf16, true);
+    out->p = p;
+    out->tiles = (a.total_q + kBM - 1) / kBM + (a.cu_q ? a.num_seqs : 0);
+    if (out->tiles > 65535) return fail(NVK_ERR_UNSUPPORTED, "prefill attention (tcgen05): too many query tiles");
+    return NVK_OK;
+}
+
+// Shared-memory attribute and SM count of the persistent head-pair kernel, once per device.
+template <typename T, bool MIXED>
+int prepare_tc5(int* sms_out) {
+    static bool done[64] = {};
+    static int sm_count[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64) return fail(NVK_ERR_UNSUPPORTED, "prefill attention: device index %d not supported", device);
+    if (!done[device]) {
+        const cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel<T, MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes4);
+        if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill attention (head pairs): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        if (cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count[device] <= 0)
+            return fail(NVK_ERR_CUDA, "prefill attention (head pairs): cannot read the SM count");
+        done[device] = true;
+    }
+    *sms_out = sm_count[device];
+    return NVK_OK;
+}
+
 template <typename T>
 int launch_typed(const PrefillArgs& a, bool bf16) {
     static bool attr_done[64] = {};
@@ -1121,45 +1211,25 @@ int launch_typed(const PrefillArgs& a, bool bf16) {
         if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill attention (tcgen05): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         attr_done[device] = true;
     }
-    const bool paged = a.block_tables != nullptr;
-    const int64_t key_rows = paged ? a.num_cache_blocks * a.block_size : a.total_k;
-    CUtensorMap tq, tk, tv;
-    if (!make_map(&tq, a.q, a.total_q, a.num_heads, bf16) ||
-        !make_map(&tk, paged ? a.k_cache : a.k, key_rows, a.num_kv_heads, bf16) ||
-        !make_map(&tv, paged ? a.v_cache : a.v, key_rows, a.num_kv_heads, bf16))
-        return fail(NVK_ERR_CUDA, "prefill attention (tcgen05): cuTensorMapEncodeTiled failed");
-    TcParams p{};
-    p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.block_tables = a.block_tables; p.out = a.out;
-    p.num_seqs = a.cu_q ? a.num_seqs : 1; p.total_q = a.total_q; p.total_k = a.total_k; p.max_blocks = a.max_blocks;
-    p.key_rows = key_rows; p.num_cache_blocks = a.num_cache_blocks;
-    p.num_heads = a.num_heads; p.num_kv_heads = a.num_kv_heads; p.block_size = paged ? a.block_size : 1;
-    p.scale_log2 = a.scale * kLog2e;
-    p.idesc_s = make_idesc(bf16, false);
-    p.idesc_pv = make_idesc(bf16, true);
-    const int64_t tiles = (a.total_q + kBM - 1) / kBM + (a.cu_q ? a.num_seqs : 0);
-    if (tiles > 65535) return fail(NVK_ERR_UNSUPPORTED, "prefill attention (tcgen05): too many query tiles");
+    TcLaunch L;
+    const int rc = prepare_tc_launch(a, bf16, &L);
+    if (rc != NVK_OK) return rc;
+    const CUtensorMap &tq = L.tq, &tk = L.tk, &tv = L.tv;
+    const TcParams& p = L.p;
+    const int64_t tiles = L.tiles;
     const int group = a.num_heads / a.num_kv_heads;
     if (group % 2 == 0) {   // pairs of query heads that share a KV head: persistent blocks, one per SM, items from a ticket counter
-        static bool attr5_done[64] = {};
-        static int sm_count[64] = {};
-        static std::atomic<unsigned int> launch_seq{0};
-        if (device >= 0 && device < 64 && !attr5_done[device]) {
-            const cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes4);
-            if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "prefill attention (tcgen05 v5): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            if (cudaDeviceGetAttribute(&sm_count[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count[device] <= 0)
-                return fail(NVK_ERR_CUDA, "prefill attention (tcgen05 v5): cannot read the SM count");
-            attr5_done[device] = true;
-        }
+        int sms = 0;
+        const int rc5 = prepare_tc5<T, false>(&sms);
+        if (rc5 != NVK_OK) return rc5;
         Tc5Params pp{};
         pp.base = p;
         pp.pairs = a.num_heads / 2;
         pp.tiles = static_cast<int>(tiles);
         pp.total = static_cast<unsigned int>(pp.pairs) * static_cast<unsigned int>(tiles);
-        // Launches that may run at the same time on one device need different counters; 64 of them rotate.
-        pp.slot = static_cast<int>(launch_seq.fetch_add(1u) % kTicketSlots);
-        const int sms = (device >= 0 && device < 64) ? sm_count[device] : 1;
+        pp.slot = static_cast<int>(g_launch_seq.fetch_add(1u) % kTicketSlots);
         const unsigned int blocks = pp.total < static_cast<unsigned int>(sms) ? pp.total : static_cast<unsigned int>(sms);
-        prefill_tc5_kernel<T><<<blocks, kThreads5, kSmemBytes4, a.stream>>>(tq, tk, tv, pp);
+        prefill_tc5_kernel<T, false><<<blocks, kThreads5, kSmemBytes4, a.stream>>>(tq, tk, tv, pp, MixedDecode{});
         return check_launch("prefill_tc5_kernel launch");
     }
     // odd group sizes: one block per (query tile, head)
@@ -1188,6 +1258,61 @@ bool prefill_tc_supported(const PrefillArgs& a) {
 
 int launch_prefill_tc(const PrefillArgs& a) {
     return a.dtype == NVK_BF16 ? launch_typed<__nv_bfloat16>(a, true) : launch_typed<__half>(a, false);
+}
+
+namespace {
+
+template <typename T>
+int launch_mixed_typed(const PrefillArgs& a, const DecodeArgs& d, int prefill_blocks, bool bf16) {
+    TcLaunch L;
+    int rc = prepare_tc_launch(a, bf16, &L);
+    if (rc != NVK_OK) return rc;
+    int sms = 0;
+    rc = prepare_tc5<T, true>(&sms);
+    if (rc != NVK_OK) return rc;
+    MixedDecode md{};
+    rc = decode_plan(d, &md.dp);
+    if (rc != NVK_OK) return rc;
+    md.items = static_cast<unsigned int>(d.num_kv_heads) * static_cast<unsigned int>(md.dp.num_splits) * static_cast<unsigned int>(d.batch);
+    Tc5Params pp{};
+    pp.base = L.p;
+    pp.pairs = a.num_heads / 2;
+    pp.tiles = static_cast<int>(L.tiles);
+    pp.total = static_cast<unsigned int>(pp.pairs) * static_cast<unsigned int>(L.tiles);
+    pp.slot = static_cast<int>(g_launch_seq.fetch_add(1u) % kTicketSlots);
+    if (prefill_blocks <= 0) {
+        // No hint: split the SMs by a crude estimate from host-known sizes -- prefill flops as if all sequences were equally
+        // long and had no prefix, at 0.55 PFLOP/s (what the prefill half sustains on a share of the SMs at a few thousand tokens per
+        // sequence); decode bytes as if every block table were half full, at 6.5 TB/s.
+        const double mean_q = static_cast<double>(a.total_q) / static_cast<double>(a.cu_q ? a.num_seqs : 1);
+        const double t_prefill = 4.0 * a.num_heads * kHeadDim * static_cast<double>(a.total_q) * (mean_q + 1.0) / 2.0 / 0.55e15;
+        const double t_decode = 0.5 * static_cast<double>(d.batch) * d.max_blocks * d.block_size * d.num_kv_heads * kHeadDim * 4.0 / 6.5e12;
+        prefill_blocks = static_cast<int>(sms * t_prefill / (t_prefill + t_decode) + 0.5);
+    }
+    if (prefill_blocks < 1) prefill_blocks = 1;
+    if (prefill_blocks > sms) prefill_blocks = sms;
+    md.prefill_blocks = prefill_blocks;
+    prefill_tc5_kernel<T, true><<<static_cast<unsigned int>(sms), kThreads5, kSmemBytes4, a.stream>>>(L.tq, L.tk, L.tv, pp, md);
+    rc = check_launch("mixed prefill + decode kernel launch");
+    if (rc != NVK_OK) return rc;
+    return launch_decode_merge(md.dp, d.batch, d.dtype, d.stream);
+}
+
+}  // namespace
+
+// One launch for a step with prefill and decode sequences: the head-pair prefill kernel and the tensor-core decode kernel
+// must both take their halves, and the decode half needs its split-K workspace.
+bool mixed_step_supported(const PrefillArgs& p, const DecodeArgs& d) {
+    if (!prefill_tc_supported(p) || (p.num_heads / p.num_kv_heads) % 2 != 0) return false;
+    if (!decode_mma_supported(d) || d.workspace == nullptr) return false;
+    if (p.dtype != d.dtype || p.num_heads != d.num_heads || p.num_kv_heads != d.num_kv_heads || p.stream != d.stream) return false;
+    if (p.total_q <= 0 || d.batch <= 0) return false;
+    return true;
+}
+
+int launch_mixed_step(const PrefillArgs& p, const DecodeArgs& d, int prefill_blocks) {
+    return p.dtype == NVK_BF16 ? launch_mixed_typed<__nv_bfloat16>(p, d, prefill_blocks, true)
+                               : launch_mixed_typed<__half>(p, d, prefill_blocks, false);
 }
 
 }  // namespace nvk
