@@ -105,6 +105,24 @@ class PeerAllReduce:
         nvk.launch_count += 1
         return self.result[:n].view(rows, cols), self.normed[:n].view(rows, cols)
 
+    def row_linear_all_reduce_add_rmsnorm(self, x, weight, residual, norm_weight, eps: float):
+        """``h = residual + sum over ranks of x @ weight.T``, ``x_norm = rmsnorm(h) * norm_weight``: this library's GEMM whose
+        epilogue pushes the partial sums to the ranks that reduce them, then the all-reduce kernel without its own push."""
+        nvk, torch = self.nvk, self.torch
+        rows, cols = x.shape[0], weight.shape[0]
+        n = rows * cols
+        if n > self.max_elems or rows % self.world != 0:
+            raise ValueError("rows must be a multiple of world and the message must fit the peer buffers")
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nvk._check(nvk.lib().nvk_tp_row_linear_allreduce_add_rmsnorm(
+            ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(weight.data_ptr()), ctypes.c_int64(rows), ctypes.c_int64(cols),
+            ctypes.c_int64(weight.shape[1]), ctypes.c_void_p(self.addend.data_ptr()), ctypes.c_void_p(self.result.data_ptr()),
+            ctypes.c_void_p(self.normed.data_ptr()), self._stage_tab, ctypes.c_size_t(self.stage_bytes), self._flags,
+            ctypes.c_void_p(residual.data_ptr()), ctypes.c_void_p(norm_weight.data_ptr()), ctypes.c_float(eps), ctypes.c_int(self.rank),
+            ctypes.c_int(self.world), ctypes.c_int(nvk._dtype_code(self.addend)), stream))
+        nvk.launch_count += 2
+        return self.result[:n].view(rows, cols), self.normed[:n].view(rows, cols)
+
     def status(self) -> int:
         """0 when every wait on the peers completed; 1 / 2 when a peer's data never arrived (synchronises the stream)."""
         out = ctypes.c_int(0)
@@ -152,6 +170,18 @@ class InProcessAllReduce:
             ctypes.c_void_p(weight.data_ptr()) if fused else None, ctypes.c_float(eps), ctypes.c_int(self.world),
             ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(nvk._dtype_code(self.addend[0])), stream))
         nvk.launch_count += 1
+
+    def row_linear_launch(self, xs, weights, residuals, norm_weight, eps: float = 1e-6) -> None:
+        """Every rank's row-parallel GEMM (its epilogue pushing the partial sums) and the fused all-reduce that skips its push."""
+        nvk, torch = self.nvk, self.torch
+        rows, cols = xs[0].shape[0], weights[0].shape[0]
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nvk._check(nvk.lib().nvk_tp_row_linear_allreduce_add_rmsnorm_inprocess(
+            self._tab(xs), self._tab(weights), ctypes.c_int64(rows), ctypes.c_int64(cols), ctypes.c_int64(weights[0].shape[1]),
+            self._tab(self.addend), self._tab(self.result), self._tab(self.normed), self._tab(self.stage),
+            ctypes.c_size_t(self.stage_bytes), self._tab(self.flags), self._tab(residuals), ctypes.c_void_p(norm_weight.data_ptr()),
+            ctypes.c_float(eps), ctypes.c_int(self.world), ctypes.c_int(nvk._dtype_code(self.addend[0])), stream))
+        nvk.launch_count += self.world + 1
 
     def status(self, rank: int = 0) -> int:
         out = ctypes.c_int(0)

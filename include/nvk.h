@@ -288,6 +288,52 @@ int nvk_attention_mixed_step(const void* p_query, const void* p_key, const void*
                              int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
                              int dtype, void* workspace, size_t workspace_bytes, int prefill_blocks, void* stream);
 
+/*
+ * The linears on either side of attention, as tcgen05 GEMMs whose epilogue does what follows them.  Weights are
+ * [out_features, in_features] row-major (how the reference's Linear layers and its loader keep them,
+ * src/layers/linear.cpp:77-140), activations [rows, in_features]; F16 / BF16, fp32 accumulation, the product rounded
+ * to the 16-bit type before anything else is done with it (so the results are those of the unfused sequence to
+ * within one unit of that type).  out_features must be a multiple of 128, in_features a multiple of 8, pointers
+ * 16-byte aligned.  A bounded wait inside these kernels that runs out is reported by nvk_gemm_status (synchronises the
+ * stream, reads and clears the device's error word; 0 = every launch completed).
+ *
+ * nvk_linear: out = x * weight^T and nothing else (Linear::forward without bias; it exists so that the GEMM core can
+ * be tested on its own).
+ *
+ * nvk_qkv_linear_norm_rope_store: QKVParallelLinear::forward (src/layers/linear.cpp:348-420) followed by
+ * fused_split_norm_rope_store (src/kernels/split_qkv.cu:62-154) -- the first half of
+ * TransformerAttention::forward (src/models/transformer.cpp:118-139) -- as ONE launch: head_dim 128 makes a 128-column
+ * tile of the product one head, so the RMSNorm, the rotation and the scatter into the paged cache happen on the
+ * accumulator and the packed qkv tensor is never written.  qkv_weight [(Hq + 2 Hkv) * 128, in_features]; the other
+ * arguments as in nvk_fused_split_norm_rope_store (slot_mapping NULL = rows go to rows; both norm weights NULL = no norm).
+ *
+ * nvk_tp_row_linear_allreduce_add_rmsnorm: RowParallelLinear::forward with its all-reduce (src/layers/linear.cpp:306-320)
+ * plus the residual add and the RMSNorm that follow in the decoder layer.  The GEMM's epilogue delivers every row of
+ * this rank's partial sum to the rank that reduces it -- its own rows into `addend` (scratch, [rows, out_features]), the
+ * others as tagged vectors over NVLink into the owners' staging areas -- so the transfer overlaps the remaining tiles,
+ * and the all-reduce kernel that follows starts with the reduction.  Buffers, contract and results as for
+ * nvk_tp_allreduce_add_rmsnorm (same staging areas and flag area; calls of either kind may alternate).
+ * The _inprocess form runs all ranks on one device (one GEMM launch per rank, one cooperative all-reduce launch).
+ */
+int nvk_linear(const void* x, const void* weight, void* out, int64_t rows, int64_t out_features, int64_t in_features, int dtype,
+               void* stream);
+int nvk_qkv_linear_norm_rope_store(const void* x, const void* qkv_weight, int64_t rows, int64_t in_features,
+                                   const int32_t* positions, const void* q_norm_weight, const void* k_norm_weight,
+                                   float norm_eps, const float* cos_sin_cache, int64_t max_positions,
+                                   const int32_t* slot_mapping, void* k_cache, void* v_cache, int64_t cache_rows,
+                                   int num_q_heads, int num_kv_heads, int head_dim, void* q_out, int dtype, void* stream);
+int nvk_tp_row_linear_allreduce_add_rmsnorm(const void* x, const void* weight, int64_t rows, int64_t out_features,
+                                            int64_t in_features, void* addend, void* out, void* norm, void* const* stage_ptrs,
+                                            size_t stage_bytes, void* flags, const void* residual, const void* norm_weight,
+                                            float eps, int rank, int world, int dtype, void* stream);
+int nvk_tp_row_linear_allreduce_add_rmsnorm_inprocess(const void* const* x_ptrs, const void* const* weight_ptrs, int64_t rows,
+                                                      int64_t out_features, int64_t in_features, void* const* addend_ptrs,
+                                                      void* const* out_ptrs, void* const* norm_ptrs, void* const* stage_ptrs,
+                                                      size_t stage_bytes, void* const* flag_ptrs,
+                                                      const void* const* residual_ptrs, const void* norm_weight, float eps,
+                                                      int world, int dtype, void* stream);
+int nvk_gemm_status(void* stream, int* status);
+
 #ifdef __cplusplus
 }
 #endif

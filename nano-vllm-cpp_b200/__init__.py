@@ -30,6 +30,8 @@ EXPORTED_SYMBOLS = (
     "nvk_tp_allreduce_flag_bytes", "nvk_tp_allreduce_stage_bytes", "nvk_tp_allreduce_set_wait_limit_ms", "nvk_tp_allreduce",
     "nvk_tp_allreduce_status", "nvk_tp_allreduce_reset", "nvk_tp_allreduce_add_rmsnorm", "nvk_tp_allreduce_inprocess",
     "nvk_prefill_status", "nvk_decode_attention_static_scratch_bytes", "nvk_attention_mixed_step",
+    "nvk_linear", "nvk_qkv_linear_norm_rope_store", "nvk_tp_row_linear_allreduce_add_rmsnorm",
+    "nvk_tp_row_linear_allreduce_add_rmsnorm_inprocess", "nvk_gemm_status",
 )
 
 _lib = None
@@ -314,3 +316,36 @@ def attention_mixed_step(p_query, cu_seqlens_q, p_key, p_value, cu_seqlens_k, p_
         ctypes.c_int(_dtype_code(p_query)), _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
         ctypes.c_int(prefill_blocks), _stream()))
     launch_count += 2
+
+
+def linear(x, weight, out) -> None:
+    """``out = x @ weight.T`` on this library's tcgen05 GEMM (``nvk_linear``); weight [out_features, in_features]."""
+    global launch_count
+    for n, t in (("x", x), ("weight", weight), ("out", out)):
+        _require_cuda(n, t)
+    _check(lib().nvk_linear(_ptr(x), _ptr(weight), _ptr(out), ctypes.c_int64(x.shape[0]), ctypes.c_int64(weight.shape[0]),
+                            ctypes.c_int64(weight.shape[1]), ctypes.c_int(_dtype_code(x)), _stream()))
+    launch_count += 1
+
+
+def qkv_linear_norm_rope_store(x, qkv_weight, positions, q_norm_weight, k_norm_weight, norm_eps, cos_sin_cache, slot_mapping,
+                               k_cache, v_cache, num_q_heads, num_kv_heads, head_dim, q_out) -> None:
+    """QKV projection + split + q / k RMSNorm + RoPE + cache store as one launch (``nvk_qkv_linear_norm_rope_store``)."""
+    global launch_count
+    for n, t in (("x", x), ("qkv_weight", qkv_weight), ("positions", positions), ("cos_sin_cache", cos_sin_cache),
+                 ("k_cache", k_cache), ("v_cache", v_cache), ("q_out", q_out)):
+        _require_cuda(n, t)
+    row = num_kv_heads * head_dim
+    _check(lib().nvk_qkv_linear_norm_rope_store(
+        _ptr(x), _ptr(qkv_weight), ctypes.c_int64(x.shape[0]), ctypes.c_int64(x.shape[1]), _ptr(positions), _ptr(q_norm_weight),
+        _ptr(k_norm_weight), ctypes.c_float(norm_eps), _ptr(cos_sin_cache), ctypes.c_int64(cos_sin_cache.shape[0]),
+        _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), ctypes.c_int64(k_cache.numel() // row), ctypes.c_int(num_q_heads),
+        ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim), _ptr(q_out), ctypes.c_int(_dtype_code(x)), _stream()))
+    launch_count += 1
+
+
+def gemm_status() -> int:
+    """Reads and clears the error word of the GEMM kernels on the current device (synchronises the current stream)."""
+    out = ctypes.c_int(0)
+    _check(lib().nvk_gemm_status(_stream(), ctypes.byref(out)))
+    return int(out.value)

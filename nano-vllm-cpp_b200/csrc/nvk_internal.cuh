@@ -101,6 +101,14 @@ int launch_decode_mma(const DecodeArgs& a);
 namespace dec { struct DecodeParams; }
 int decode_plan(const DecodeArgs& a, dec::DecodeParams* out);
 int launch_decode_merge(const dec::DecodeParams& p, int64_t batch, int dtype, cudaStream_t stream);
+// Fused all-reduce launchers (tp_allreduce.cu); `pushed`: the other ranks' slices were already pushed by the GEMM
+// that produced the addend (gemm_fused.cu), the kernel starts with the reduction.
+int launch_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes, void* flags,
+                                 const void* residual, const void* weight, float eps, int rank, int world, int rows, int cols,
+                                 int dtype, bool pushed, cudaStream_t stream);
+int launch_allreduce_inprocess(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs, void* const* stage_ptrs,
+                               size_t stage_bytes, void* const* flag_ptrs, const void* const* residual_ptrs, const void* weight,
+                               float eps, int world, int rows, int cols, int dtype, bool pushed, cudaStream_t stream);
 // One launch for a step that holds prefill sequences and decode sequences (prefill_attn_tc.cu), then the split merge.
 bool mixed_step_supported(const PrefillArgs& p, const DecodeArgs& d);
 int launch_mixed_step(const PrefillArgs& p, const DecodeArgs& d, int prefill_blocks);

@@ -62,6 +62,7 @@ struct ArParams {
     long long wait_cycles;
     float eps;
     int rank, world, cols;
+    int pushed;                              // 1: the producer of the addend already pushed the other ranks' slices (gemm_fused.cu)
 };
 struct ArGroup { ArParams r[NVK_TP_MAX_RANKS]; };   // in-process form: one parameter set per rank
 
@@ -184,7 +185,7 @@ __device__ __forceinline__ void allreduce_body(const ArParams& p, int block, int
 
     if (!poisoned) {
         // ---- 1. push this rank's slices of the other ranks' chunks ---------------------------------------------
-        for (int64_t seg = block; seg < segs; seg += blocks) {
+        for (int64_t seg = block; seg < segs && !p.pushed; seg += blocks) {
             const int64_t v0 = seg * p.seg_vecs;
             const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
             for (int v = tid; v < n; v += kArThreads) {
@@ -411,10 +412,10 @@ extern "C" int nvk_tp_allreduce(const void* in, void* out, void* const* stage_pt
     return launch<false>(p, pl.blocks, dtype, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes,
-                                            void* flags, const void* residual, const void* weight, float eps, int rank, int world,
-                                            int rows, int cols, int dtype, void* stream) {
-    using namespace nvk;
+namespace nvk {
+int launch_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes, void* flags,
+                                 const void* residual, const void* weight, float eps, int rank, int world, int rows, int cols,
+                                 int dtype, bool pushed, cudaStream_t stream) {
     const char* what = "tp all-reduce + add + rmsnorm";
     if (rows <= 0 || world <= 0 || rows % world != 0) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: rows must be a positive multiple of world", what);
     if (cols <= 0 || cols % 8 != 0 || cols > kArThreads * kMaxVecs * 8)
@@ -428,14 +429,22 @@ extern "C" int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* nor
     ArParams p{};
     fill_common(p, stage_ptrs, flags, rank, world, stage_bytes, pl);
     p.in = in; p.out = out; p.norm = norm; p.residual = residual; p.weight = weight; p.eps = eps; p.cols = cols;
-    return launch<true>(p, pl.blocks, dtype, static_cast<cudaStream_t>(stream));
+    p.pushed = pushed ? 1 : 0;
+    return launch<true>(p, pl.blocks, dtype, stream);
+}
+}  // namespace nvk
+
+extern "C" int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes,
+                                            void* flags, const void* residual, const void* weight, float eps, int rank, int world,
+                                            int rows, int cols, int dtype, void* stream) {
+    return nvk::launch_allreduce_add_rmsnorm(in, out, norm, stage_ptrs, stage_bytes, flags, residual, weight, eps, rank, world, rows,
+                                             cols, dtype, false, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int nvk_tp_allreduce_inprocess(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
-                                          void* const* stage_ptrs, size_t stage_bytes, void* const* flag_ptrs,
-                                          const void* const* residual_ptrs, const void* weight, float eps, int world, int rows,
-                                          int cols, int dtype, void* stream) {
-    using namespace nvk;
+namespace nvk {
+int launch_allreduce_inprocess(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs, void* const* stage_ptrs,
+                               size_t stage_bytes, void* const* flag_ptrs, const void* const* residual_ptrs, const void* weight,
+                               float eps, int world, int rows, int cols, int dtype, bool pushed, cudaStream_t stream) {
     const char* what = "tp all-reduce (in-process)";
     const bool fused = norm_ptrs != nullptr;
     if (!in_ptrs || !out_ptrs || !flag_ptrs) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: pointer tables must be defined", what);
@@ -456,6 +465,7 @@ extern "C" int nvk_tp_allreduce_inprocess(const void* const* in_ptrs, void* cons
         fill_common(g.r[r], stage_ptrs, flag_ptrs[r], r, world, stage_bytes, pl);
         g.r[r].in = in_ptrs[r]; g.r[r].out = out_ptrs[r];
         if (fused) { g.r[r].norm = norm_ptrs[r]; g.r[r].residual = residual_ptrs[r]; g.r[r].weight = weight; g.r[r].eps = eps; g.r[r].cols = cols; }
+        g.r[r].pushed = pushed ? 1 : 0;
     }
     // every block of every rank must be resident at once: ask the occupancy calculator, shrink the grid if needed
     const void* fn = fused ? (dtype == NVK_BF16 ? reinterpret_cast<const void*>(allreduce_ll_inprocess_kernel<__nv_bfloat16, true>)
@@ -472,10 +482,18 @@ extern "C" int nvk_tp_allreduce_inprocess(const void* const* in_ptrs, void* cons
     if (fit < 1) return fail(NVK_ERR_UNSUPPORTED, "%s: %d ranks do not fit on this device at once", what, world);
     if (blocks > fit) blocks = fit;   // blocks stride over the segments, any count is valid
     void* args[] = {&g};
-    e = cudaLaunchCooperativeKernel(fn, dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(world)), dim3(kArThreads), args, 0,
-                                    static_cast<cudaStream_t>(stream));
+    e = cudaLaunchCooperativeKernel(fn, dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(world)), dim3(kArThreads), args, 0, stream);
     if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
     return check_launch("tp all-reduce (in-process) launch");
+}
+}  // namespace nvk
+
+extern "C" int nvk_tp_allreduce_inprocess(const void* const* in_ptrs, void* const* out_ptrs, void* const* norm_ptrs,
+                                          void* const* stage_ptrs, size_t stage_bytes, void* const* flag_ptrs,
+                                          const void* const* residual_ptrs, const void* weight, float eps, int world, int rows,
+                                          int cols, int dtype, void* stream) {
+    return nvk::launch_allreduce_inprocess(in_ptrs, out_ptrs, norm_ptrs, stage_ptrs, stage_bytes, flag_ptrs, residual_ptrs, weight, eps,
+                                           world, rows, cols, dtype, false, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int nvk_tp_allreduce_status(const void* flags, void* stream, int* status) {
