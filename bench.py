@@ -486,7 +486,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--no-other-kernels", action="store_true", help="N = 1: skip the short runs of the kernels beside paged decode")
     ap.add_argument("--no-tp-e2e", action="store_true", help="N > 1: skip the tensor-parallel end-to-end decoder run")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e", "decode_int8"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e", "decode_int8", "linears", "decode_tp"],
                     help="decode is the benchmark; prefill / store / prologue / mixed / decode_int8 time the remaining kernels of the path "
                          "(1 GPU); e2e reports output tokens per second of the whole decoder, tensor-parallel over --gpus")
     ap.add_argument("--e2e-layers", type=int, default=36, help="e2e workload: decoder layers (36 = the named model)")
@@ -494,6 +494,8 @@ def main():
     ap.add_argument("--e2e-maxlen", type=int, default=1024, help="e2e workload: longest prompt / output")
     ap.add_argument("--no-graph", action="store_true", help="e2e workload: run decode steps eagerly")
     ap.add_argument("--e2e-kv", default="bf16", choices=["bf16", "int8"], help="e2e workload: KV cache format")
+    ap.add_argument("--e2e-linears", default="cublas", choices=["cublas", "fused"],
+                    help="e2e workload: decode-step QKV / o_proj / down_proj as cuBLAS GEMMs + kernels, or this library's fused GEMMs")
     ap.add_argument("--e2e-allreduce", default="peer", choices=["nccl", "peer"],
                     help="e2e workload, N > 1: all-reduce of the decode steps through NCCL or the peer-memory kernel")
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
@@ -544,7 +546,7 @@ def main():
         line = eb.run_e2e(nvk, torch, dist, rank, world, torch.device(f"cuda:{local_rank}"),
                           em.DecoderConfig(layers=args.e2e_layers), num_seqs=args.e2e_seqs,
                           len_lo=min(100, args.e2e_maxlen), len_hi=args.e2e_maxlen, use_graph=not args.no_graph,
-                          kv_dtype=args.e2e_kv, allreduce=args.e2e_allreduce)
+                          kv_dtype=args.e2e_kv, allreduce=args.e2e_allreduce, linears=args.e2e_linears)
         if sampler:
             line["clocks"] = sampler.finish()
         if rank == 0:
@@ -594,6 +596,10 @@ def main():
             line = kb.bench_store(nvk, torch, dev, steps, args.warmup)
         elif args.workload == "decode_int8":
             line = kb.bench_decode_int8(nvk, torch, dev, steps, args.warmup, batch=args.batch)
+        elif args.workload == "decode_tp":
+            line = kb.bench_decode_tp_shape(nvk, torch, dev, steps, args.warmup, batch=args.batch)
+        elif args.workload == "linears":
+            line = kb.bench_linears(nvk, torch, dev, min(steps, 20), args.warmup, rows=args.rows)
         elif args.workload == "mixed":
             line = kb.bench_mixed(nvk, torch, dev, min(steps, 10), min(args.warmup, 3), layers=args.layers,
                                   single_launch=args.mixed_single_launch, prefill_blocks_hint=args.mixed_prefill_blocks)

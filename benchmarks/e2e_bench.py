@@ -19,7 +19,7 @@ RING = 64   # pinned metadata slots in flight
 
 
 def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None, num_seqs=256, len_lo=100, len_hi=1024,
-            seed=0, use_graph=True, kv_dtype="bf16", allreduce="peer"):
+            seed=0, use_graph=True, kv_dtype="bf16", allreduce="peer", linears="cublas"):
     cfg = cfg or DecoderConfig()
     bs = cfg.block_size
     prompts, output_lens = make_requests(num_seqs, cfg.vocab, len_lo, len_hi, seed)
@@ -31,7 +31,8 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
     if allreduce == "peer" and world > 1:
         from .tp_comm import PeerAllReduce
         comm = PeerAllReduce(nvk, torch, dist, dev, rank, world, num_seqs * cfg.hidden, torch.bfloat16)
-    model = Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=num_blocks, seed=seed, kv_dtype=kv_dtype, peer_comm=comm)
+    model = Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=num_blocks, seed=seed, kv_dtype=kv_dtype, peer_comm=comm,
+                    linears=linears)
     torch.cuda.synchronize()
     build_s = time.time() - t0
     model.ensure_workspace(num_seqs, table_width)
@@ -153,6 +154,10 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
                    "kv_cache": "int8 with fp16 per-(token, head) scales" if model.int8 else "bf16",
                    "allreduce": ("decode steps: peer-memory all-reduce fused with the residual add and the RMSNorm "
                                  "(nvk_tp_allreduce_add_rmsnorm); prefill steps: NCCL" if comm is not None else "NCCL"),
+                   "linears": ("decode steps: QKV projection with split + norm + RoPE + cache store in its epilogue "
+                               "(nvk_qkv_linear_norm_rope_store)" + ("; o_proj / down_proj push their partial sums into the all-reduce "
+                               "from their epilogue (nvk_tp_row_linear_allreduce_add_rmsnorm)" if comm is not None else "") +
+                               "; other linears and prefill steps: cuBLAS" if model.fused_linears else "cuBLAS (torch.matmul)"),
                    "decode": "one captured CUDA graph of %d fixed rows" % num_seqs if graph is not None else "eager",
                    "prefill_batches": len(batches), "decode_steps": steps, "kv_blocks": num_blocks,
                    "l2": "weights (16.4 GB / tp) and KV cache exceed the 126 MB L2"},
@@ -162,6 +167,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
         "attention_ms_per_decode_step": attn_ms,
         "attention_share_of_decode_step": (attn_ms / (decode_ms / max(steps, 1))) if attn_ms else None,
         "model_build_s": build_s, "peer_allreduce_status": comm_status, "prefill_status": prefill_status,
+        "gemm_status": nvk.gemm_status() if model.fused_linears else None,
         "gpu_launches": our_launches, "gpu_launches_issued_eagerly": eager_launches,
         "e2e": {"value": out_tokens / (total_ms / 1e3), "unit": "tok/s",
                 "h2d_bytes_per_step": num_seqs * width * 4, "d2h_bytes_per_step": 0,

@@ -45,13 +45,20 @@ def rope_table(torch, dev, max_positions, head_dim, theta):
 class Decoder:
     """One tensor-parallel rank of the decoder."""
 
-    def __init__(self, nvk, torch, dev, cfg: DecoderConfig, rank=0, world=1, dist=None, num_blocks=0, seed=0, kv_dtype="bf16", peer_comm=None):
+    def __init__(self, nvk, torch, dev, cfg: DecoderConfig, rank=0, world=1, dist=None, num_blocks=0, seed=0, kv_dtype="bf16", peer_comm=None,
+                 linears="cublas"):
         if cfg.num_kv_heads % world or cfg.ffn % world or cfg.vocab % world:
             raise ValueError("heads, ffn and vocab must divide by the tensor-parallel size")
         self.nvk, self.torch, self.dev, self.cfg = nvk, torch, dev, cfg
         self.rank, self.world, self.dist = rank, world, dist
         # optional tp_comm.PeerAllReduce: messages that fit its buffers take the peer-memory kernel, larger ones NCCL
         self.peer_comm = peer_comm if world > 1 else None
+        # "fused": at decode sizes the QKV projection runs with the prologue in its epilogue and the row-parallel linears push their
+        # partial sums into the all-reduce from theirs (this library's GEMMs); "cublas": plain torch.matmul followed by the kernels
+        if linears not in ("cublas", "fused"):
+            raise ValueError("linears must be cublas or fused")
+        self.fused_linears = linears == "fused"
+        self.fused_rows_max = 512
         self.hq, self.hkv = cfg.num_heads // world, cfg.num_kv_heads // world
         self.ffn, self.vocab = cfg.ffn // world, cfg.vocab // world
         bf = torch.bfloat16
@@ -116,6 +123,8 @@ class Decoder:
         comm = self.peer_comm
         if (comm is not None and n * cols <= comm.max_elems and n % self.world == 0 and cols % 8 == 0 and cols <= 8192
                 and h.is_contiguous()):
+            if self.fused_linears and n <= self.fused_rows_max and cols % 128 == 0 and a.is_contiguous():
+                return comm.row_linear_all_reduce_add_rmsnorm(a, w, h, norm_w, self.cfg.eps)
             addend, _ = comm.buffers(n, cols)
             self.torch.matmul(a, w.t(), out=addend)
             return comm.all_reduce_add_rmsnorm(h, norm_w, self.cfg.eps, n, cols)
@@ -145,8 +154,16 @@ class Decoder:
             rows = torch.arange(n, device=self.dev, dtype=torch.int32)
         x = self.rmsnorm(h, self.layers[0]["norm_in"])
         for l, w in enumerate(self.layers):
-            qkv = x @ w["w_qkv"].t()
-            if self.int8:
+            if self.fused_linears and not self.int8 and n <= self.fused_rows_max and cfg.head_dim == 128:
+                nvk.qkv_linear_norm_rope_store(x if x.is_contiguous() else x.contiguous(), w["w_qkv"], positions, w["q_norm"],
+                                               w["k_norm"], cfg.eps, self.cos_sin, slot_mapping, self.kv_cache[0, l],
+                                               self.kv_cache[1, l], self.hq, self.hkv, cfg.head_dim, q)
+                qkv = None
+            else:
+                qkv = x @ w["w_qkv"].t()
+            if qkv is None:
+                pass
+            elif self.int8:
                 nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, rows,
                                                 k_step, v_step, self.hq, self.hkv, cfg.head_dim, q)
                 nvk.store_kvcache_int8(k_step, v_step, self.kv_cache[0, l], self.kv_cache[1, l], self.kv_scale[0, l],

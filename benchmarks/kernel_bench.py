@@ -159,14 +159,25 @@ def bench_store(nvk, torch, dev, steps, warmup, tokens=36864):
     nbytes = 2 * (2 * tokens * HKV * D * 2) + 4 * tokens
     hbm, _, kind = _peaks()
     ach = nbytes / (mean_ms * 1e-3) / 1e9
-    return {"metric": "store_kvcache_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+    clocks = LAST_CLOCKS
+    # the slot_mapping a prefill step really produces (prepare_prefill, src/engine/model_runner.cpp:520-548): consecutive
+    # tokens fill whole 256-token blocks, the blocks lie anywhere in the pool
+    order = np.random.default_rng(8).permutation(pool)[: (tokens + BS - 1) // BS].astype(np.int64)
+    blockwise = (order[:, None] * BS + np.arange(BS)[None, :]).reshape(-1)[:tokens].astype(np.int32)
+    slots_b = torch.from_numpy(blockwise).to(dev)
+    mean_b, _ = _time(torch, lambda: nvk.store_kvcache(key, value, kc, vc, slots_b), steps, warmup, flush=lambda: flush_buf.fill_(1))
+    ach_b = nbytes / (mean_b * 1e-3) / 1e9
+    LAST_CLOCKS_B = LAST_CLOCKS
+    return {"block_contiguous_slots": {"ms": mean_b, "achieved": ach_b, "unit": "GB/s", "frac": ach_b / hbm, "clocks": LAST_CLOCKS_B,
+                                       "note": "whole 256-token blocks in random order, as prepare_prefill lays a prompt out"},
+            "metric": "store_kvcache_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps,
             "warmup": warmup, "ms_per_step": mean_ms, "median_ms": med_ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": f"store_kvcache of {tokens} tokens x 8 KV heads x 128 bf16 into random slots",
                        "l2": "a 256 MB buffer is written between timed iterations"},
             "roofline": {"bound": "hbm", "kernel": "store_rows_kernel", "achieved": ach, "peak": hbm,
                          "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
-            "gpu_launches": steps, "clocks": LAST_CLOCKS}
+            "gpu_launches": 2 * steps, "clocks": clocks}
 
 
 def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ctx_hi=8192):
@@ -395,6 +406,145 @@ def bench_mixed(nvk, torch, dev, steps, warmup, layers=36, decode_seqs=192, ctx_
             "gpu_launches": steps * layers * (3 if single_launch else 5), "clocks": LAST_CLOCKS}
 
 
+def bench_decode_tp_shape(nvk, torch, dev, steps, warmup, tp=8, batch=256, layers=36, ctx_lo=100, ctx_hi=2048):
+    """Paged decode attention at the per-rank shape of a tensor-parallel decoder (``32 / tp`` query heads, ``8 / tp`` KV heads:
+    256-byte cache rows at tp = 8) with the contexts of the end-to-end configuration (prompt U[100,1024] plus up to 1024
+    generated tokens), timed as in a decoder: ``layers`` attention calls on ``layers`` distinct caches inside one replayed
+    CUDA graph; the figure is the time per layer (split-K kernel + merge)."""
+    from . import workloads as wl
+    hq, hkv = HQ // tp, HKV // tp
+    rng = np.random.default_rng(77)
+    ctx = rng.integers(ctx_lo, ctx_hi + 1, size=batch).astype(np.int32)
+    width = (2 * 1024 + BS - 1) // BS
+    tables, pool = wl.build_block_tables(rng, ctx, BS, pad_to=width)
+    bf = torch.bfloat16
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    caches = [(torch.empty((pool, BS, hkv, D), device=dev, dtype=bf).normal_(generator=gen),
+               torch.empty((pool, BS, hkv, D), device=dev, dtype=bf).normal_(generator=gen)) for _ in range(layers)]
+    q = torch.randn((batch, hq, D), generator=gen, device=dev).to(bf)
+    out = torch.empty_like(q)
+    ctx_dev, tab_dev = torch.from_numpy(ctx).to(dev), torch.from_numpy(tables).to(dev)
+    scale = 1.0 / math.sqrt(D)
+    ws = torch.empty(max(16, nvk.decode_attention_workspace_bytes(batch, hq, hkv, D, tables.shape[1], BS)), dtype=torch.uint8, device=dev)
+
+    def layer(l):
+        nvk.launch_decode_attention_paged(q, caches[l][0], caches[l][1], ctx_dev, tab_dev, hkv, D, BS, scale, out, ws)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer(0)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for l in range(layers):
+            layer(l)
+    mean_ms, med_ms = _time(torch, graph.replay, steps, warmup)
+    eager_ms, _ = _time(torch, lambda: [layer(l) for l in range(layers)], max(3, steps // 4), 2)
+    tokens = int(ctx.astype(np.int64).sum())
+    used = int(((ctx.astype(np.int64) + BS - 1) // BS).sum())
+    nbytes = tokens * hkv * D * 2 * 2 + 2 * batch * hq * D * 2 + 4 * (used + batch)
+    hbm, _, kind = _peaks()
+    per_layer_ms = mean_ms / layers
+    ach = nbytes / (per_layer_ms * 1e-3) / 1e9
+    return {"metric": "paged_decode_attention_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": per_layer_ms, "median_ms": med_ms / layers, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"paged decode attention at the per-rank shape of tp{tp}: batch {batch}, {hq}/{hkv} heads, head_dim {D}, "
+                                   f"block_size {BS}, context U[{ctx_lo},{ctx_hi}], table width {tables.shape[1]}",
+                       "context_tokens": tokens, "algorithmic_bytes": nbytes,
+                       "l2": f"time per layer of a replayed CUDA graph of {layers} calls on {layers} distinct caches "
+                             f"({layers * 2 * pool * BS * hkv * D * 2 >> 20} MB in total: beyond L2)"},
+            "eager_ms_per_layer": eager_ms / layers,
+            "roofline": {"bound": "hbm", "kernel": "decode_split_kernel + decode_merge_kernel", "achieved": ach, "peak": hbm,
+                         "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
+            "gpu_launches": steps * layers * 2, "clocks": LAST_CLOCKS}
+
+
+def bench_linears(nvk, torch, dev, steps, warmup, rows=256, layers=36):
+    """The two linears next to attention at decode size, fused with what follows them, against the sequence they replace.
+    Every figure is the time per layer of a replayed CUDA graph that walks ``layers`` distinct weight matrices (so weights
+    stream from HBM as in a decoder; together they exceed L2).
+
+    * QKV: ``nvk_qkv_linear_norm_rope_store`` against cuBLAS GEMM + ``nvk_fused_split_norm_rope_store``.
+    * plain GEMM core: ``nvk_linear`` against ``torch.matmul`` for the QKV and o_proj shapes.
+    """
+    bf = torch.bfloat16
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    hidden = 4096
+    n_qkv = (HQ + 2 * HKV) * D
+    max_pos = 4096
+    inv_freq = 1.0 / (1.0e6 ** (np.arange(0, D, 2, dtype=np.float32) / D))
+    ang = np.arange(max_pos, dtype=np.float32)[:, None] * inv_freq[None, :]
+    table = torch.from_numpy(np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)).to(dev)
+    pos = torch.randint(0, max_pos, (rows,), generator=gen, device=dev, dtype=torch.int32)
+    pool = max(64, (rows + BS - 1) // BS)
+    slots = torch.from_numpy(np.random.default_rng(11).permutation(pool * BS)[:rows].astype(np.int32)).to(dev)
+    qw = torch.ones(D, device=dev, dtype=bf)
+    kw = torch.ones(D, device=dev, dtype=bf)
+    x = torch.randn((rows, hidden), generator=gen, device=dev).mul_(0.5).to(bf)
+    w_qkv = [torch.randn((n_qkv, hidden), generator=gen, device=dev).mul_(0.02).to(bf) for _ in range(layers)]
+    w_o = [torch.randn((hidden, HQ * D), generator=gen, device=dev).mul_(0.02).to(bf) for _ in range(layers)]
+    kc = torch.zeros((pool, BS, HKV, D), device=dev, dtype=bf)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty((rows, HQ, D), device=dev, dtype=bf)
+    qkv = torch.empty((rows, n_qkv), device=dev, dtype=bf)
+    o_in = torch.randn((rows, HQ * D), generator=gen, device=dev).mul_(0.5).to(bf)
+    o_out = torch.empty((rows, hidden), device=dev, dtype=bf)
+
+    def fused_qkv(l):
+        nvk.qkv_linear_norm_rope_store(x, w_qkv[l], pos, qw, kw, 1e-6, table, slots, kc, vc, HQ, HKV, D, q_out)
+
+    def unfused_qkv(l):
+        torch.matmul(x, w_qkv[l].t(), out=qkv)
+        nvk.fused_split_norm_rope_store(qkv, pos, qw, kw, 1e-6, table, slots, kc, vc, HQ, HKV, D, q_out)
+
+    cases = {
+        "qkv_fused": fused_qkv,
+        "qkv_cublas_then_prologue": unfused_qkv,
+        "qkv_gemm_nvk_linear": lambda l: nvk.linear(x, w_qkv[l], qkv),
+        "qkv_gemm_cublas": lambda l: torch.matmul(x, w_qkv[l].t(), out=qkv),
+        "o_proj_gemm_nvk_linear": lambda l: nvk.linear(o_in, w_o[l], o_out),
+        "o_proj_gemm_cublas": lambda l: torch.matmul(o_in, w_o[l].t(), out=o_out),
+    }
+    out = {}
+    clocks = None
+    for name, fn in cases.items():
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn(0)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for l in range(layers):
+                fn(l)
+        mean_ms, med_ms = _time(torch, graph.replay, steps, warmup)
+        clocks = LAST_CLOCKS
+        wbytes = (n_qkv if name.startswith("qkv") else hidden) * hidden * 2
+        out[name] = {"us_per_layer": mean_ms * 1e3 / layers, "median_us_per_layer": med_ms * 1e3 / layers,
+                     "weight_GBps": wbytes / (mean_ms * 1e-3 / layers) / 1e9}
+        del graph
+    status = nvk.gemm_status()
+    hbm, _, kind = _peaks()
+    best = out["qkv_fused"]
+    nbytes = n_qkv * hidden * 2 + rows * hidden * 2 + rows * (HQ + 2 * HKV) * D * 2
+    ach = nbytes / (best["us_per_layer"] * 1e-6) / 1e9
+    return {"metric": "qkv_linear_norm_rope_store_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": best["us_per_layer"] * 1e-3, "median_ms": best["median_us_per_layer"] * 1e-3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"QKV projection ({hidden} -> {n_qkv}) + split + q/k RMSNorm + RoPE + KV store as one launch, {rows} rows",
+                       "l2": f"time per layer of a replayed CUDA graph over {layers} distinct weight matrices ({layers * n_qkv * hidden * 2 >> 20} MB: beyond L2)"},
+            "cases": out, "gemm_status": status,
+            "roofline": {"bound": "hbm", "kernel": "gemm_tc_kernel<T, qkv prologue epilogue>", "achieved": ach, "peak": hbm,
+                         "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
+            "gpu_launches": steps * layers * len(cases), "clocks": clocks}
+
+
 def other_kernels(nvk, torch, dev, steps=20, warmup=3):
     """Short runs of the kernels beside paged decode, for the default benchmark line: the prefill configuration
     (tensor roofline), store_kvcache at prefill size, the fused prologue at decode and prefill row counts, decode over
@@ -420,12 +570,18 @@ def other_kernels(nvk, torch, dev, steps=20, warmup=3):
     out["prefill_32x512"]["flops"] = line["config"]["flops_per_step"]
     torch.cuda.empty_cache()
     line = bench_store(nvk, torch, dev, steps, warmup)
-    out["store_kvcache_36864_tokens"] = brief(line)
+    out["store_kvcache_36864_tokens"] = brief(line, extra=("block_contiguous_slots",))
     for rows in (256, 16384):
         line = bench_prologue(nvk, torch, dev, steps, warmup, rows=rows)
         out[f"fused_prologue_{rows}_rows"] = brief(line)
     torch.cuda.empty_cache()
     line = bench_decode_int8(nvk, torch, dev, steps, warmup)
     out["decode_int8_kv"] = brief(line, extra=("bf16_cache_same_shape", "store_kvcache_int8"))
+    torch.cuda.empty_cache()
+    line = bench_decode_tp_shape(nvk, torch, dev, steps, warmup)
+    out["decode_tp8_rank_shape_in_graph"] = brief(line, extra=("eager_ms_per_layer",))
+    torch.cuda.empty_cache()
+    line = bench_linears(nvk, torch, dev, min(steps, 10), warmup)
+    out["qkv_linear_fused_prologue_256_rows"] = brief(line, extra=("cases",))
     torch.cuda.empty_cache()
     return out

@@ -84,6 +84,95 @@ store_int8_kernel(const T* __restrict__ key, const T* __restrict__ value, int8_t
     if (sub == 0) { k_scale[dst_row] = __float2half(k_sc); v_scale[dst_row] = __float2half(v_sc); }
 }
 
+// ---- 16-bit inputs: the same arithmetic in about half the instructions (the kernel above is bound by issue slots, not
+// by HBM).  Absolute maxima are taken on packed pairs in the 16-bit type (abs and max do not round, and max drops NaNs
+// as fmaxf does), K's and V's maxima travel through the shuffles as one packed register, the IEEE divisions run once
+// per lane for the two inverse scales and once for the scale the lane may store, products are converted with one F2I
+// each and packed with saturating byte packs (|x * inv| <= 127.00002, so the +-127 clamp of the reference cannot
+// bind), and the (token, head) split is 32-bit arithmetic.
+template <typename T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+    using type = __nv_bfloat162;
+    static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+    static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+    static __device__ __forceinline__ float first(type v) { return __bfloat162float(v.x); }
+    static __device__ __forceinline__ float second(type v) { return __bfloat162float(v.y); }
+    static __device__ __forceinline__ type join(type a, type b) { return __halves2bfloat162(a.x, b.x); }
+};
+template <> struct Pair16<__half> {
+    using type = __half2;
+    static __device__ __forceinline__ float lo(uint32_t w) { return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu))); }
+    static __device__ __forceinline__ float hi(uint32_t w) { return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16))); }
+    static __device__ __forceinline__ float first(type v) { return __half2float(v.x); }
+    static __device__ __forceinline__ float second(type v) { return __half2float(v.y); }
+    static __device__ __forceinline__ type join(type a, type b) { return __halves2half2(a.x, b.x); }
+};
+
+// maximum of |x| over the eight elements of a 16-byte piece (in the low half of the result)
+template <typename T>
+__device__ __forceinline__ typename Pair16<T>::type absmax8(const uint4& v) {
+    using P = typename Pair16<T>::type;
+    const P a = __habs2(*reinterpret_cast<const P*>(&v.x)), b = __habs2(*reinterpret_cast<const P*>(&v.y));
+    const P c = __habs2(*reinterpret_cast<const P*>(&v.z)), d = __habs2(*reinterpret_cast<const P*>(&v.w));
+    const P m = __hmax2(__hmax2(a, b), __hmax2(c, d));
+    return __hmax2(m, __lowhigh2highlow(m));
+}
+
+// bytes {e0, e1, e2, e3} (e0 lowest) of four integers, each saturated to int8
+__device__ __forceinline__ uint32_t pack_s8x4(int e0, int e1, int e2, int e3) {
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;\n" : "=r"(hi) : "r"(e3), "r"(e2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;\n" : "=r"(out) : "r"(e1), "r"(e0), "r"(hi));
+    return out;
+}
+
+template <typename T>
+__device__ __forceinline__ uint2 quantise8(const uint4& v, float inv) {
+    using P = Pair16<T>;
+    uint2 q;
+    q.x = pack_s8x4(__float2int_rn(__fmul_rn(P::lo(v.x), inv)), __float2int_rn(__fmul_rn(P::hi(v.x), inv)),
+                    __float2int_rn(__fmul_rn(P::lo(v.y), inv)), __float2int_rn(__fmul_rn(P::hi(v.y), inv)));
+    q.y = pack_s8x4(__float2int_rn(__fmul_rn(P::lo(v.z), inv)), __float2int_rn(__fmul_rn(P::hi(v.z), inv)),
+                    __float2int_rn(__fmul_rn(P::lo(v.w), inv)), __float2int_rn(__fmul_rn(P::hi(v.w), inv)));
+    return q;
+}
+
+template <typename T, int LANES>
+__global__ void __launch_bounds__(kStoreWarps * 32)
+store_int8_packed_kernel(const T* __restrict__ key, const T* __restrict__ value, int8_t* __restrict__ k_cache,
+                         int8_t* __restrict__ v_cache, __half* __restrict__ k_scale, __half* __restrict__ v_scale,
+                         const int32_t* __restrict__ slot_mapping, uint32_t total, uint32_t num_kv_heads, int64_t cache_rows) {
+    using P = typename Pair16<T>::type;
+    constexpr int D = 8 * LANES;
+    constexpr int kPerWarp = 32 / LANES;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t sub = lane % LANES;
+    uint32_t work = (blockIdx.x * kStoreWarps + (threadIdx.x >> 5)) * kPerWarp + lane / LANES;   // (token, head)
+    if (work >= total) work = total - 1;   // lanes past the end repeat the last vector: the shuffles stay full-warp
+    const uint32_t token = work / num_kv_heads;
+    const uint32_t head = work - token * num_kv_heads;
+    const size_t src = static_cast<size_t>(work) * D + sub * 8;
+    const uint4 kv = __ldcs(reinterpret_cast<const uint4*>(key + src));
+    const uint4 vv = __ldcs(reinterpret_cast<const uint4*>(value + src));
+    const int64_t slot = slot_mapping[token];
+    P m = Pair16<T>::join(absmax8<T>(kv), absmax8<T>(vv));   // K's maximum in the low half, V's in the high half
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) {
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const uint32_t*>(&m), o);
+        m = __hmax2(m, *reinterpret_cast<const P*>(&other));
+    }
+    if (slot < 0 || slot >= cache_rows) return;
+    const float kmax = Pair16<T>::first(m), vmax = Pair16<T>::second(m);
+    const float k_inv = __fdiv_rn(127.0f, fmaxf(kmax, 1e-10f)), v_inv = __fdiv_rn(127.0f, fmaxf(vmax, 1e-10f));
+    const size_t dst_row = static_cast<size_t>(slot) * num_kv_heads + head;
+    *reinterpret_cast<uint2*>(k_cache + dst_row * D + sub * 8) = quantise8<T>(kv, k_inv);
+    *reinterpret_cast<uint2*>(v_cache + dst_row * D + sub * 8) = quantise8<T>(vv, v_inv);
+    if (sub < 2) {   // lane 0 of the group stores K's scale, lane 1 V's
+        const float sc = fmaxf(__fdiv_rn(sub == 0 ? kmax : vmax, 127.0f), 1e-10f);
+        (sub == 0 ? k_scale : v_scale)[dst_row] = __float2half(sc);
+    }
+}
+
 // General decode path: one warp per (sequence, query head), lane owns D / 32 contiguous elements; serial online
 // softmax over the keys as in the reference.  Used for fp32 queries and head dims other than 128.
 template <typename T, int V>
@@ -147,6 +236,22 @@ int launch_store_typed(const void* key, const void* value, void* k_cache, void* 
     const int64_t per_block = static_cast<int64_t>(kStoreWarps) * (32 / lanes);
     const int64_t blocks = (work + per_block - 1) / per_block;
     if (blocks > 0x7fffffffLL) return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_int8: too many tokens");
+    if constexpr (sizeof(T) == 2) {
+        if (work > 0 && work < 0x7fffffffLL) {
+#define NVK_LAUNCH_PACKED(L)                                                                                        \
+    store_int8_packed_kernel<T, L><<<static_cast<unsigned>(blocks), kStoreWarps * 32, 0, stream>>>(                  \
+        static_cast<const T*>(key), static_cast<const T*>(value), static_cast<int8_t*>(k_cache),                   \
+        static_cast<int8_t*>(v_cache), static_cast<__half*>(k_scale), static_cast<__half*>(v_scale), slot_mapping, \
+        static_cast<uint32_t>(work), static_cast<uint32_t>(num_kv_heads), cache_rows)
+            switch (lanes) {
+                case 8: NVK_LAUNCH_PACKED(8); break;
+                case 16: NVK_LAUNCH_PACKED(16); break;
+                default: NVK_LAUNCH_PACKED(32); break;
+            }
+#undef NVK_LAUNCH_PACKED
+            return check_launch("store_kvcache_int8 kernel launch");
+        }
+    }
 #define NVK_LAUNCH(L)                                                                                               \
     store_int8_kernel<T, V, L><<<static_cast<unsigned>(blocks), kStoreWarps * 32, 0, stream>>>(                      \
         static_cast<const T*>(key), static_cast<const T*>(value), static_cast<int8_t*>(k_cache),                   \

@@ -26,8 +26,8 @@ def tiny(em, layers=2):
                             max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=2048)
 
 
-@pytest.mark.parametrize("kv_dtype,tol", [("bf16", 0.03), ("int8", 0.06)])
-def test_decode_continues_a_sequence_like_a_longer_prefill(mods, kv_dtype, tol):
+@pytest.mark.parametrize("kv_dtype,tol,linears", [("bf16", 0.03, "cublas"), ("int8", 0.06, "cublas"), ("bf16", 0.03, "fused")])
+def test_decode_continues_a_sequence_like_a_longer_prefill(mods, kv_dtype, tol, linears):
     torch, nvk, em, es, _ = mods
     dev = torch.device("cuda:0")
     cfg = tiny(em)
@@ -35,7 +35,7 @@ def test_decode_continues_a_sequence_like_a_longer_prefill(mods, kv_dtype, tol):
     lens = [37, 300, 256]                       # inside a block, across a block boundary, exactly at one
     extra = 3                                   # tokens continued by decode steps
     full = [rng.integers(0, cfg.vocab, size=n + extra) for n in lens]
-    model = em.Decoder(nvk, torch, dev, cfg, num_blocks=16, seed=1, kv_dtype=kv_dtype)
+    model = em.Decoder(nvk, torch, dev, cfg, num_blocks=16, seed=1, kv_dtype=kv_dtype, linears=linears)
     model.ensure_workspace(len(lens), 4)
 
     hidden = {}
@@ -72,11 +72,13 @@ def test_decode_continues_a_sequence_like_a_longer_prefill(mods, kv_dtype, tol):
             assert err <= tol * max(1.0, np.abs(want).max()), (i, step, err, np.abs(want).max())
 
 
-@pytest.mark.parametrize("use_graph,kv_dtype", [(True, "bf16"), (False, "bf16"), (True, "int8")])
-def test_benchmark_loop_runs(mods, use_graph, kv_dtype):
+@pytest.mark.parametrize("use_graph,kv_dtype,linears", [(True, "bf16", "cublas"), (False, "bf16", "cublas"), (True, "int8", "cublas"),
+                                                        (True, "bf16", "fused")])
+def test_benchmark_loop_runs(mods, use_graph, kv_dtype, linears):
     torch, nvk, em, _, eb = mods
     line = eb.run_e2e(nvk, torch, None, 0, 1, torch.device("cuda:0"), tiny(em, layers=2), num_seqs=6, len_lo=5, len_hi=300,
-                      seed=2, use_graph=use_graph, kv_dtype=kv_dtype)
+                      seed=2, use_graph=use_graph, kv_dtype=kv_dtype, linears=linears)
     assert line["output_tokens"] > 0 and line["value"] > 0
+    assert not line["gemm_status"]
     assert line["config"]["decode_steps"] == line["steps"] - line["config"]["prefill_batches"]
     assert line["gpu_launches"] > 0

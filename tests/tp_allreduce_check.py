@@ -227,6 +227,49 @@ def main():
 
     us_fused = timed(lambda: comm.all_reduce_add_rmsnorm(res_buf, weight, 1e-6, rows, cols))
     us_unfused = timed(unfused)
+    # row-parallel linear whose epilogue pushes the partial sums (o_proj shape: in_features 4096 / world), against
+    # cuBLAS GEMM + NCCL + add + rms_norm; then timing over 36 distinct weight matrices (weights stream from HBM)
+    k_in = 4096 // world
+    w_rows = [(0.02 * torch.randn((cols, k_in), generator=gen, device=dev)).to(torch.bfloat16) for _ in range(36)]
+    x_in = (0.5 * torch.randn((rows, k_in), generator=gen, device=dev)).to(torch.bfloat16)
+    part = x_in @ w_rows[0].t()
+    dist.all_reduce(part)
+    want_h = res_buf + part
+    want_x = torch.nn.functional.rms_norm(want_h, (cols,), weight, 1e-6)
+    h_f, x_f = comm.row_linear_all_reduce_add_rmsnorm(x_in, w_rows[0], res_buf, weight, 1e-6)
+    torch.cuda.synchronize()
+    eh = float((h_f.float() - want_h.float()).abs().max())
+    ex = float((x_f.float() - want_x.float()).abs().max())
+    tol_h = 2.0 ** -7 * float(want_h.float().abs().max())
+    tol_x = 2.0 ** -6 * float(want_x.float().abs().max())
+    gemm_word = nvk.gemm_status()
+    if rank == 0:
+        print(f"row-parallel linear + all-reduce + add + rmsnorm: max |h - ref| = {eh:.4e} (allowed {tol_h:.4e}), "
+              f"max |x - ref| = {ex:.4e} (allowed {tol_x:.4e}), gemm status {gemm_word}", flush=True)
+    ok = ok and eh <= tol_h and ex <= tol_x and gemm_word == 0 and comm.status() == 0
+    turn = [0]
+    addend_buf, _ = comm.buffers(rows, cols)
+
+    def next_w():
+        turn[0] += 1
+        return w_rows[turn[0] % len(w_rows)]
+
+    def gemm_then_fused():
+        torch.matmul(x_in, next_w().t(), out=addend_buf)
+        comm.all_reduce_add_rmsnorm(res_buf, weight, 1e-6, rows, cols)
+
+    def gemm_then_nccl():
+        torch.matmul(x_in, next_w().t(), out=scratch)
+        dist.all_reduce(scratch)
+        torch.nn.functional.rms_norm(res_buf + scratch, (cols,), weight, 1e-6)
+
+    us_row_fused = timed(lambda: comm.row_linear_all_reduce_add_rmsnorm(x_in, next_w(), res_buf, weight, 1e-6))
+    us_row_two = timed(gemm_then_fused)
+    us_row_nccl = timed(gemm_then_nccl)
+    ok = ok and nvk.gemm_status() == 0 and comm.status() == 0
+    if rank == 0:
+        print(f"timing world {world}: row-parallel linear ({k_in} -> {cols}) + all-reduce + add + rmsnorm: pushed from the GEMM epilogue "
+              f"{us_row_fused:.2f} us, cuBLAS + fused all-reduce {us_row_two:.2f} us, cuBLAS + NCCL + add + rms_norm {us_row_nccl:.2f} us", flush=True)
     if rank == 0:
         print(f"timing world {world}: peer-memory all-reduce {us_peer:.2f} us, NCCL {us_nccl:.2f} us per 2 MiB message (in a graph)", flush=True)
         print(f"timing world {world}: fused all-reduce + add + rmsnorm {us_fused:.2f} us, NCCL + add + rms_norm {us_unfused:.2f} us", flush=True)

@@ -46,10 +46,14 @@ def main():
         return hs
 
     comm = None
-    if os.environ.get("TP_CHECK_PEER") == "1":   # decode-step all-reduces through the peer-memory kernel
+    mode = os.environ.get("TP_CHECK_PEER", "0")   # 1: decode-step all-reduces through the peer-memory kernel; 2: and the fused linears
+    if mode in ("1", "2"):
         tc = importlib.import_module("benchmarks.tp_comm")
         comm = tc.PeerAllReduce(nvk, torch, dist, dev, rank, world, 8 * cfg.hidden, torch.bfloat16)
-    sharded = run(em.Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=16, seed=4, peer_comm=comm))
+    sharded = run(em.Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=16, seed=4, peer_comm=comm,
+                             linears="fused" if mode == "2" else "cublas"))
+    if mode == "2":
+        assert nvk.gemm_status() == 0
     if comm is not None:
         assert comm.status() == 0
         comm.close()
