@@ -131,8 +131,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
     return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 __device__ __forceinline__ void st_tagged(uint4* slot, const uint4& v, uint32_t ep) {   // the all-reduce's wire format
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(slot), "r"(v.x), "r"(ep), "r"(v.y), "r"(ep) : "memory");
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(slot + 1), "r"(v.z), "r"(ep), "r"(v.w), "r"(ep) : "memory");
+    // one 32-byte store per payload vector: a warp writes 1 KiB of contiguous, fully covered 128-byte lines (two 16-byte
+    // stores per lane left every sector half written per instruction, which costs NVLink packets)
+    asm volatile("st.volatile.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                 ::"l"(slot), "r"(v.x), "r"(ep), "r"(v.y), "r"(ep), "r"(v.z), "r"(ep), "r"(v.w), "r"(ep) : "memory");
 }
 
 // 32 accumulator columns of this thread's row, rounded to T (what the unfused GEMM would have written)

@@ -67,8 +67,10 @@ struct ArParams {
 struct ArGroup { ArParams r[NVK_TP_MAX_RANKS]; };   // in-process form: one parameter set per rank
 
 __device__ __forceinline__ void st_tagged(uint4* slot, const uint4& v, uint32_t ep) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(slot), "r"(v.x), "r"(ep), "r"(v.y), "r"(ep) : "memory");
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(slot + 1), "r"(v.z), "r"(ep), "r"(v.w), "r"(ep) : "memory");
+    // one 32-byte store per payload vector: a warp writes 1 KiB of contiguous, fully covered 128-byte lines (two 16-byte
+    // stores per lane left every sector half written per instruction, which costs NVLink packets)
+    asm volatile("st.volatile.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                 ::"l"(slot), "r"(v.x), "r"(ep), "r"(v.y), "r"(ep), "r"(v.z), "r"(ep), "r"(v.w), "r"(ep) : "memory");
 }
 __device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
     uint4 v;
@@ -185,17 +187,36 @@ __device__ __forceinline__ void allreduce_body(const ArParams& p, int block, int
 
     if (!poisoned) {
         // ---- 1. push this rank's slices of the other ranks' chunks ---------------------------------------------
-        for (int64_t seg = block; seg < segs && !p.pushed; seg += blocks) {
-            const int64_t v0 = seg * p.seg_vecs;
-            const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
-            for (int v = tid; v < n; v += kArThreads) {
-                uint4 mine[NVK_TP_MAX_RANKS];
+        if (FUSED) {
+            // work items = (other rank, row of its chunk), strided over all blocks: with many ranks a chunk has fewer rows than
+            // the launch has blocks, and the pushes are what the wire time is made of
+            const int64_t items = static_cast<int64_t>(p.world - 1) * segs;
+            for (int64_t item = block; item < items && !p.pushed; item += blocks) {
+                const int o = static_cast<int>(item / segs);
+                const int r = o < p.rank ? o : o + 1;
+                const int64_t v0 = (item - o * segs) * p.seg_vecs;
+                uint4 mine[kMaxVecs];
 #pragma unroll
-                for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
-                    if (r < p.world && r != p.rank) mine[r] = in[r * p.chunk_vecs + v0 + v];
+                for (int u = 0; u < kMaxVecs; ++u)
+                    if (tid + u * kArThreads < seg_len) mine[u] = in[r * p.chunk_vecs + v0 + tid + u * kArThreads];
 #pragma unroll
-                for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
-                    if (r < p.world && r != p.rank) st_tagged(p.stage[r] + 2 * (p.rank * p.chunk_vecs + v0 + v), mine[r], epoch);
+                for (int u = 0; u < kMaxVecs; ++u)
+                    if (tid + u * kArThreads < seg_len)
+                        st_tagged(p.stage[r] + 2 * (p.rank * p.chunk_vecs + v0 + tid + u * kArThreads), mine[u], epoch);
+            }
+        } else {
+            for (int64_t seg = block; seg < segs && !p.pushed; seg += blocks) {
+                const int64_t v0 = seg * p.seg_vecs;
+                const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
+                for (int v = tid; v < n; v += kArThreads) {
+                    uint4 mine[NVK_TP_MAX_RANKS];
+#pragma unroll
+                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
+                        if (r < p.world && r != p.rank) mine[r] = in[r * p.chunk_vecs + v0 + v];
+#pragma unroll
+                    for (int r = 0; r < NVK_TP_MAX_RANKS; ++r)
+                        if (r < p.world && r != p.rank) st_tagged(p.stage[r] + 2 * (p.rank * p.chunk_vecs + v0 + v), mine[r], epoch);
+                }
             }
         }
         // ---- 2. reduce this rank's chunk, 3. push the results ---------------------------------------------------
@@ -251,12 +272,14 @@ __device__ __forceinline__ void allreduce_body(const ArParams& p, int block, int
         // ---- 4. gather the other chunks' results ---------------------------------------------------------------
         const uint4* stage_b = p.stage[p.rank] + 2 * p.region_b;
         const Waiter waiter_b{p, &s_gave_up, 2};
-        for (int64_t seg = block; seg < segs; seg += blocks) {
-            const int64_t v0 = seg * p.seg_vecs;
-            const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
-            if (FUSED) {
-                for (int s = 0; s < p.world; ++s) {
-                    if (s == p.rank) continue;
+        if (FUSED) {
+            const int64_t items = static_cast<int64_t>(p.world - 1) * segs;   // (other rank, row of its chunk), as in the push
+            for (int64_t item = block; item < items; item += blocks) {
+                const int o = static_cast<int>(item / segs);
+                const int s = o < p.rank ? o : o + 1;
+                const int64_t v0 = (item - o * segs) * p.seg_vecs;
+                const int n = seg_len;
+                {
                     const int64_t base = s * p.chunk_vecs + v0;
                     uint4 h[kMaxVecs];
                     {
@@ -273,7 +296,11 @@ __device__ __forceinline__ void allreduce_body(const ArParams& p, int block, int
                     }
                     norm_row<T>(p, h, n, base, s_scratch);
                 }
-            } else {
+            }
+        } else {
+            for (int64_t seg = block; seg < segs; seg += blocks) {
+                const int64_t v0 = seg * p.seg_vecs;
+                const int n = static_cast<int>(min(static_cast<int64_t>(seg_len), p.chunk_vecs - v0));
                 for (int v = tid; v < n; v += kArThreads) {
                     const uint4* slot[NVK_TP_MAX_RANKS];
                     uint4 got[NVK_TP_MAX_RANKS];
@@ -332,7 +359,9 @@ Plan plan_fused(int rows, int cols, int world) {
     Plan pl{};
     pl.seg_vecs = cols / 8;
     pl.chunk_vecs = static_cast<int64_t>(rows / world) * pl.seg_vecs;
-    pl.blocks = rows / world < kArBlocks ? rows / world : kArBlocks;
+    // one block per row of the own chunk for the reduction; more, up to one per (other rank, row), for the pushes and the gather
+    const int64_t items = static_cast<int64_t>(world - 1) * (rows / world);
+    pl.blocks = static_cast<int>(items < kArBlocks ? items : kArBlocks);
     return pl;
 }
 
@@ -349,7 +378,7 @@ int check_common(const char* what, void* const* stage_ptrs, const void* flags, i
                     nvk_tp_allreduce_stage_bytes(count), static_cast<long long>(count));
     for (int r = 0; r < world; ++r) {
         if (!stage_ptrs[r]) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: null staging area of rank %d", what, r);
-        if (!aligned_to(stage_ptrs[r], 16)) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: staging areas must be 16-byte aligned", what);
+        if (!aligned_to(stage_ptrs[r], 32)) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: staging areas must be 32-byte aligned", what);
     }
     if (!aligned_to(flags, 16)) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: the flag area must be 16-byte aligned", what);
     return NVK_OK;
