@@ -496,8 +496,9 @@ def main():
     ap.add_argument("--e2e-kv", default="bf16", choices=["bf16", "int8"], help="e2e workload: KV cache format")
     ap.add_argument("--e2e-linears", default="cublas", choices=["cublas", "fused"],
                     help="e2e workload: decode-step QKV / o_proj / down_proj as cuBLAS GEMMs + kernels, or this library's fused GEMMs")
-    ap.add_argument("--e2e-allreduce", default="peer", choices=["nccl", "peer"],
-                    help="e2e workload, N > 1: all-reduce of the decode steps through NCCL or the peer-memory kernel")
+    ap.add_argument("--e2e-allreduce", default="auto", choices=["auto", "nccl", "peer", "multimem"],
+                    help="e2e workload, N > 1: all-reduce of the decode steps through NCCL, the peer-memory kernel or the in-switch "
+                         "(multimem) kernel; auto = multimem from 8 ranks on (its time does not grow with the ranks), else peer")
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
                     help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")
     ap.add_argument("--layers", type=int, default=36, help="mixed workload: layer caches per step")

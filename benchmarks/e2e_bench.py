@@ -19,7 +19,7 @@ RING = 64   # pinned metadata slots in flight
 
 
 def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None, num_seqs=256, len_lo=100, len_hi=1024,
-            seed=0, use_graph=True, kv_dtype="bf16", allreduce="peer", linears="cublas"):
+            seed=0, use_graph=True, kv_dtype="bf16", allreduce="auto", linears="cublas"):
     cfg = cfg or DecoderConfig()
     bs = cfg.block_size
     prompts, output_lens = make_requests(num_seqs, cfg.vocab, len_lo, len_hi, seed)
@@ -28,9 +28,34 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
     num_blocks = blocks_needed(prompt_lens, output_lens, bs) + 8
     t0 = time.time()
     comm = None
-    if allreduce == "peer" and world > 1:
-        from .tp_comm import PeerAllReduce
-        comm = PeerAllReduce(nvk, torch, dist, dev, rank, world, num_seqs * cfg.hidden, torch.bfloat16)
+    allreduce_kind = "NCCL"
+    if allreduce == "auto":
+        # measured per 2 MiB message, fused form: tagged-word kernel 12.2 / 16.7 us at 2 / 4 ranks and growing with the
+        # bytes it sends to every peer; in-switch kernel 17.6 / 17.6 us
+        allreduce = "multimem" if world >= 8 else "peer"
+    if allreduce in ("peer", "multimem") and world > 1:
+        from .tp_comm import MulticastAllReduce, PeerAllReduce
+        if allreduce == "multimem":
+            # every rank must take the same path: the ranks agree on whether the multicast object could be made
+            try:
+                comm = MulticastAllReduce(nvk, torch, dist, dev, rank, world, num_seqs * cfg.hidden, torch.bfloat16)
+                made = 1
+            except Exception as exc:   # no multicast support on this box: the peer-memory kernel instead
+                comm, made = None, 0
+                if rank == 0:
+                    print(f"# multimem all-reduce unavailable ({type(exc).__name__}: {exc}); using the peer-memory kernel", flush=True)
+            agree = torch.tensor([made], device=dev)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            if int(agree.item()) == 0 and comm is not None:
+                comm.close()
+                comm = None
+            if comm is not None:
+                allreduce_kind = ("decode steps: in-switch reduction and broadcast (multimem.ld_reduce / multimem.st) fused with the residual "
+                                  "add and the RMSNorm (nvk_tp_allreduce_add_rmsnorm_multimem); prefill steps: NCCL")
+        if comm is None:
+            comm = PeerAllReduce(nvk, torch, dist, dev, rank, world, num_seqs * cfg.hidden, torch.bfloat16)
+            allreduce_kind = ("decode steps: peer-memory all-reduce fused with the residual add and the RMSNorm "
+                              "(nvk_tp_allreduce_add_rmsnorm); prefill steps: NCCL")
     model = Decoder(nvk, torch, dev, cfg, rank, world, dist, num_blocks=num_blocks, seed=seed, kv_dtype=kv_dtype, peer_comm=comm,
                     linears=linears)
     torch.cuda.synchronize()
@@ -152,8 +177,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
                                f"prompt and output lengths U[{len_lo},{len_hi}], greedy, ignore_eos",
                    "parallelism": f"tp{world} (KV-head shards, all-reduce after o_proj / down_proj)",
                    "kv_cache": "int8 with fp16 per-(token, head) scales" if model.int8 else "bf16",
-                   "allreduce": ("decode steps: peer-memory all-reduce fused with the residual add and the RMSNorm "
-                                 "(nvk_tp_allreduce_add_rmsnorm); prefill steps: NCCL" if comm is not None else "NCCL"),
+                   "allreduce": allreduce_kind,
                    "linears": ("decode steps: QKV projection with split + norm + RoPE + cache store in its epilogue "
                                "(nvk_qkv_linear_norm_rope_store)" + ("; o_proj / down_proj push their partial sums into the all-reduce "
                                "from their epilogue (nvk_tp_row_linear_allreduce_add_rmsnorm)" if comm is not None else "") +

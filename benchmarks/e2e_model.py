@@ -123,7 +123,8 @@ class Decoder:
         comm = self.peer_comm
         if (comm is not None and n * cols <= comm.max_elems and n % self.world == 0 and cols % 8 == 0 and cols <= 8192
                 and h.is_contiguous()):
-            if self.fused_linears and n <= self.fused_rows_max and cols % 128 == 0 and a.is_contiguous():
+            if (self.fused_linears and n <= self.fused_rows_max and cols % 128 == 0 and a.is_contiguous()
+                    and hasattr(comm, "row_linear_all_reduce_add_rmsnorm")):
                 return comm.row_linear_all_reduce_add_rmsnorm(a, w, h, norm_w, self.cfg.eps)
             addend, _ = comm.buffers(n, cols)
             self.torch.matmul(a, w.t(), out=addend)

@@ -143,6 +143,95 @@ class PeerAllReduce:
         self._own = {}
 
 
+class MulticastAllReduce:
+    """The all-reduce through the NVSwitch (``nvk_tp_allreduce_multimem`` / ``nvk_tp_allreduce_add_rmsnorm_multimem``).  Addend,
+    result and norm buffers and the signal area are carved out of one symmetric allocation made with torch's symmetric
+    memory (which creates the NVLink multicast object and binds every rank's part to it); the flag area is private.
+    Same ``buffers`` / ``all_reduce`` / ``all_reduce_add_rmsnorm`` / ``status`` / ``close`` surface as ``PeerAllReduce``.
+    Raises ``RuntimeError`` when the group has no multicast support."""
+
+    def __init__(self, nvk, torch, dist, dev, rank: int, world: int, max_elems: int, dtype):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.nvk, self.torch, self.dist, self.dev = nvk, torch, dist, dev
+        self.rank, self.world, self.max_elems, self.dtype = rank, world, int(max_elems), dtype
+        lib = nvk.lib()
+        declare(lib)
+        lib.nvk_tp_allreduce_signal_bytes.restype = ctypes.c_size_t
+        esize = torch.empty((), dtype=dtype).element_size()
+        part = (self.max_elems * esize + 4095) // 4096 * 4096
+        signal_bytes = (int(lib.nvk_tp_allreduce_signal_bytes()) + 4095) // 4096 * 4096
+        total = 3 * part + signal_bytes
+        group = dist.group.WORLD
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:   # newer torch enables every group by itself
+            pass
+        self._buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self._buf.zero_()
+        torch.cuda.synchronize()
+        self._hdl = symm_mem.rendezvous(self._buf, group.group_name)
+        mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0)
+        if mc == 0:
+            raise RuntimeError("this process group has no NVLink multicast support")
+        peers = [int(x) for x in self._hdl.buffer_ptrs]
+        self._mc_in, self._mc_out, self._mc_norm = mc, mc + part, mc + 2 * part
+        self._signal_tab = (ctypes.c_void_p * world)(*[x + 3 * part for x in peers])
+        view = lambda k: self._buf[k * part: k * part + self.max_elems * esize].view(dtype)  # noqa: E731
+        self.addend, self.result, self.normed = view(0), view(1), view(2)
+        self._flag_t = torch.zeros(64, device=dev, dtype=torch.int32)
+        self._flags = ctypes.c_void_p(self._flag_t.data_ptr())
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    def buffers(self, rows: int, cols: int):
+        n = rows * cols
+        if n > self.max_elems:
+            raise ValueError("message larger than the symmetric buffers")
+        return self.addend[:n].view(rows, cols), self.result[:n].view(rows, cols)
+
+    def all_reduce(self, count: int, cols: int = 0) -> None:
+        """Sums the first ``count`` elements of every rank's addend buffer into every rank's result buffer."""
+        nvk, torch = self.nvk, self.torch
+        cols = cols or min(count // self.world, 4096)
+        rows = count // cols
+        if rows * cols != count or rows % self.world or cols % 8 or count > self.max_elems:
+            raise ValueError("count must split into rows % world == 0 of cols % 8 == 0 elements")
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nvk._check(nvk.lib().nvk_tp_allreduce_multimem(
+            ctypes.c_void_p(self._mc_in), ctypes.c_void_p(self._mc_out), self._signal_tab, self._flags, ctypes.c_int(self.rank),
+            ctypes.c_int(self.world), ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(nvk._dtype_code(self.addend)), stream))
+        nvk.launch_count += 1
+
+    def all_reduce_add_rmsnorm(self, residual, weight, eps: float, rows: int, cols: int):
+        nvk, torch = self.nvk, self.torch
+        n = rows * cols
+        if n > self.max_elems or rows % self.world != 0:
+            raise ValueError("rows must be a multiple of world and the message must fit the symmetric buffers")
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        nvk._check(nvk.lib().nvk_tp_allreduce_add_rmsnorm_multimem(
+            ctypes.c_void_p(self._mc_in), ctypes.c_void_p(self._mc_out), ctypes.c_void_p(self._mc_norm), self._signal_tab, self._flags,
+            ctypes.c_void_p(residual.data_ptr()), ctypes.c_void_p(weight.data_ptr()), ctypes.c_float(eps), ctypes.c_int(self.rank),
+            ctypes.c_int(self.world), ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(nvk._dtype_code(self.addend)), stream))
+        nvk.launch_count += 1
+        return self.result[:n].view(rows, cols), self.normed[:n].view(rows, cols)
+
+    def status(self) -> int:
+        out = ctypes.c_int(0)
+        stream = ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+        self.nvk._check(self.nvk.lib().nvk_tp_allreduce_status(self._flags, stream, ctypes.byref(out)))
+        return int(out.value)
+
+    def close(self) -> None:
+        # every rank stops launching before any rank lets go of the symmetric allocation
+        self.torch.cuda.synchronize()
+        self.dist.barrier()
+        self.addend = self.result = self.normed = None
+        self._hdl = None
+        self._buf = None
+        self.torch.cuda.synchronize()
+        self.dist.barrier()
+
+
 class InProcessAllReduce:
     """``world`` ranks on ONE device (``nvk_tp_allreduce_inprocess``): a buffer set per rank, one cooperative launch per
     collective.  The counterpart of the reference's in-process communicator (src/utils/tensor_parallel.cpp:165-277)."""

@@ -178,8 +178,8 @@ int nvk_decode_attention_paged_static(const void* query, const void* k_cache, co
  * One process per GPU.  Every rank owns a STAGING area of at least nvk_tp_allreduce_stage_bytes(largest count) bytes
  * and a FLAG area of nvk_tp_allreduce_flag_bytes() bytes, both zeroed once.  The staging areas are mapped into every
  * process (cudaIpc* or equivalent; plain peer mappings, no multicast); stage_ptrs is a HOST array of `world` device
- * pointers as mapped in the calling process, index = rank, and stage_bytes the size every one of them has (the same
- * on all ranks).  The addend `in`, the result `out` and the flag area are ordinary device memory of the calling
+ * pointers as mapped in the calling process (32-byte aligned), index = rank, and stage_bytes the size every one of them
+ * has (the same on all ranks).  The addend `in`, the result `out` and the flag area are ordinary device memory of the calling
  * rank: peers never access them, so a GEMM may write `in` and read `out` in place.  Every rank calls with the same
  * count (a multiple of 8 * world elements) in the same order; the result, identical on all ranks, is in `out` when the
  * launch completes.  The launch may be captured in a CUDA graph.
@@ -213,6 +213,30 @@ int nvk_tp_allreduce_reset(void* flags, void* stream);
 int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes,
                                  void* flags, const void* residual, const void* weight, float eps, int rank, int world,
                                  int rows, int cols, int dtype, void* stream);
+/*
+ * The same two operations through the NVSwitch (multimem.ld_reduce / multimem.st on an NVLink multicast object): a rank
+ * pulls the sum of its rows / world rows from the switch and stores the result rows once, the switch copying them to every
+ * rank, so the bytes on a rank's links do not grow with the number of ranks.  No counterpart in the reference (it calls
+ * ncclAllReduce, src/utils/tensor_parallel.cpp:331-353).
+ *
+ * mc_in, mc_out and mc_norm are MULTICAST addresses: the buffers lie at the same offset in every rank's part of one
+ * symmetric allocation bound to a multicast object (cuMulticastCreate / cuMulticastBindMem, or a library that does it);
+ * every rank writes its addend through its ordinary mapping of that memory before the call and reads result and norm rows
+ * through it afterwards.  signal_ptrs is a HOST array of `world` device pointers: every rank's signal area of
+ * nvk_tp_allreduce_signal_bytes() bytes (plain peer mappings, zeroed once), index = rank.  flags is a private flag area
+ * as above (nvk_tp_allreduce_flag_bytes, nvk_tp_allreduce_status, nvk_tp_allreduce_reset; a reset also needs the signal areas
+ * zeroed); residual and weight are the caller's own memory.  rows a multiple of world, cols a multiple of 8, at most 8192.
+ * Sums are accumulated in fp32 inside the switch in an order the hardware chooses and rounded once to the 16-bit type, so
+ * results agree with the other entry points to within one unit of that type, and are identical on all ranks.
+ * Every wait is bounded and the error word sticky, as above.  A process must not exit while its peers still run launches
+ * on the multicast object.
+ */
+size_t nvk_tp_allreduce_signal_bytes(void);
+int nvk_tp_allreduce_multimem(const void* mc_in, void* mc_out, void* const* signal_ptrs, void* flags, int rank, int world,
+                              int rows, int cols, int dtype, void* stream);
+int nvk_tp_allreduce_add_rmsnorm_multimem(const void* mc_in, void* mc_out, void* mc_norm, void* const* signal_ptrs, void* flags,
+                                          const void* residual, const void* weight, float eps, int rank, int world, int rows,
+                                          int cols, int dtype, void* stream);
 /*
  * All `world` ranks of either form on ONE device in one cooperative launch: in_ptrs / out_ptrs / stage_ptrs /
  * flag_ptrs (and, for the fused form, norm_ptrs / residual_ptrs; pass norm_ptrs == NULL for the plain sum) are host

@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "nvk_prefill_status", "nvk_decode_attention_static_scratch_bytes", "nvk_attention_mixed_step",
     "nvk_linear", "nvk_qkv_linear_norm_rope_store", "nvk_tp_row_linear_allreduce_add_rmsnorm",
     "nvk_tp_row_linear_allreduce_add_rmsnorm_inprocess", "nvk_gemm_status",
+    "nvk_tp_allreduce_signal_bytes", "nvk_tp_allreduce_multimem", "nvk_tp_allreduce_add_rmsnorm_multimem",
 )
 
 _lib = None

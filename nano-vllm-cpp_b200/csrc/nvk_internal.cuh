@@ -103,6 +103,7 @@ int decode_plan(const DecodeArgs& a, dec::DecodeParams* out);
 int launch_decode_merge(const dec::DecodeParams& p, int64_t batch, int dtype, cudaStream_t stream);
 // Fused all-reduce launchers (tp_allreduce.cu); `pushed`: the other ranks' slices were already pushed by the GEMM
 // that produced the addend (gemm_fused.cu), the kernel starts with the reduction.
+void set_multimem_wait_cycles(long long cycles);   // tp_allreduce_mm.cu: the wait limit of the multimem kernels
 int launch_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* const* stage_ptrs, size_t stage_bytes, void* flags,
                                  const void* residual, const void* weight, float eps, int rank, int world, int rows, int cols,
                                  int dtype, bool pushed, cudaStream_t stream);

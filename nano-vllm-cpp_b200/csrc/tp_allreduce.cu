@@ -425,6 +425,7 @@ extern "C" size_t nvk_tp_allreduce_stage_bytes(int64_t max_count) {
 extern "C" void nvk_tp_allreduce_set_wait_limit_ms(int ms) {
     if (ms < 1) ms = 1;
     nvk::g_wait_cycles.store(static_cast<long long>(ms) * 2000000LL, std::memory_order_relaxed);   // cycles at 2 GHz
+    nvk::set_multimem_wait_cycles(static_cast<long long>(ms) * 2000000LL);
 }
 
 extern "C" int nvk_tp_allreduce(const void* in, void* out, void* const* stage_ptrs, size_t stage_bytes, void* flags, int rank,

@@ -8,7 +8,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("peer", ["0", "1", "2"])
+@pytest.mark.parametrize("peer", ["0", "1", "2", "3"])
 def test_kv_head_sharded_decoder_matches_single_gpu(peer):
     import torch
     if torch.cuda.device_count() < 2:

@@ -274,6 +274,53 @@ def main():
         print(f"timing world {world}: peer-memory all-reduce {us_peer:.2f} us, NCCL {us_nccl:.2f} us per 2 MiB message (in a graph)", flush=True)
         print(f"timing world {world}: fused all-reduce + add + rmsnorm {us_fused:.2f} us, NCCL + add + rms_norm {us_unfused:.2f} us", flush=True)
     comm.close()
+
+    # the same two operations through the switch (multimem), where the group has a multicast object
+    mm = None
+    try:
+        mm = tc.MulticastAllReduce(nvk, torch, dist, dev, rank, world, rows * cols, torch.bfloat16)
+        made = 1
+    except Exception as exc:
+        made = 0
+        if rank == 0:
+            print(f"multimem: unavailable ({type(exc).__name__}: {exc})", flush=True)
+    agree = torch.tensor([made], device=dev)
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+    if int(agree.item()) == 1:
+        mm_addend, mm_result = mm.buffers(rows, cols)
+        res_mm = residual.clone()
+        for it in range(3):
+            mm_addend.copy_((0.5 * torch.randn((rows, cols), generator=gen, device=dev)).to(torch.bfloat16))
+            want = mm_addend.clone()
+            dist.all_reduce(want)
+            mm.all_reduce(rows * cols, cols)
+            torch.cuda.synchronize()
+            err = float((mm_result.float() - want.float()).abs().max())
+            tol = 2.0 ** -7 * float(want.float().abs().max())
+            want_h = res_mm + want
+            want_x = torch.nn.functional.rms_norm(want_h, (cols,), weight, 1e-6)
+            h_mm, x_mm = mm.all_reduce_add_rmsnorm(res_mm, weight, 1e-6, rows, cols)
+            torch.cuda.synchronize()
+            eh = float((h_mm.float() - want_h.float()).abs().max())
+            ex = float((x_mm.float() - want_x.float()).abs().max())
+            tol_h = 2.0 ** -7 * float(want_h.float().abs().max())
+            tol_x = 2.0 ** -6 * float(want_x.float().abs().max())
+            got = torch.cat([h_mm.reshape(-1), x_mm.reshape(-1)]).clone()
+            gathered = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(gathered, got)
+            same = all(bool(torch.equal(g, got)) for g in gathered)
+            if rank == 0:
+                print(f"multimem {it}: max |sum - nccl| = {err:.4e} (allowed {tol:.4e}), max |h - ref| = {eh:.4e} (allowed {tol_h:.4e}), "
+                      f"max |x - ref| = {ex:.4e} (allowed {tol_x:.4e}), identical on all ranks: {same}", flush=True)
+            ok = ok and err <= tol and eh <= tol_h and ex <= tol_x and same
+        us_mm = timed(lambda: mm.all_reduce(rows * cols, cols))
+        us_mm_fused = timed(lambda: mm.all_reduce_add_rmsnorm(res_mm, weight, 1e-6, rows, cols))
+        st = mm.status()
+        ok = ok and st == 0
+        if rank == 0:
+            print(f"timing world {world}: multimem all-reduce {us_mm:.2f} us, multimem all-reduce + add + rmsnorm {us_mm_fused:.2f} us (status {st})", flush=True)
+    if mm is not None:
+        mm.close()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

@@ -47,6 +47,22 @@ def main():
 
     comm = None
     mode = os.environ.get("TP_CHECK_PEER", "0")   # 1: decode-step all-reduces through the peer-memory kernel; 2: and the fused linears
+    if mode == "3":   # decode-step all-reduces through the switch (multimem), where the group has a multicast object
+        tc = importlib.import_module("benchmarks.tp_comm")
+        try:
+            comm, made = tc.MulticastAllReduce(nvk, torch, dist, dev, rank, world, 8 * cfg.hidden, torch.bfloat16), 1
+        except Exception as exc:
+            comm, made = None, 0
+            print(f"rank {rank}: multimem unavailable ({type(exc).__name__}: {exc})", flush=True)
+        agree = torch.tensor([made], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            if comm is not None:
+                comm.close()
+            if rank == 0:
+                print("step 0: skipped, no multicast support\nstep 1: skipped\nstep 2: skipped", flush=True)
+            dist.destroy_process_group()
+            return 0
     if mode in ("1", "2"):
         tc = importlib.import_module("benchmarks.tp_comm")
         comm = tc.PeerAllReduce(nvk, torch, dist, dev, rank, world, 8 * cfg.hidden, torch.bfloat16)
