@@ -125,8 +125,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) fused_prologue_kernel(
             const bool valid = head < heads;          // lanes without a head still take part in the shuffles
             const bool is_q = head < p.hq;
             const bool is_k = !is_q && head < p.hq + p.hkv;
-            uint4 out_lo, out_hi;
-            {                                         // every lane runs the arithmetic (the shuffles need the whole warp)
+            uint4 out_lo = lo[s], out_hi = hi[s];     // v heads (and lanes without a head): the loaded values as they are
+            // every lane of a warp that has a q or k head runs the arithmetic (the shuffles need the whole warp); a warp
+            // whose heads of this step are all v heads skips it
+            if (__any_sync(0xffffffffu, valid && (is_q || is_k))) {
                 float inv_rms = 1.0f;
                 if (normed) {
                     F2 sq = f2_make(0.0f, 0.0f);
@@ -169,11 +171,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) fused_prologue_kernel(
                         r_hi[i] = f2_pack<T>(b);
                     }
                 }
-                out_lo = make_uint4(r_lo[0], r_lo[1], r_lo[2], r_lo[3]);
-                out_hi = make_uint4(r_hi[0], r_hi[1], r_hi[2], r_hi[3]);
+                if (is_q || is_k) {
+                    out_lo = make_uint4(r_lo[0], r_lo[1], r_lo[2], r_lo[3]);
+                    out_hi = make_uint4(r_hi[0], r_hi[1], r_hi[2], r_hi[3]);
+                }
             }
             if (!valid) continue;
-            if (!is_q && !is_k) { out_lo = lo[s]; out_hi = hi[s]; }   // v heads: plain copy
             T* dst;
             if (is_q) {
                 dst = static_cast<T*>(p.q_out) + (row * p.hq + head) * D;
