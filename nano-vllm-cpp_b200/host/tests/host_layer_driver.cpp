@@ -16,7 +16,7 @@
 //               -> out_decode_graph.bin, k_cache_decode_graph.bin
 //   4. the decode step once more through the UNFUSED route (split_norm_rope + Attention::forward, i.e. store_kvcache +
 //      decode), as the reference runs it for fp32 models -> out_decode_unfused.bin, k_cache_decode_unfused.bin
-// Exit code 0 when every step ran; the numbers are judged by the caller.
+// Exit code 0 when every step ran; the numbers are checked by the caller.
 #include "kernels/attention.h"
 #include "layers/attention.h"
 #include "models/transformer_attention.h"
