@@ -174,7 +174,7 @@ class MulticastAllReduce:
         if mc == 0:
             raise RuntimeError("this process group has no NVLink multicast support")
         peers = [int(x) for x in self._hdl.buffer_ptrs]
-        self._mc_in, self._mc_out, self._mc_norm = mc, mc + part, mc + 2 * part
+        self._mc_in, self._mc_out = mc, mc + part
         self._signal_tab = (ctypes.c_void_p * world)(*[x + 3 * part for x in peers])
         view = lambda k: self._buf[k * part: k * part + self.max_elems * esize].view(dtype)  # noqa: E731
         self.addend, self.result, self.normed = view(0), view(1), view(2)
@@ -209,7 +209,8 @@ class MulticastAllReduce:
             raise ValueError("rows must be a multiple of world and the message must fit the symmetric buffers")
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         nvk._check(nvk.lib().nvk_tp_allreduce_add_rmsnorm_multimem(
-            ctypes.c_void_p(self._mc_in), ctypes.c_void_p(self._mc_out), ctypes.c_void_p(self._mc_norm), self._signal_tab, self._flags,
+            ctypes.c_void_p(self._mc_in), ctypes.c_void_p(self._mc_out), ctypes.c_void_p(self.result.data_ptr()),
+            ctypes.c_void_p(self.normed.data_ptr()), self._signal_tab, self._flags,
             ctypes.c_void_p(residual.data_ptr()), ctypes.c_void_p(weight.data_ptr()), ctypes.c_float(eps), ctypes.c_int(self.rank),
             ctypes.c_int(self.world), ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(nvk._dtype_code(self.addend)), stream))
         nvk.launch_count += 1

@@ -219,10 +219,12 @@ int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* co
  * rank, so the bytes on a rank's links do not grow with the number of ranks.  No counterpart in the reference (it calls
  * ncclAllReduce, src/utils/tensor_parallel.cpp:331-353).
  *
- * mc_in, mc_out and mc_norm are MULTICAST addresses: the buffers lie at the same offset in every rank's part of one
+ * mc_in and mc_out are MULTICAST addresses of the addend and the result: the buffers lie at the same offset in every rank's part of one
  * symmetric allocation bound to a multicast object (cuMulticastCreate / cuMulticastBindMem, or a library that does it);
- * every rank writes its addend through its ordinary mapping of that memory before the call and reads result and norm rows
- * through it afterwards.  signal_ptrs is a HOST array of `world` device pointers: every rank's signal area of
+ * every rank writes its addend through its ordinary mapping of that memory before the call and reads the result rows
+ * through it afterwards.  In the fused form `out` is that ordinary mapping of the result buffer (the kernel reads the rows
+ * its peers broadcast from it; only result rows cross the wire) and `norm` [rows, cols] ordinary memory of the calling rank
+ * that receives the RMSNorm of every row.  signal_ptrs is a HOST array of `world` device pointers: every rank's signal area of
  * nvk_tp_allreduce_signal_bytes() bytes (plain peer mappings, zeroed once), index = rank.  flags is a private flag area
  * as above (nvk_tp_allreduce_flag_bytes, nvk_tp_allreduce_status, nvk_tp_allreduce_reset; a reset also needs the signal areas
  * zeroed); residual and weight are the caller's own memory.  rows a multiple of world, cols a multiple of 8, at most 8192.
@@ -234,7 +236,7 @@ int nvk_tp_allreduce_add_rmsnorm(const void* in, void* out, void* norm, void* co
 size_t nvk_tp_allreduce_signal_bytes(void);
 int nvk_tp_allreduce_multimem(const void* mc_in, void* mc_out, void* const* signal_ptrs, void* flags, int rank, int world,
                               int rows, int cols, int dtype, void* stream);
-int nvk_tp_allreduce_add_rmsnorm_multimem(const void* mc_in, void* mc_out, void* mc_norm, void* const* signal_ptrs, void* flags,
+int nvk_tp_allreduce_add_rmsnorm_multimem(const void* mc_in, void* mc_out, const void* out, void* norm, void* const* signal_ptrs, void* flags,
                                           const void* residual, const void* weight, float eps, int rank, int world, int rows,
                                           int cols, int dtype, void* stream);
 /*

@@ -8,16 +8,18 @@
 // its rows from the switch (it receives rows / world reduced rows, each peer sends its slice once) and stores the
 // result once, the switch copying it to all ranks: 2 MiB in and 2 MiB out per rank whatever the world size.
 //
-// Buffers: addend, result and (fused form) norm buffers live at the same offset in every rank's part of one symmetric
+// Buffers: addend and result buffers live at the same offset in every rank's part of one symmetric
 // allocation that is bound to a multicast object; the caller passes their MULTICAST addresses.  Every rank also owns a
 // signal area (plain peer mapping, zeroed once) and a private flag area as in tp_allreduce.cu.  One launch:
 //   1. barrier: block b tells block b of every peer "my addend is complete" (it was written by the kernel before this
 //      one) and waits for theirs -- one word per (block, peer), valued with the launch's epoch;
 //   2. the block pulls its rows' sums (fp32 accumulation in the switch, rounded once to the 16-bit type), adds the
-//      residual and computes the RMSNorm (fused form), and stores result (and norm) rows through the multicast address;
-//   3. a system-scope fence, then the same barrier on a second set of words: when a block has heard from block b of every
-//      peer, their rows are in this rank's memory.  Rows are assigned to blocks identically on all ranks, so after the
-//      barriers of all blocks the whole result is local.
+//      residual (fused form) and stores the result rows through the multicast address;
+//   3. a system-scope fence, then a second set of words says "block b's rows are stored" to every peer.  Plain form: the
+//      block waits for the same word of every peer, so after the barriers of all blocks the whole result is local.
+//      Fused form: nobody waits there; the rows of the peers' chunks are dealt out over all blocks of the (larger) grid,
+//      each of which waits for the word of a row's block, reads the row from this rank's own copy of the result and
+//      writes its RMSNorm -- so only result rows cross the wire, and every row has been awaited when the launch ends.
 // Every wait is bounded and the error word is sticky, as in tp_allreduce.cu (same flag area layout, same status and
 // reset calls).  A rank must not exit while its peers still run launches: its memory is bound to the multicast object.
 #include "nvk_internal.cuh"
@@ -34,7 +36,8 @@ constexpr int kMmMaxVecs = 4;             // 16-byte vectors of a row per thread
 std::atomic<long long> g_mm_wait_cycles{20000000000LL};
 
 struct MmParams {
-    const void* mc_in; void* mc_out; void* mc_norm;      // multicast addresses
+    const void* mc_in; void* mc_out;                     // multicast addresses
+    const void* out_local; void* norm;                   // fused form: this rank's own mapping of the result buffer, its norm buffer
     const void* residual; const void* weight;            // this rank's own memory
     uint32_t* signal[NVK_TP_MAX_RANKS];                  // every rank's signal area as mapped here (index = rank)
     uint32_t* flags;                                     // private: [0] epoch of the last launch, [1] blocks finished, [2] error
@@ -111,6 +114,40 @@ __device__ __forceinline__ float mm_block_sum(float v, float* scratch) {
     return total;
 }
 
+// x = h * rsqrt(mean(h^2) + eps) * weight for this thread's vectors of one row (h as rounded to T), stored to this
+// rank's own norm buffer.
+template <typename T>
+__device__ __forceinline__ void mm_norm_row(const MmParams& p, const uint4 (&h)[kMmMaxVecs], int row_vecs, int64_t base, float* scratch) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kMmMaxVecs; ++u) {
+        if (static_cast<int>(threadIdx.x) + u * kMmThreads < row_vecs) {
+            const T* e = reinterpret_cast<const T*>(&h[u]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { const float f = ElemTraits<T>::to_float(e[i]); ss += f * f; }
+        }
+    }
+    const float inv_rms = rsqrtf(mm_block_sum(ss, scratch) / static_cast<float>(p.cols) + p.eps);
+#pragma unroll
+    for (int u = 0; u < kMmMaxVecs; ++u) {
+        const int v = static_cast<int>(threadIdx.x) + u * kMmThreads;
+        if (v < row_vecs) {
+            const uint4 wv = __ldg(static_cast<const uint4*>(p.weight) + v);
+            const T* we = reinterpret_cast<const T*>(&wv);
+            const T* e = reinterpret_cast<const T*>(&h[u]);
+            float x[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = ElemTraits<T>::to_float(e[i]) * inv_rms * ElemTraits<T>::to_float(we[i]);
+            uint4 xv;
+            xv.x = ElemTraits<T>::pack2(x[0], x[1]); xv.y = ElemTraits<T>::pack2(x[2], x[3]);
+            xv.z = ElemTraits<T>::pack2(x[4], x[5]); xv.w = ElemTraits<T>::pack2(x[6], x[7]);
+            static_cast<uint4*>(p.norm)[base + v] = xv;
+        }
+    }
+}
+
+// Grid: `reducers` = min(rows / world, kMmBlocks) blocks pull and broadcast the rows of this rank's chunk; in the fused
+// form the grid may be larger, and all of its blocks then normalise the rows that arrive from the peers.
 template <typename T, bool FUSED>
 __global__ void __launch_bounds__(kMmThreads) allreduce_mm_kernel(const MmParams p) {
     __shared__ int s_gave_up;
@@ -125,66 +162,89 @@ __global__ void __launch_bounds__(kMmThreads) allreduce_mm_kernel(const MmParams
     const bool poisoned = *reinterpret_cast<volatile uint32_t*>(p.flags + 2) != 0u;
     const int row_vecs = p.cols / 8;
     const int rows_per_rank = p.rows / p.world;
+    const int reducers = rows_per_rank < kMmBlocks ? rows_per_rank : kMmBlocks;
 
-    if (!poisoned && peer_barrier(p, 0, block, epoch, &s_gave_up, 1)) {
-        // rows of this rank's chunk, strided over the blocks (the same assignment on every rank)
-        for (int r = block; r < rows_per_rank; r += blocks) {
-            const int64_t base = (static_cast<int64_t>(p.rank) * rows_per_rank + r) * row_vecs;
-            uint4 h[kMmMaxVecs];
-            float ss = 0.0f;
+    if (!poisoned) {
+        if (block < reducers) {
+            if (peer_barrier(p, 0, block, epoch, &s_gave_up, 1)) {
+                // rows of this rank's chunk, strided over the reducing blocks (the same assignment on every rank)
+                for (int r = block; r < rows_per_rank; r += reducers) {
+                    const int64_t base = (static_cast<int64_t>(p.rank) * rows_per_rank + r) * row_vecs;
+                    uint4 h[kMmMaxVecs];
 #pragma unroll
-            for (int u = 0; u < kMmMaxVecs; ++u) {
-                const int v = tid + u * kMmThreads;
-                if (v < row_vecs) h[u] = MmOps<T>::ld_reduce(static_cast<const uint4*>(p.mc_in) + base + v);
-            }
-            if (FUSED) {
+                    for (int u = 0; u < kMmMaxVecs; ++u) {
+                        const int v = tid + u * kMmThreads;
+                        if (v < row_vecs) h[u] = MmOps<T>::ld_reduce(static_cast<const uint4*>(p.mc_in) + base + v);
+                    }
+                    if (FUSED) {
 #pragma unroll
-                for (int u = 0; u < kMmMaxVecs; ++u) {
-                    const int v = tid + u * kMmThreads;
-                    if (v < row_vecs) {
-                        const uint4 res = static_cast<const uint4*>(p.residual)[base + v];
-                        const T* a = reinterpret_cast<const T*>(&h[u]);
-                        const T* b = reinterpret_cast<const T*>(&res);
-                        float f[8];
+                        for (int u = 0; u < kMmMaxVecs; ++u) {
+                            const int v = tid + u * kMmThreads;
+                            if (v < row_vecs) {
+                                const uint4 res = static_cast<const uint4*>(p.residual)[base + v];
+                                const T* a = reinterpret_cast<const T*>(&h[u]);
+                                const T* b = reinterpret_cast<const T*>(&res);
+                                float f[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {     // the sum arrives rounded to T; the residual is added in T
-                            f[i] = ElemTraits<T>::to_float(ElemTraits<T>::from_float(ElemTraits<T>::to_float(a[i]) + ElemTraits<T>::to_float(b[i])));
-                            ss += f[i] * f[i];
+                                for (int i = 0; i < 8; ++i)     // the sum arrives rounded to T; the residual is added in T
+                                    f[i] = ElemTraits<T>::to_float(a[i]) + ElemTraits<T>::to_float(b[i]);
+                                h[u].x = ElemTraits<T>::pack2(f[0], f[1]); h[u].y = ElemTraits<T>::pack2(f[2], f[3]);
+                                h[u].z = ElemTraits<T>::pack2(f[4], f[5]); h[u].w = ElemTraits<T>::pack2(f[6], f[7]);
+                            }
                         }
-                        h[u].x = ElemTraits<T>::pack2(f[0], f[1]); h[u].y = ElemTraits<T>::pack2(f[2], f[3]);
-                        h[u].z = ElemTraits<T>::pack2(f[4], f[5]); h[u].w = ElemTraits<T>::pack2(f[6], f[7]);
                     }
+#pragma unroll
+                    for (int u = 0; u < kMmMaxVecs; ++u) {
+                        const int v = tid + u * kMmThreads;
+                        if (v < row_vecs) mc_store(static_cast<uint4*>(p.mc_out) + base + v, h[u]);
+                    }
+                    if (FUSED) mm_norm_row<T>(p, h, row_vecs, base, s_scratch);   // the own rows' norm from registers
                 }
             }
-#pragma unroll
-            for (int u = 0; u < kMmMaxVecs; ++u) {
-                const int v = tid + u * kMmThreads;
-                if (v < row_vecs) mc_store(static_cast<uint4*>(p.mc_out) + base + v, h[u]);
-            }
+            // every store of this block is ordered before the signals: barrier, then a system-scope fence by the signalling threads
+            __syncthreads();
+            if (tid < p.world) __threadfence_system();
             if (FUSED) {
-                const float inv_rms = rsqrtf(mm_block_sum(ss, s_scratch) / static_cast<float>(p.cols) + p.eps);
-#pragma unroll
-                for (int u = 0; u < kMmMaxVecs; ++u) {
-                    const int v = tid + u * kMmThreads;
-                    if (v < row_vecs) {
-                        const uint4 wv = __ldg(static_cast<const uint4*>(p.weight) + v);
-                        const T* we = reinterpret_cast<const T*>(&wv);
-                        const T* e = reinterpret_cast<const T*>(&h[u]);
-                        float x[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) x[i] = ElemTraits<T>::to_float(e[i]) * inv_rms * ElemTraits<T>::to_float(we[i]);
-                        uint4 xv;
-                        xv.x = ElemTraits<T>::pack2(x[0], x[1]); xv.y = ElemTraits<T>::pack2(x[2], x[3]);
-                        xv.z = ElemTraits<T>::pack2(x[4], x[5]); xv.w = ElemTraits<T>::pack2(x[6], x[7]);
-                        mc_store(static_cast<uint4*>(p.mc_norm) + base + v, xv);
-                    }
-                }
+                // tell block `block`'s rows to every peer; nobody waits here: the rows are awaited where they are normalised
+                if (tid < p.world && tid != p.rank && *reinterpret_cast<volatile int*>(&s_gave_up) == 0)
+                    st_signal(p.signal[tid] + signal_index(1, block, p.rank), epoch);
+            } else {
+                peer_barrier(p, 1, block, epoch, &s_gave_up, 2);
             }
         }
-        // every store of this block is ordered before the signals: barrier, then a system-scope fence by the signalling threads
-        __syncthreads();
-        if (tid < p.world) __threadfence_system();
-        peer_barrier(p, 1, block, epoch, &s_gave_up, 2);
+        if (FUSED) {
+            // rows of the peers' chunks, strided over ALL blocks: wait for the row's block on its rank, normalise it from this
+            // rank's own copy of the result (only result rows cross the wire)
+            const int64_t items = static_cast<int64_t>(p.world - 1) * rows_per_rank;
+            for (int64_t item = block; item < items; item += blocks) {
+                const int o = static_cast<int>(item / rows_per_rank);
+                const int src = o < p.rank ? o : o + 1;
+                const int r = static_cast<int>(item - static_cast<int64_t>(o) * rows_per_rank);
+                if (tid == 0) {
+                    const uint32_t* word = p.signal[p.rank] + signal_index(1, r % reducers, src);
+                    long long start = 0;
+                    while (ld_signal(word) != epoch) {
+                        if (*reinterpret_cast<volatile int*>(&s_gave_up)) break;
+                        if (start == 0) start = clock64();
+                        else if (clock64() - start > p.wait_cycles) {
+                            *reinterpret_cast<volatile int*>(&s_gave_up) = 1;
+                            atomicCAS(reinterpret_cast<unsigned int*>(p.flags + 2), 0u, 2u);
+                            break;
+                        }
+                    }
+                }
+                __syncthreads();
+                if (*reinterpret_cast<volatile int*>(&s_gave_up)) break;
+                const int64_t base = (static_cast<int64_t>(src) * rows_per_rank + r) * row_vecs;
+                uint4 h[kMmMaxVecs];
+#pragma unroll
+                for (int u = 0; u < kMmMaxVecs; ++u) {
+                    const int v = tid + u * kMmThreads;
+                    if (v < row_vecs) h[u] = __ldcg(static_cast<const uint4*>(p.out_local) + base + v);
+                }
+                mm_norm_row<T>(p, h, row_vecs, base, s_scratch);
+            }
+        }
     }
 
     __syncthreads();
@@ -198,8 +258,7 @@ __global__ void __launch_bounds__(kMmThreads) allreduce_mm_kernel(const MmParams
     }
 }
 
-
-int launch_mm(const void* mc_in, void* mc_out, void* mc_norm, void* const* signal_ptrs, void* flags, const void* residual,
+int launch_mm(const void* mc_in, void* mc_out, const void* out_local, void* norm, void* const* signal_ptrs, void* flags, const void* residual,
               const void* weight, float eps, int rank, int world, int rows, int cols, int dtype, bool fused, cudaStream_t stream) {
     const char* what = fused ? "tp all-reduce + add + rmsnorm (multimem)" : "tp all-reduce (multimem)";
     if (world < 2 || world > NVK_TP_MAX_RANKS || rank < 0 || rank >= world)
@@ -208,12 +267,12 @@ int launch_mm(const void* mc_in, void* mc_out, void* mc_norm, void* const* signa
     if (rows <= 0 || rows % world != 0) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: rows must be a positive multiple of world", what);
     if (cols <= 0 || cols % 8 != 0 || cols > kMmThreads * kMmMaxVecs * 8)
         return fail(NVK_ERR_UNSUPPORTED, "%s: cols must be a multiple of 8 and at most %d", what, kMmThreads * kMmMaxVecs * 8);
-    if (!mc_in || !mc_out || !signal_ptrs || !flags || (fused && (!mc_norm || !residual || !weight)))
+    if (!mc_in || !mc_out || !signal_ptrs || !flags || (fused && (!out_local || !norm || !residual || !weight)))
         return fail(NVK_ERR_INVALID_ARGUMENT, "%s: every pointer must be defined", what);
-    if (!aligned_to(mc_in, 16) || !aligned_to(mc_out, 16) || (fused && (!aligned_to(mc_norm, 16) || !aligned_to(residual, 16) || !aligned_to(weight, 16))))
+    if (!aligned_to(mc_in, 16) || !aligned_to(mc_out, 16) || (fused && (!aligned_to(out_local, 16) || !aligned_to(norm, 16) || !aligned_to(residual, 16) || !aligned_to(weight, 16))))
         return fail(NVK_ERR_INVALID_ARGUMENT, "%s: buffers must be 16-byte aligned", what);
     MmParams p{};
-    p.mc_in = mc_in; p.mc_out = mc_out; p.mc_norm = mc_norm; p.residual = residual; p.weight = weight;
+    p.mc_in = mc_in; p.mc_out = mc_out; p.out_local = out_local; p.norm = norm; p.residual = residual; p.weight = weight;
     for (int r = 0; r < world; ++r) {
         if (!signal_ptrs[r] || !aligned_to(signal_ptrs[r], 16)) return fail(NVK_ERR_INVALID_ARGUMENT, "%s: signal area of rank %d missing or misaligned", what, r);
         p.signal[r] = static_cast<uint32_t*>(signal_ptrs[r]);
@@ -222,7 +281,11 @@ int launch_mm(const void* mc_in, void* mc_out, void* mc_norm, void* const* signa
     p.wait_cycles = g_mm_wait_cycles.load(std::memory_order_relaxed);
     p.eps = eps; p.rank = rank; p.world = world; p.rows = rows; p.cols = cols;
     const int per_rank = rows / world;
-    const int blocks = per_rank < kMmBlocks ? per_rank : kMmBlocks;
+    int blocks = per_rank < kMmBlocks ? per_rank : kMmBlocks;             // the reducing blocks
+    if (fused) {                                                          // and up to one block per row that arrives
+        const int64_t items = static_cast<int64_t>(world - 1) * per_rank;
+        blocks = static_cast<int>(items < kMmBlocks ? (items > blocks ? items : blocks) : kMmBlocks);
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(blocks));
     cfg.blockDim = dim3(kMmThreads);
@@ -249,13 +312,13 @@ extern "C" size_t nvk_tp_allreduce_signal_bytes(void) { return static_cast<size_
 
 extern "C" int nvk_tp_allreduce_multimem(const void* mc_in, void* mc_out, void* const* signal_ptrs, void* flags, int rank, int world,
                                          int rows, int cols, int dtype, void* stream) {
-    return nvk::launch_mm(mc_in, mc_out, nullptr, signal_ptrs, flags, nullptr, nullptr, 0.0f, rank, world, rows, cols, dtype, false,
+    return nvk::launch_mm(mc_in, mc_out, nullptr, nullptr, signal_ptrs, flags, nullptr, nullptr, 0.0f, rank, world, rows, cols, dtype, false,
                           static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int nvk_tp_allreduce_add_rmsnorm_multimem(const void* mc_in, void* mc_out, void* mc_norm, void* const* signal_ptrs, void* flags,
+extern "C" int nvk_tp_allreduce_add_rmsnorm_multimem(const void* mc_in, void* mc_out, const void* out, void* norm, void* const* signal_ptrs, void* flags,
                                                      const void* residual, const void* weight, float eps, int rank, int world, int rows,
                                                      int cols, int dtype, void* stream) {
-    return nvk::launch_mm(mc_in, mc_out, mc_norm, signal_ptrs, flags, residual, weight, eps, rank, world, rows, cols, dtype, true,
+    return nvk::launch_mm(mc_in, mc_out, out, norm, signal_ptrs, flags, residual, weight, eps, rank, world, rows, cols, dtype, true,
                           static_cast<cudaStream_t>(stream));
 }
