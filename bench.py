@@ -498,7 +498,7 @@ def main():
                     help="e2e workload: decode-step QKV / o_proj / down_proj as cuBLAS GEMMs + kernels, or this library's fused GEMMs")
     ap.add_argument("--e2e-allreduce", default="auto", choices=["auto", "nccl", "peer", "multimem"],
                     help="e2e workload, N > 1: all-reduce of the decode steps through NCCL, the peer-memory kernel or the in-switch "
-                         "(multimem) kernel; auto = multimem from 8 ranks on (its time does not grow with the ranks), else peer")
+                         "(multimem) kernel; auto = peer")
     ap.add_argument("--shard", default="batch", choices=["batch", "kv_heads"],
                     help="N > 1: independent batch per GPU (weak scaling) or KV-head tensor-parallel shards (strong)")
     ap.add_argument("--layers", type=int, default=36, help="mixed workload: layer caches per step")

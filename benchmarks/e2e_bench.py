@@ -31,8 +31,10 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
     allreduce_kind = "NCCL"
     if allreduce == "auto":
         # measured per 2 MiB message, fused form: tagged-word kernel 12.2 / 16.7 us at 2 / 4 ranks and growing with the
-        # bytes it sends to every peer; in-switch kernel 17.6 / 17.6 us
-        allreduce = "multimem" if world >= 8 else "peer"
+        # bytes it sends to every peer; in-switch kernel 16.8 / 17.6 us.  The in-switch kernel has not been timed at 8 ranks,
+        # and a rank that dies while bound to a multicast object disturbs its peers' GPUs, so the default stays with the
+        # kernel that needs nothing but peer mappings; "multimem" selects the other one.
+        allreduce = "peer"
     if allreduce in ("peer", "multimem") and world > 1:
         from .tp_comm import MulticastAllReduce, PeerAllReduce
         if allreduce == "multimem":
