@@ -63,6 +63,32 @@ def test_store_kvcache_bit_exact_with_padding_and_oob(dtype, row_elems, slot_dty
     assert np.array_equal(v_cache.cpu().view(torch.uint8).numpy(), vc_ref)
 
 
+@pytest.mark.parametrize("dtype,row_elems,slot_dtype,n", [
+    ("bf16", 8 * 128, np.int32, 5000), ("f16", 2 * 128, np.int64, 4099), ("bf16", 8 * 128, np.int32, 9001),
+])
+def test_store_kvcache_large_copies_bit_exact(dtype, row_elems, slot_dtype, n):
+    """Sizes at which whole rows go through the bulk-copy engine: padding and out-of-range slots in runs and alone,
+    at the start and at the end, every row and every untouched cache row compared byte for byte."""
+    rng = np.random.default_rng(31)
+    cache_rows = n + 777
+    key = rng.standard_normal((n, row_elems)).astype(np.float32)
+    value = rng.standard_normal((n, row_elems)).astype(np.float32)
+    slots = rng.permutation(cache_rows)[:n].astype(slot_dtype)
+    slots[::5] = -1
+    slots[0:9] = -1                      # a run of skipped rows at the start
+    slots[100:140] = cache_rows + 3      # a run beyond the cache
+    slots[-3:] = -1                      # and at the end
+    tk, tv = to_dev(key, _dt(dtype)), to_dev(value, _dt(dtype))
+    k_cache = torch.randn(cache_rows, row_elems, device="cuda").to(_dt(dtype))
+    v_cache = torch.randn(cache_rows, row_elems, device="cuda").to(_dt(dtype))
+    kc_ref = k_cache.cpu().view(torch.uint8).numpy().copy()
+    vc_ref = v_cache.cpu().view(torch.uint8).numpy().copy()
+    oracle.store_kvcache(tk.cpu().view(torch.uint8).numpy(), tv.cpu().view(torch.uint8).numpy(), kc_ref, vc_ref, slots)
+    nvk().store_kvcache(tk, tv, k_cache, v_cache, to_dev(slots))
+    assert np.array_equal(k_cache.cpu().view(torch.uint8).numpy(), kc_ref)
+    assert np.array_equal(v_cache.cpu().view(torch.uint8).numpy(), vc_ref)
+
+
 def test_store_kvcache_misaligned_views_and_duplicate_slots():
     rng = np.random.default_rng(5)
     n, row, cache_rows = 64, 24, 128
