@@ -69,10 +69,28 @@ __device__ __forceinline__ void mc_store(void* mc, const uint4& v) {
 __device__ __forceinline__ void st_signal(uint32_t* p, uint32_t v) {
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_signal(const uint32_t* p) {
+__device__ __forceinline__ uint32_t ld_signal_acquire(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+// Polls with relaxed loads and a short sleep between them (a block may wait for most of the launch, and system-scope acquire
+// loads in a tight loop cost the memory system more than they gain); one acquire load once the word has the value.
+__device__ __forceinline__ bool wait_signal(const uint32_t* word, uint32_t epoch, const MmParams& p, int* gave_up, unsigned int code) {
+    long long start = 0;
+    while (true) {
+        uint32_t v;
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(word) : "memory");
+        if (v == epoch) { ld_signal_acquire(word); return true; }
+        if (*reinterpret_cast<volatile int*>(gave_up)) return false;
+        if (start == 0) start = clock64();
+        else if (clock64() - start > p.wait_cycles) {
+            *reinterpret_cast<volatile int*>(gave_up) = 1;
+            atomicCAS(reinterpret_cast<unsigned int*>(p.flags + 2), 0u, code);
+            return false;
+        }
+        __nanosleep(64);
+    }
 }
 
 // Word layout of a signal area: [set (2)][block (kMmBlocks)][source rank (NVK_TP_MAX_RANKS)].
@@ -86,17 +104,7 @@ __device__ __forceinline__ bool peer_barrier(const MmParams& p, int set, int blo
     const int t = threadIdx.x;
     if (t < p.world && t != p.rank) {
         st_signal(p.signal[t] + signal_index(set, block, p.rank), epoch);
-        const uint32_t* mine = p.signal[p.rank] + signal_index(set, block, t);
-        long long start = 0;
-        while (ld_signal(mine) != epoch) {
-            if (*reinterpret_cast<volatile int*>(gave_up)) break;
-            if (start == 0) start = clock64();
-            else if (clock64() - start > p.wait_cycles) {
-                *reinterpret_cast<volatile int*>(gave_up) = 1;
-                atomicCAS(reinterpret_cast<unsigned int*>(p.flags + 2), 0u, static_cast<unsigned int>(code));
-                break;
-            }
-        }
+        wait_signal(p.signal[p.rank] + signal_index(set, block, t), epoch, p, gave_up, static_cast<unsigned int>(code));
     }
     __syncthreads();
     return *reinterpret_cast<volatile int*>(gave_up) == 0;
@@ -215,24 +223,13 @@ __global__ void __launch_bounds__(kMmThreads) allreduce_mm_kernel(const MmParams
         if (FUSED) {
             // rows of the peers' chunks, strided over ALL blocks: wait for the row's block on its rank, normalise it from this
             // rank's own copy of the result (only result rows cross the wire)
+            // (separate blocks for this part, waiting from the start of the launch, measured 3 us slower at 2 ranks)
             const int64_t items = static_cast<int64_t>(p.world - 1) * rows_per_rank;
             for (int64_t item = block; item < items; item += blocks) {
                 const int o = static_cast<int>(item / rows_per_rank);
                 const int src = o < p.rank ? o : o + 1;
                 const int r = static_cast<int>(item - static_cast<int64_t>(o) * rows_per_rank);
-                if (tid == 0) {
-                    const uint32_t* word = p.signal[p.rank] + signal_index(1, r % reducers, src);
-                    long long start = 0;
-                    while (ld_signal(word) != epoch) {
-                        if (*reinterpret_cast<volatile int*>(&s_gave_up)) break;
-                        if (start == 0) start = clock64();
-                        else if (clock64() - start > p.wait_cycles) {
-                            *reinterpret_cast<volatile int*>(&s_gave_up) = 1;
-                            atomicCAS(reinterpret_cast<unsigned int*>(p.flags + 2), 0u, 2u);
-                            break;
-                        }
-                    }
-                }
+                if (tid == 0) wait_signal(p.signal[p.rank] + signal_index(1, r % reducers, src), epoch, p, &s_gave_up, 2u);
                 __syncthreads();
                 if (*reinterpret_cast<volatile int*>(&s_gave_up)) break;
                 const int64_t base = (static_cast<int64_t>(src) * rows_per_rank + r) * row_vecs;
