@@ -374,7 +374,9 @@ def run_ours(args, torch, dist, rank, world, dev):
         from benchmarks import kernel_bench as kb
         line["other_kernels"] = kb.other_kernels(nvk, torch, dev)
         line["gpu_launches_other_kernels"] = "not counted in gpu_launches (outside the timed region)"
-    if world > 1 and not args.no_tp_e2e:
+    # at N = 1 too: the metric asks for output tokens per second at 1, 2, 4 and 8 GPUs (profiling runs, which pass
+    # --no-other-kernels, measure the decode step alone)
+    if not args.no_tp_e2e and (world > 1 or not args.no_other_kernels):
         line["tp_e2e"] = tp_e2e(args, nvk, torch, dist, rank, world, dev)
     return line
 
@@ -484,8 +486,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
-    ap.add_argument("--no-other-kernels", action="store_true", help="N = 1: skip the short runs of the kernels beside paged decode")
-    ap.add_argument("--no-tp-e2e", action="store_true", help="N > 1: skip the tensor-parallel end-to-end decoder run")
+    ap.add_argument("--no-other-kernels", action="store_true", help="N = 1: measure the paged-decode step alone (skips the short runs of the other kernels and the decoder run)")
+    ap.add_argument("--no-tp-e2e", action="store_true", help="skip the end-to-end decoder run (tensor-parallel over the N GPUs of the run)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e", "decode_int8", "linears", "decode_tp"],
                     help="decode is the benchmark; prefill / store / prologue / mixed / decode_int8 time the remaining kernels of the path "
                          "(1 GPU); e2e reports output tokens per second of the whole decoder, tensor-parallel over --gpus")
