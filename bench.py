@@ -571,7 +571,8 @@ def main():
             raise SystemExit("--gpus must divide the number of KV heads")
         dist.barrier()
         line = kb.bench_mixed(nvk, torch, dev, min(args.steps, 10), min(args.warmup, 3), layers=args.layers,
-                              hq=CFG["num_heads"] // world, hkv=CFG["num_kv_heads"] // world)
+                              hq=CFG["num_heads"] // world, hkv=CFG["num_kv_heads"] // world,
+                              single_launch=args.mixed_single_launch, prefill_blocks_hint=args.mixed_prefill_blocks)
         t = torch.tensor([line["ms_per_step"]], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if rank == 0:
