@@ -488,14 +488,14 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--no-other-kernels", action="store_true", help="N = 1: measure the paged-decode step alone (skips the short runs of the other kernels and the decoder run)")
     ap.add_argument("--no-tp-e2e", action="store_true", help="skip the end-to-end decoder run (tensor-parallel over the N GPUs of the run)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e", "decode_int8", "linears", "decode_tp"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "store", "prologue", "mixed", "e2e", "decode_int8", "decode_fp8", "linears", "decode_tp"],
                     help="decode is the benchmark; prefill / store / prologue / mixed / decode_int8 time the remaining kernels of the path "
                          "(1 GPU); e2e reports output tokens per second of the whole decoder, tensor-parallel over --gpus")
     ap.add_argument("--e2e-layers", type=int, default=36, help="e2e workload: decoder layers (36 = the named model)")
     ap.add_argument("--e2e-seqs", type=int, default=256, help="e2e workload: number of sequences")
     ap.add_argument("--e2e-maxlen", type=int, default=1024, help="e2e workload: longest prompt / output")
     ap.add_argument("--no-graph", action="store_true", help="e2e workload: run decode steps eagerly")
-    ap.add_argument("--e2e-kv", default="bf16", choices=["bf16", "int8"], help="e2e workload: KV cache format")
+    ap.add_argument("--e2e-kv", default="bf16", choices=["bf16", "int8", "fp8"], help="e2e workload: KV cache format")
     ap.add_argument("--e2e-linears", default="cublas", choices=["cublas", "fused"],
                     help="e2e workload: decode-step QKV / o_proj / down_proj as cuBLAS GEMMs + kernels, or this library's fused GEMMs")
     ap.add_argument("--e2e-allreduce", default="auto", choices=["auto", "nccl", "peer", "multimem"],
@@ -598,8 +598,8 @@ def main():
             line = kb.bench_prefill(nvk, torch, dev, steps, args.warmup, args.seqs, min(512, args.qmax), args.qmax)
         elif args.workload == "store":
             line = kb.bench_store(nvk, torch, dev, steps, args.warmup)
-        elif args.workload == "decode_int8":
-            line = kb.bench_decode_int8(nvk, torch, dev, steps, args.warmup, batch=args.batch)
+        elif args.workload in ("decode_int8", "decode_fp8"):
+            line = kb.bench_decode_int8(nvk, torch, dev, steps, args.warmup, batch=args.batch, fmt=args.workload[7:])
         elif args.workload == "decode_tp":
             line = kb.bench_decode_tp_shape(nvk, torch, dev, steps, args.warmup, batch=args.batch)
         elif args.workload == "linears":

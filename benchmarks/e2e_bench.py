@@ -178,7 +178,7 @@ def run_e2e(nvk, torch, dist, rank, world, dev, cfg: DecoderConfig | None = None
                                f"head_dim {cfg.head_dim}, FFN {cfg.ffn}, vocab {cfg.vocab}, random-init bf16 weights; {num_seqs} sequences, "
                                f"prompt and output lengths U[{len_lo},{len_hi}], greedy, ignore_eos",
                    "parallelism": f"tp{world} (KV-head shards, all-reduce after o_proj / down_proj)",
-                   "kv_cache": "int8 with fp16 per-(token, head) scales" if model.int8 else "bf16",
+                   "kv_cache": (("e4m3" if model.fp8 else "int8") + " with fp16 per-(token, head) scales") if model.int8 else "bf16",
                    "allreduce": allreduce_kind,
                    "linears": ("decode steps: QKV projection with split + norm + RoPE + cache store in its epilogue "
                                "(nvk_qkv_linear_norm_rope_store)" + ("; o_proj / down_proj push their partial sums into the all-reduce "

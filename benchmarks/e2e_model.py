@@ -96,11 +96,12 @@ class Decoder:
         self.scale = 1.0 / math.sqrt(d)
         # [2, layers, blocks, block_size, Hkv/t, D] as in allocate_kv_cache (src/engine/model_runner.cpp:355-472)
         self.num_blocks = int(num_blocks)
-        if kv_dtype not in ("bf16", "int8"):
-            raise ValueError("kv_dtype must be bf16 or int8")
-        self.int8 = kv_dtype == "int8"
+        if kv_dtype not in ("bf16", "int8", "fp8"):
+            raise ValueError("kv_dtype must be bf16, int8 or fp8")
+        self.int8 = kv_dtype in ("int8", "fp8")     # an 8-bit cache with per-(token, head) scales: the unfused route
+        self.fp8 = kv_dtype == "fp8"                # e4m3 bytes instead of int8 (no counterpart in the reference)
         self.kv_cache = torch.zeros((2, cfg.layers, self.num_blocks, cfg.block_size, self.hkv, d), device=dev,
-                                    dtype=torch.int8 if self.int8 else bf)
+                                    dtype=(torch.uint8 if self.fp8 else torch.int8) if self.int8 else bf)
         # int8 cache: one fp16 scale per (cache row, KV head), the reference's format (include/kernels/kvcache.h:14-24)
         self.kv_scale = (torch.zeros((2, cfg.layers, self.num_blocks, cfg.block_size, self.hkv), device=dev, dtype=torch.float16)
                          if self.int8 else None)
@@ -167,8 +168,8 @@ class Decoder:
             elif self.int8:
                 nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, rows,
                                                 k_step, v_step, self.hq, self.hkv, cfg.head_dim, q)
-                nvk.store_kvcache_int8(k_step, v_step, self.kv_cache[0, l], self.kv_cache[1, l], self.kv_scale[0, l],
-                                       self.kv_scale[1, l], slot_mapping)
+                (nvk.store_kvcache_fp8 if self.fp8 else nvk.store_kvcache_int8)(
+                    k_step, v_step, self.kv_cache[0, l], self.kv_cache[1, l], self.kv_scale[0, l], self.kv_scale[1, l], slot_mapping)
             else:
                 nvk.fused_split_norm_rope_store(qkv, positions, w["q_norm"], w["k_norm"], cfg.eps, self.cos_sin, slot_mapping,
                                                 self.kv_cache[0, l], self.kv_cache[1, l], self.hq, self.hkv, cfg.head_dim, q)
@@ -196,9 +197,9 @@ class Decoder:
 
         def attend(l, q, k, v, out):
             if self.int8:
-                nvk.launch_decode_attention_paged_int8(q, self.kv_cache[0, l], self.kv_cache[1, l], self.kv_scale[0, l],
-                                                       self.kv_scale[1, l], ctx, tables, self.hkv, cfg.head_dim, cfg.block_size,
-                                                       self.scale, out, self.workspace)
+                (nvk.launch_decode_attention_paged_fp8 if self.fp8 else nvk.launch_decode_attention_paged_int8)(
+                    q, self.kv_cache[0, l], self.kv_cache[1, l], self.kv_scale[0, l], self.kv_scale[1, l], ctx, tables, self.hkv,
+                    cfg.head_dim, cfg.block_size, self.scale, out, self.workspace)
             else:
                 nvk.launch_decode_attention_paged(q, self.kv_cache[0, l], self.kv_cache[1, l], ctx, tables, self.hkv,
                                                   cfg.head_dim, cfg.block_size, self.scale, out, self.workspace)

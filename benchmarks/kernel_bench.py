@@ -187,7 +187,7 @@ def bench_store(nvk, torch, dev, steps, warmup, tokens=36864):
             "gpu_launches": 2 * steps, "clocks": clocks}
 
 
-def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ctx_hi=8192):
+def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ctx_hi=8192, fmt="int8"):
     """Paged decode at the benchmark shape through the int8 KV cache: a bf16 cache is generated, quantised by the
     library's own store (timed as well), then decoded; the 16-bit decode of the same cache is timed beside it."""
     from . import workloads as wl
@@ -200,19 +200,22 @@ def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ct
     rows = pool * BS
     kc16 = torch.empty((pool, BS, HKV, D), device=dev, dtype=bf).normal_(generator=gen)
     vc16 = torch.empty((pool, BS, HKV, D), device=dev, dtype=bf).normal_(generator=gen)
-    kc8 = torch.empty((pool, BS, HKV, D), device=dev, dtype=torch.int8)
+    fp8 = fmt == "fp8"      # e4m3 bytes in the same layout (no counterpart in the reference)
+    store_fn = nvk.store_kvcache_fp8 if fp8 else nvk.store_kvcache_int8
+    decode_fn = nvk.launch_decode_attention_paged_fp8 if fp8 else nvk.launch_decode_attention_paged_int8
+    kc8 = torch.empty((pool, BS, HKV, D), device=dev, dtype=torch.uint8 if fp8 else torch.int8)
     vc8 = torch.empty_like(kc8)
     ks = torch.empty((pool, BS, HKV), device=dev, dtype=torch.float16)
     vs = torch.empty_like(ks)
     slots = torch.arange(rows, dtype=torch.int32, device=dev)
-    store = lambda: nvk.store_kvcache_int8(kc16.view(rows, HKV, D), vc16.view(rows, HKV, D), kc8, vc8, ks, vs, slots)  # noqa: E731
+    store = lambda: store_fn(kc16.view(rows, HKV, D), vc16.view(rows, HKV, D), kc8, vc8, ks, vs, slots)  # noqa: E731
     store_ms, _ = _time(torch, store, 5, 2)
     q = torch.randn((batch, HQ, D), generator=gen, device=dev).to(bf)
     out8, out16 = torch.empty_like(q), torch.empty_like(q)
     ctx_dev, tab_dev = torch.from_numpy(ctx).to(dev), torch.from_numpy(tables).to(dev)
     scale = 1.0 / math.sqrt(D)
     ws = torch.empty(max(16, nvk.decode_attention_workspace_bytes(batch, HQ, HKV, D, tables.shape[1], BS)), dtype=torch.uint8, device=dev)
-    dec8 = lambda: nvk.launch_decode_attention_paged_int8(q, kc8, vc8, ks, vs, ctx_dev, tab_dev, HKV, D, BS, scale, out8, ws)  # noqa: E731
+    dec8 = lambda: decode_fn(q, kc8, vc8, ks, vs, ctx_dev, tab_dev, HKV, D, BS, scale, out8, ws)  # noqa: E731
     dec16 = lambda: nvk.launch_decode_attention_paged(q, kc16, vc16, ctx_dev, tab_dev, HKV, D, BS, scale, out16, ws)  # noqa: E731
     mean8, med8 = _time(torch, dec8, steps, warmup)
     clocks8 = LAST_CLOCKS
@@ -225,17 +228,17 @@ def bench_decode_int8(nvk, torch, dev, steps, warmup, batch=256, ctx_lo=1024, ct
     store_bytes = 2 * rows * HKV * D * 2 + 2 * rows * HKV * (D + 2) + 4 * rows
     hbm, _, kind = _peaks()
     ach = bytes8 / (mean8 * 1e-3) / 1e9
-    return {"metric": "paged_decode_attention_int8_kv_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+    return {"metric": f"paged_decode_attention_{fmt}_kv_hbm_bandwidth", "value": ach, "unit": "GB/s", "n_gpus": 1, "steps": steps,
             "warmup": warmup, "ms_per_step": mean8, "median_ms": med8, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8 KV, f16 MMA", "data": "synthetic",
-            "config": {"workload": f"paged decode attention, int8 KV cache with fp16 per-(token, head) scales, batch {batch}, "
+            "vs_baseline": None, "dtype": f"{fmt} KV, f16 MMA", "data": "synthetic",
+            "config": {"workload": f"paged decode attention, {'e4m3' if fp8 else 'int8'} KV cache with fp16 per-(token, head) scales, batch {batch}, "
                                    f"{HQ}/{HKV} heads, head_dim {D}, block_size {BS}, context U[{ctx_lo},{ctx_hi}]",
                        "context_tokens": tokens, "algorithmic_bytes": bytes8, "l2": "the cache (2 x %.1f GB) exceeds the 126 MB L2" % (rows * HKV * D / 1e9)},
-            "roofline": {"bound": "hbm", "kernel": "decode_split_int8_kernel", "achieved": ach, "peak": hbm,
+            "roofline": {"bound": "hbm", "kernel": "decode_split_int8_kernel<T, fp8>" if fp8 else "decode_split_int8_kernel", "achieved": ach, "peak": hbm,
                          "peak_source": f"{kind} copy bandwidth", "unit": "GB/s", "frac": ach / hbm, "traffic": None},
-            "bf16_cache_same_shape": {"ms_per_step": mean16, "GBps": bytes16 / (mean16 * 1e-3) / 1e9, "speedup_of_int8": mean16 / mean8},
+            "bf16_cache_same_shape": {"ms_per_step": mean16, "GBps": bytes16 / (mean16 * 1e-3) / 1e9, "speedup_of_8_bit_cache": mean16 / mean8},
             "max_abs_diff_vs_bf16_cache": float(err.max()), "mean_abs_diff_vs_bf16_cache": float(err.mean()),
-            "store_kvcache_int8": {"ms": store_ms, "tokens": rows, "bytes": store_bytes, "GBps": store_bytes / (store_ms * 1e-3) / 1e9,
+            f"store_kvcache_{fmt}": {"ms": store_ms, "tokens": rows, "bytes": store_bytes, "GBps": store_bytes / (store_ms * 1e-3) / 1e9,
                                    "frac_of_measured_hbm": store_bytes / (store_ms * 1e-3) / 1e9 / hbm},
             "gpu_launches": steps * 2, "clocks": clocks8}
 
@@ -594,6 +597,9 @@ def other_kernels(nvk, torch, dev, steps=20, warmup=3):
     torch.cuda.empty_cache()
     line = bench_decode_int8(nvk, torch, dev, steps, warmup)
     out["decode_int8_kv"] = brief(line, extra=("bf16_cache_same_shape", "store_kvcache_int8"))
+    torch.cuda.empty_cache()
+    line = bench_decode_int8(nvk, torch, dev, steps, warmup, fmt="fp8")
+    out["decode_fp8_kv"] = brief(line, extra=("bf16_cache_same_shape", "store_kvcache_fp8"))
     torch.cuda.empty_cache()
     line = bench_decode_tp_shape(nvk, torch, dev, steps, warmup)
     out["decode_tp8_rank_shape_in_graph"] = brief(line, extra=("eager_ms_per_layer",))

@@ -144,6 +144,26 @@ int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, cons
                                     size_t workspace_bytes, void* stream);
 
 /*
+ * fp8 (e4m3) KV cache.  NO COUNTERPART IN THE REFERENCE (it has the int8 cache above and names an fp8 cache as a next step);
+ * the layout and the arithmetic follow the int8 cache with the range of the type:
+ *   k_cache, v_cache  e4m3 bytes [cache_rows, num_kv_heads, head_dim]
+ *   k_scale, v_scale  fp16 [cache_rows, num_kv_heads]: scale = max(absmax / 448, 1e-10) of the head vector,
+ *                     element = e4m3(x * 448 / max(absmax, 1e-10)), round to nearest even from the fp32 product, saturating
+ * key / value F16 or BF16, head_dim 64 / 128 / 256 for the store; the decode entry point has the semantics of
+ * nvk_decode_attention_paged with k = e4m3 * k_scale, v = e4m3 * v_scale and takes the shapes of the tensor-core path only
+ * (F16 / BF16 queries, head_dim 128, at most 8 query heads per KV head, block_size a multiple of 16); workspace as there.
+ */
+int nvk_store_kvcache_fp8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale,
+                          void* v_scale, const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads,
+                          int head_dim, int64_t cache_rows, int dtype, void* stream);
+int nvk_decode_attention_paged_fp8(const void* query, const void* k_cache, const void* v_cache,
+                                   const void* k_scale, const void* v_scale, const void* context_lens,
+                                   int context_lens_dtype, const void* block_tables, int block_tables_dtype,
+                                   int64_t batch, int64_t max_blocks, int64_t num_cache_blocks, int num_heads,
+                                   int num_kv_heads, int head_dim, int block_size, float scale, void* output,
+                                   int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Same computation as nvk_decode_attention_paged for callers that cannot provide a workspace and
  * must not allocate device memory.  (No counterpart in the reference: its decode entry point simply
  * has no scratch.)  Typical callers: a wrapper with the reference's launch_decode_attention_paged

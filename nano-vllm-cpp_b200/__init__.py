@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "nvk_linear", "nvk_qkv_linear_norm_rope_store", "nvk_tp_row_linear_allreduce_add_rmsnorm",
     "nvk_tp_row_linear_allreduce_add_rmsnorm_inprocess", "nvk_gemm_status",
     "nvk_tp_allreduce_signal_bytes", "nvk_tp_allreduce_multimem", "nvk_tp_allreduce_add_rmsnorm_multimem",
+    "nvk_store_kvcache_fp8", "nvk_decode_attention_paged_fp8",
 )
 
 _lib = None
@@ -234,6 +235,48 @@ def launch_decode_attention_paged_int8(query, k_cache, v_cache, k_scale, v_scale
     batch, num_heads = query.shape[0], query.shape[1]
     num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
     _check(lib().nvk_decode_attention_paged_int8(
+        _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), *_index("context_lens", context_lens),
+        *_index("block_tables", block_tables), ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
+        ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim), ctypes.c_int(block_size),
+        ctypes.c_float(scale), _ptr(output), ctypes.c_int(_dtype_code(query)), _ptr(workspace),
+        ctypes.c_size_t(workspace.numel() * workspace.element_size() if workspace is not None else 0), _stream()))
+    ws_need = decode_attention_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, block_tables.shape[1], block_size)
+    launch_count += 2 if (workspace is not None and ws_need > 0) else 1
+
+
+def store_kvcache_fp8(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping) -> None:
+    """Quantising scatter into e4m3 caches (uint8 or float8_e4m3fn tensors) + fp16 scales (``nvk_store_kvcache_fp8``)."""
+    global launch_count
+    import torch
+    for n, t in (("key", key), ("value", value), ("k_cache", k_cache), ("v_cache", v_cache), ("k_scale", k_scale),
+                 ("v_scale", v_scale), ("slot_mapping", slot_mapping)):
+        _require_cuda(n, t)
+    if k_cache.element_size() != 1 or v_cache.element_size() != 1:
+        raise ValueError("store_kvcache_fp8 requires one-byte caches")
+    if k_scale.dtype != torch.float16 or v_scale.dtype != torch.float16:
+        raise ValueError("store_kvcache_fp8 requires float16 scales")
+    if key.dim() != 3:
+        raise ValueError("key must be rank-3 for the fp8 store")
+    if slot_mapping.dtype.itemsize != 4:
+        raise ValueError("slot_mapping must be int32")
+    hkv, d = key.shape[1], key.shape[2]
+    _check(lib().nvk_store_kvcache_fp8(
+        _ptr(key), _ptr(value), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(slot_mapping),
+        ctypes.c_int64(slot_mapping.numel()), ctypes.c_int(hkv), ctypes.c_int(d),
+        ctypes.c_int64(k_cache.numel() // (hkv * d)), ctypes.c_int(_dtype_code(key)), _stream()))
+    launch_count += 1
+
+
+def launch_decode_attention_paged_fp8(query, k_cache, v_cache, k_scale, v_scale, context_lens, block_tables,
+                                      num_kv_heads, head_dim, block_size, scale, output, workspace=None) -> None:
+    """Paged decode attention over an e4m3 cache (``nvk_decode_attention_paged_fp8``)."""
+    global launch_count
+    for n, t in (("query", query), ("k_cache", k_cache), ("v_cache", v_cache), ("k_scale", k_scale), ("v_scale", v_scale),
+                 ("context_lens", context_lens), ("block_tables", block_tables), ("output", output)):
+        _require_cuda(n, t)
+    batch, num_heads = query.shape[0], query.shape[1]
+    num_cache_blocks = k_cache.numel() // (block_size * num_kv_heads * head_dim)
+    _check(lib().nvk_decode_attention_paged_fp8(
         _ptr(query), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), *_index("context_lens", context_lens),
         *_index("block_tables", block_tables), ctypes.c_int64(batch), ctypes.c_int64(block_tables.shape[1]), ctypes.c_int64(num_cache_blocks),
         ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim), ctypes.c_int(block_size),

@@ -138,7 +138,29 @@ struct DecodeInt8Params {
     const __half* k_scale; const __half* v_scale;
 };
 
-template <typename T>
+// Two 8-bit cache elements -> two f16 (MMA operand halves).  int8: the byte glued under the exponent byte of 1024 (the word has
+// had its sign bits flipped: value + 1152, taken out algebraically afterwards); e4m3: the hardware conversion, exact.
+template <bool FP8> __device__ __forceinline__ uint32_t widen_pair_lo(uint32_t x) {   // bytes 0, 1
+    if constexpr (FP8) {
+        uint32_t d;
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(d) : "h"(static_cast<unsigned short>(x & 0xffffu)));
+        return d;
+    } else {
+        return __byte_perm(x, 0x64646464u, 0x4140);
+    }
+}
+template <bool FP8> __device__ __forceinline__ uint32_t widen_pair_hi(uint32_t x) {   // bytes 2, 3
+    if constexpr (FP8) {
+        uint32_t d;
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(d) : "h"(static_cast<unsigned short>(x >> 16)));
+        return d;
+    } else {
+        return __byte_perm(x, 0x64646464u, 0x4342);
+    }
+}
+
+// FP8 = false: int8 cache (the reference's format); FP8 = true: e4m3 cache of the same layout.
+template <typename T, bool FP8>
 __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const DecodeInt8Params pp) {
     const DecodeParams& p = pp.base;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -193,7 +215,8 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
         qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
         qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
     }
-    const float q_off = kI8Offset * qsum;
+    const float q_off = FP8 ? 0.0f : kI8Offset * qsum;
+    constexpr uint32_t kFlip = FP8 ? 0u : 0x80808080u;   // int8: sign bits flipped before the glue
 
     const uint32_t ring_u32 = smem_u32(smem + warp * kWarpBytesI8);
     const int num_tiles = (t1 - t0 + kTileTokens - 1) / kTileTokens;
@@ -245,7 +268,6 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
 #pragma unroll
     for (int s = 0; s < kStagesI8 - 1; ++s) issue(s);
 
-    constexpr uint32_t kGlue = 0x64646464u;   // exponent byte of 1024.0 in f16
     constexpr uint32_t kOnes = 0x3C003C00u;   // {1.0, 1.0}
 
     for (int j = 0; j < my_tiles; ++j) {
@@ -272,9 +294,9 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 const int ks = 4 * q + wi;
-                const uint32_t x0 = w0[wi] ^ 0x80808080u, x1 = w1[wi] ^ 0x80808080u;
-                mma_16816<__half>(s0, qa[ks][0], 0u, qa[ks][1], 0u, __byte_perm(x0, kGlue, 0x4140), __byte_perm(x0, kGlue, 0x4342));
-                mma_16816<__half>(s1, qa[ks][0], 0u, qa[ks][1], 0u, __byte_perm(x1, kGlue, 0x4140), __byte_perm(x1, kGlue, 0x4342));
+                const uint32_t x0 = w0[wi] ^ kFlip, x1 = w1[wi] ^ kFlip;
+                mma_16816<__half>(s0, qa[ks][0], 0u, qa[ks][1], 0u, widen_pair_lo<FP8>(x0), widen_pair_hi<FP8>(x0));
+                mma_16816<__half>(s1, qa[ks][0], 0u, qa[ks][1], 0u, widen_pair_lo<FP8>(x1), widen_pair_hi<FP8>(x1));
             }
         }
         // scores of head g: tokens tok0 + {2t, 2t+1, 8+2t, 9+2t}; remove the offset, apply each key's K scale
@@ -323,18 +345,16 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
         lds32x4(vbase + (2 * t + 9) * kRowBytesI8 + ((g ^ ((2 * t + 9) & 6)) << 4), v3);
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
-            const uint32_t x0 = v0[a] ^ 0x80808080u, x1 = v1[a] ^ 0x80808080u, x2 = v2[a] ^ 0x80808080u, x3 = v3[a] ^ 0x80808080u;
+            const uint32_t x0 = v0[a] ^ kFlip, x1 = v1[a] ^ kFlip, x2 = v2[a] ^ kFlip, x3 = v3[a] ^ kFlip;
             // bytes of one d from two consecutive keys, side by side
             const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
             const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
             float (&oe)[4] = o[2 * a];
             float (&oo)[4] = o[2 * a + 1];
-            mma_16816<__half>(oe, __byte_perm(lo01, kGlue, 0x4140), __byte_perm(lo01, kGlue, 0x4342),
-                              __byte_perm(lo23, kGlue, 0x4140), __byte_perm(lo23, kGlue, 0x4342), pb0, pb1);
-            mma_16816<__half>(oo, __byte_perm(hi01, kGlue, 0x4140), __byte_perm(hi01, kGlue, 0x4342),
-                              __byte_perm(hi23, kGlue, 0x4140), __byte_perm(hi23, kGlue, 0x4342), pb0, pb1);
+            mma_16816<__half>(oe, widen_pair_lo<FP8>(lo01), widen_pair_hi<FP8>(lo01), widen_pair_lo<FP8>(lo23), widen_pair_hi<FP8>(lo23), pb0, pb1);
+            mma_16816<__half>(oo, widen_pair_lo<FP8>(hi01), widen_pair_hi<FP8>(hi01), widen_pair_lo<FP8>(hi23), widen_pair_hi<FP8>(hi23), pb0, pb1);
         }
-        mma_16816<__half>(osum, kOnes, kOnes, kOnes, kOnes, pb0, pb1);
+        if (!FP8) mma_16816<__half>(osum, kOnes, kOnes, kOnes, kOnes, pb0, pb1);
         __syncwarp();   // the stage is refilled two iterations from now by other lanes' copies
     }
     cp_async_wait<0>();
@@ -352,10 +372,11 @@ __global__ void __launch_bounds__(kThreads, 3) decode_split_int8_kernel(const De
         // accumulator rows g / g + 8 of d-tile mt = 2 a + e hold d = 16 g + 4 a + 2 e (+ 1); columns are heads 2t, 2t + 1
         const int d = 16 * g + 4 * (mt >> 1) + 2 * (mt & 1);
         float* dst = sm_o + (warp * kMaxGroup + 2 * t) * kHeadDim + d;
-        dst[0] = o[mt][0] - kI8Offset * osum[0];
-        dst[kHeadDim] = o[mt][1] - kI8Offset * osum[1];
-        dst[1] = o[mt][2] - kI8Offset * osum[0];
-        dst[kHeadDim + 1] = o[mt][3] - kI8Offset * osum[1];
+        const float off = FP8 ? 0.0f : kI8Offset;
+        dst[0] = o[mt][0] - off * osum[0];
+        dst[kHeadDim] = o[mt][1] - off * osum[1];
+        dst[1] = o[mt][2] - off * osum[0];
+        dst[kHeadDim + 1] = o[mt][3] - off * osum[1];
     }
     __syncthreads();
 
@@ -472,14 +493,14 @@ int launch_typed(const DecodeArgs& a) {
     return rc;
 }
 
-template <typename T>
+template <typename T, bool FP8>
 int launch_int8_typed(const DecodeInt8Args& x) {
     const DecodeArgs& a = x.base;
     static bool attr_done[64] = {};
     int device = 0;
     cudaGetDevice(&device);
     if (device >= 0 && device < 64 && !attr_done[device]) {
-        const cudaError_t e = cudaFuncSetAttribute(decode_split_int8_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesI8);
+        const cudaError_t e = cudaFuncSetAttribute(decode_split_int8_kernel<T, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesI8);
         if (e != cudaSuccess) return fail(NVK_ERR_CUDA, "decode attention (int8): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         attr_done[device] = true;
     }
@@ -508,7 +529,7 @@ int launch_int8_typed(const DecodeInt8Args& x) {
     }
     if (a.batch > 65535 || p.num_splits > 65535) return fail(NVK_ERR_UNSUPPORTED, "decode attention (int8): batch or split count exceeds grid limits");
     const dim3 grid(a.num_kv_heads, p.num_splits, static_cast<unsigned>(a.batch));
-    cudaError_t le = launch_pdl(decode_split_int8_kernel<T>, grid, dim3(kThreads), kSmemBytesI8, a.stream, pp);
+    cudaError_t le = launch_pdl(decode_split_int8_kernel<T, FP8>, grid, dim3(kThreads), kSmemBytesI8, a.stream, pp);
     if (le != cudaSuccess) return fail(NVK_ERR_CUDA, "decode_split_int8_kernel launch: %s", cudaGetErrorString(le));
     int rc = check_launch("decode_split_int8_kernel launch");
     if (rc != NVK_OK) return rc;
@@ -561,7 +582,8 @@ bool decode_int8_mma_supported(const DecodeInt8Args& x) {
 }
 
 int launch_decode_int8_mma(const DecodeInt8Args& x) {
-    return x.base.dtype == NVK_BF16 ? launch_int8_typed<__nv_bfloat16>(x) : launch_int8_typed<__half>(x);
+    if (x.fp8) return x.base.dtype == NVK_BF16 ? launch_int8_typed<__nv_bfloat16, true>(x) : launch_int8_typed<__half, true>(x);
+    return x.base.dtype == NVK_BF16 ? launch_int8_typed<__nv_bfloat16, false>(x) : launch_int8_typed<__half, false>(x);
 }
 
 int launch_decode_mma(const DecodeArgs& a) {

@@ -173,6 +173,86 @@ store_int8_packed_kernel(const T* __restrict__ key, const T* __restrict__ value,
     }
 }
 
+// ---- fp8 (e4m3) cache: the packed kernel with the other element type.  No counterpart in the reference; the format follows
+// its int8 cache: one fp16 scale per (cache row, KV head) = max(absmax / 448, 1e-10), elements = e4m3(x * 448 / max(absmax,
+// 1e-10)) rounded to nearest even from the fp32 product, saturating at +-448.
+__device__ __forceinline__ uint32_t pack_e4m3x4(float e0, float e1, float e2, float e3) {   // bytes {e0, e1, e2, e3}, e0 lowest
+    unsigned short lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(lo) : "f"(e1), "f"(e0));   // first source -> upper byte
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(hi) : "f"(e3), "f"(e2));
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+template <typename T>
+__device__ __forceinline__ uint2 quantise8_e4m3(const uint4& v, float inv) {
+    using P = Pair16<T>;
+    uint2 q;
+    q.x = pack_e4m3x4(__fmul_rn(P::lo(v.x), inv), __fmul_rn(P::hi(v.x), inv), __fmul_rn(P::lo(v.y), inv), __fmul_rn(P::hi(v.y), inv));
+    q.y = pack_e4m3x4(__fmul_rn(P::lo(v.z), inv), __fmul_rn(P::hi(v.z), inv), __fmul_rn(P::lo(v.w), inv), __fmul_rn(P::hi(v.w), inv));
+    return q;
+}
+
+template <typename T, int LANES>
+__global__ void __launch_bounds__(kStoreWarps * 32)
+store_fp8_packed_kernel(const T* __restrict__ key, const T* __restrict__ value, uint8_t* __restrict__ k_cache,
+                        uint8_t* __restrict__ v_cache, __half* __restrict__ k_scale, __half* __restrict__ v_scale,
+                        const int32_t* __restrict__ slot_mapping, uint32_t total, uint32_t num_kv_heads, int64_t cache_rows) {
+    using P = typename Pair16<T>::type;
+    constexpr int D = 8 * LANES;
+    constexpr int kPerWarp = 32 / LANES;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t sub = lane % LANES;
+    uint32_t work = (blockIdx.x * kStoreWarps + (threadIdx.x >> 5)) * kPerWarp + lane / LANES;   // (token, head)
+    if (work >= total) work = total - 1;   // lanes past the end repeat the last vector: the shuffles stay full-warp
+    const uint32_t token = work / num_kv_heads;
+    const uint32_t head = work - token * num_kv_heads;
+    const size_t src = static_cast<size_t>(work) * D + sub * 8;
+    const uint4 kv = __ldcs(reinterpret_cast<const uint4*>(key + src));
+    const uint4 vv = __ldcs(reinterpret_cast<const uint4*>(value + src));
+    const int64_t slot = slot_mapping[token];
+    P m = Pair16<T>::join(absmax8<T>(kv), absmax8<T>(vv));   // K's maximum in the low half, V's in the high half
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) {
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const uint32_t*>(&m), o);
+        m = __hmax2(m, *reinterpret_cast<const P*>(&other));
+    }
+    if (slot < 0 || slot >= cache_rows) return;
+    const float kmax = Pair16<T>::first(m), vmax = Pair16<T>::second(m);
+    const float k_inv = __fdiv_rn(448.0f, fmaxf(kmax, 1e-10f)), v_inv = __fdiv_rn(448.0f, fmaxf(vmax, 1e-10f));
+    const size_t dst_row = static_cast<size_t>(slot) * num_kv_heads + head;
+    *reinterpret_cast<uint2*>(k_cache + dst_row * D + sub * 8) = quantise8_e4m3<T>(kv, k_inv);
+    *reinterpret_cast<uint2*>(v_cache + dst_row * D + sub * 8) = quantise8_e4m3<T>(vv, v_inv);
+    if (sub < 2) {   // lane 0 of the group stores K's scale, lane 1 V's
+        const float sc = fmaxf(__fdiv_rn(sub == 0 ? kmax : vmax, 448.0f), 1e-10f);
+        (sub == 0 ? k_scale : v_scale)[dst_row] = __float2half(sc);
+    }
+}
+
+template <typename T>
+int launch_store_fp8_typed(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                           const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,
+                           cudaStream_t stream) {
+    const int lanes = head_dim / 8;
+    if (head_dim % 8 != 0 || (lanes != 8 && lanes != 16 && lanes != 32))
+        return fail(NVK_ERR_UNSUPPORTED, "store_kvcache_fp8: head_dim must be 64, 128 or 256 (got %d)", head_dim);
+    const int64_t work = num_tokens * num_kv_heads;
+    if (work <= 0) return NVK_OK;
+    if (work >= 0x7fffffffLL) return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_fp8: too many tokens");
+    const int64_t per_block = static_cast<int64_t>(kStoreWarps) * (32 / lanes);
+    const int64_t blocks = (work + per_block - 1) / per_block;
+#define NVK_LAUNCH_FP8(L)                                                                                           \
+    store_fp8_packed_kernel<T, L><<<static_cast<unsigned>(blocks), kStoreWarps * 32, 0, stream>>>(                   \
+        static_cast<const T*>(key), static_cast<const T*>(value), static_cast<uint8_t*>(k_cache),                  \
+        static_cast<uint8_t*>(v_cache), static_cast<__half*>(k_scale), static_cast<__half*>(v_scale), slot_mapping, \
+        static_cast<uint32_t>(work), static_cast<uint32_t>(num_kv_heads), cache_rows)
+    switch (lanes) {
+        case 8: NVK_LAUNCH_FP8(8); break;
+        case 16: NVK_LAUNCH_FP8(16); break;
+        default: NVK_LAUNCH_FP8(32); break;
+    }
+#undef NVK_LAUNCH_FP8
+    return check_launch("store_kvcache_fp8 kernel launch");
+}
+
 // General decode path: one warp per (sequence, query head), lane owns D / 32 contiguous elements; serial online
 // softmax over the keys as in the reference.  Used for fp32 queries and head dims other than 128.
 template <typename T, int V>
@@ -296,6 +376,16 @@ int launch_store_int8(const void* key, const void* value, void* k_cache, void* v
         case NVK_BF16: return launch_store_typed<__nv_bfloat16>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
         case NVK_F16: return launch_store_typed<__half>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
         default: return launch_store_typed<float>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
+    }
+}
+
+int launch_store_fp8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                     const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,
+                     int dtype, cudaStream_t stream) {
+    switch (dtype) {
+        case NVK_BF16: return launch_store_fp8_typed<__nv_bfloat16>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
+        case NVK_F16: return launch_store_fp8_typed<__half>(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim, cache_rows, stream);
+        default: return fail(NVK_ERR_UNSUPPORTED, "store_kvcache_fp8: key / value must be F16 or BF16");
     }
 }
 

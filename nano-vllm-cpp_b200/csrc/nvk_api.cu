@@ -173,6 +173,54 @@ int nvk_decode_attention_paged_int8(const void* query, const void* k_cache, cons
     return launch_rowwise_decode_int8(a);
 }
 
+int nvk_store_kvcache_fp8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                          const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,
+                          int dtype, void* stream) {
+    if (!key || !value || !k_cache || !v_cache || !k_scale || !v_scale || !slot_mapping)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_fp8 requires key, value, caches, scales and slot_mapping");
+    if (dtype != NVK_F16 && dtype != NVK_BF16) return fail(NVK_ERR_UNSUPPORTED, "store_kvcache_fp8: key / value must be F16 or BF16");
+    if (num_tokens < 0 || num_kv_heads <= 0 || head_dim <= 0 || cache_rows <= 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_fp8: sizes must be positive");
+    if (!aligned_to(key, 16) || !aligned_to(value, 16) || !aligned_to(k_cache, 8) || !aligned_to(v_cache, 8))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "store_kvcache_fp8: key / value must be 16-byte aligned, the caches 8-byte aligned");
+    if (num_tokens == 0) return NVK_OK;
+    return launch_store_fp8(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping, num_tokens, num_kv_heads, head_dim,
+                            cache_rows, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int nvk_decode_attention_paged_fp8(const void* query, const void* k_cache, const void* v_cache, const void* k_scale,
+                                   const void* v_scale, const void* context_lens, int context_lens_dtype,
+                                   const void* block_tables, int block_tables_dtype, int64_t batch, int64_t max_blocks,
+                                   int64_t num_cache_blocks, int num_heads, int num_kv_heads, int head_dim,
+                                   int block_size, float scale, void* output, int dtype, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+    if (!query || !k_cache || !v_cache || !k_scale || !v_scale || !context_lens || !block_tables || !output)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (fp8) requires KV cache, scales, context_lens, and block_tables");
+    if (!is_index_dtype(context_lens_dtype) || !is_index_dtype(block_tables_dtype))
+        return fail(NVK_ERR_INVALID_ARGUMENT, "context_lens and block_tables must be int32 or int64");
+    if (batch < 0 || max_blocks <= 0 || num_cache_blocks <= 0 || num_heads <= 0 || num_kv_heads <= 0 ||
+        head_dim <= 0 || block_size <= 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "attention dimensions must be positive");
+    if (num_heads % num_kv_heads != 0)
+        return fail(NVK_ERR_INVALID_ARGUMENT, "num_heads must be divisible by num_kv_heads");
+    if (batch == 0) return NVK_OK;
+    DecodeInt8Args a{{query, k_cache, v_cache, index_array(context_lens, context_lens_dtype),
+                      index_array(block_tables, block_tables_dtype), output, batch, max_blocks, num_cache_blocks,
+                      num_heads, num_kv_heads, head_dim, block_size, scale, dtype, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream)},
+                     k_scale, v_scale, true};
+    if (!decode_int8_mma_supported(a))
+        return fail(NVK_ERR_UNSUPPORTED, "decode attention (fp8): F16 / BF16 queries, head_dim 128, at most 8 query heads per KV head, "
+                                         "block_size a multiple of 16 (and a workspace beyond 8 cache blocks per sequence)");
+    if (workspace != nullptr) {
+        const size_t need = decode_mma_workspace_bytes(batch, num_heads, num_kv_heads, head_dim, max_blocks, block_size);
+        if (workspace_bytes < need)
+            return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (fp8): workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+        if (!aligned_to(workspace, 16)) return fail(NVK_ERR_INVALID_ARGUMENT, "decode attention (fp8): workspace must be 16-byte aligned");
+    }
+    return launch_decode_int8_mma(a);
+}
+
 int nvk_prefill_attention_varlen(const void* query, const void* key, const void* value, const void* k_cache,
                                  const void* v_cache, const void* cu_seqlens_q, int cu_seqlens_q_dtype,
                                  const void* cu_seqlens_k, int cu_seqlens_k_dtype, const void* block_tables,

@@ -66,9 +66,10 @@ struct DecodeArgs {
     void* workspace; size_t workspace_bytes;
     cudaStream_t stream;
 };
-struct DecodeInt8Args {          // int8 caches with one fp16 scale per (cache row, KV head)
+struct DecodeInt8Args {          // 8-bit caches (int8, or e4m3 when fp8 is set) with one fp16 scale per (cache row, KV head)
     DecodeArgs base;
     const void* k_scale; const void* v_scale;
+    bool fp8 = false;
 };
 struct PrefillArgs {
     const void* q; const void* k; const void* v;          // dense keys (k, v) or paged (caches)
@@ -120,6 +121,9 @@ int launch_store_int8(const void* key, const void* value, void* k_cache, void* v
 int launch_rowwise_decode_int8(const DecodeInt8Args& a);
 bool decode_int8_mma_supported(const DecodeInt8Args& a);
 int launch_decode_int8_mma(const DecodeInt8Args& a);
+int launch_store_fp8(const void* key, const void* value, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                     const int32_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim, int64_t cache_rows,
+                     int dtype, cudaStream_t stream);
 bool prefill_mma_supported(const PrefillArgs& a);
 int launch_prefill_mma(const PrefillArgs& a);
 // tcgen05 / TMEM / TMA path (F16/BF16, head_dim 128, paged block_size % 128 == 0).

@@ -143,6 +143,33 @@ def decode_attention_paged_int8(q, k_cache, v_cache, k_scale, v_scale, context_l
     return out
 
 
+def store_kvcache_fp8(key, value, k_cache, v_cache, k_scale, v_scale, slot_mapping) -> None:
+    """In place: ``k_cache`` / ``v_cache`` uint8 (e4m3 bytes) [rows, Hkv, D], ``k_scale`` / ``v_scale`` float32 [rows, Hkv]
+    holding the fp16-rounded scales."""
+    key = _f32(key); value = _f32(value); sm = _i32(slot_mapping)
+    for a, dt in ((k_cache, np.uint8), (v_cache, np.uint8), (k_scale, np.float32), (v_scale, np.float32)):
+        assert a.dtype == dt and a.flags["C_CONTIGUOUS"]
+    tokens, hkv, d = key.shape
+    lib().oracle_store_kvcache_fp8(_p(key), _p(value), _p(k_cache), _p(v_cache), _p(k_scale), _p(v_scale), _p(sm),
+                                   ctypes.c_int64(tokens), ctypes.c_int(hkv), ctypes.c_int(d),
+                                   ctypes.c_int64(k_cache.size // (hkv * d)))
+
+
+def decode_attention_paged_fp8(q, k_cache, v_cache, k_scale, v_scale, context_lens, block_tables, num_kv_heads,
+                               head_dim, block_size, scale) -> np.ndarray:
+    q = _f32(q); cl = _i32(context_lens); bt = _i32(block_tables)
+    k_scale = _f32(k_scale); v_scale = _f32(v_scale)
+    assert k_cache.dtype == np.uint8 and v_cache.dtype == np.uint8
+    k_cache = np.ascontiguousarray(k_cache); v_cache = np.ascontiguousarray(v_cache)
+    batch, num_heads = q.shape[0], q.shape[1]
+    out = np.empty_like(q)
+    lib().oracle_decode_attention_paged_fp8(
+        _p(q), _p(k_cache), _p(v_cache), _p(k_scale), _p(v_scale), _p(cl), _p(bt), ctypes.c_int64(batch),
+        ctypes.c_int64(bt.shape[1]), ctypes.c_int(num_heads), ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
+        ctypes.c_int(block_size), ctypes.c_float(scale), _p(out))
+    return out
+
+
 def prefill_attention_dense(q, k, v, cu_seqlens_q, cu_seqlens_k, num_kv_heads, head_dim, scale,
                             threads: int | None = None) -> np.ndarray:
     q = _f32(q); k = _f32(k); v = _f32(v)

@@ -478,3 +478,87 @@ void oracle_fused_split_norm_rope_store(const float* qkv, const int32_t* positio
     free(normed);
     free(rotated);
 }
+
+/* ---- fp8 (e4m3) KV cache ---------------------------------------------------------------
+ * The reference has no fp8 cache (its survey of next steps names one after the int8 cache); the format here follows its
+ * int8 cache (src/kernels/kvcache.cu:222-296, src/kernels/attention.cu:746-842) with the value range of the type:
+ * one fp16 scale per (cache row, KV head) = max(absmax / 448, 1e-10), elements = e4m3(x * 448 / max(absmax, 1e-10)),
+ * round to nearest even, saturating at +-448.  No reference output exists for it: parity for this format is this
+ * restatement against the CUDA kernels, and the decode against the 16-bit cache. */
+static uint8_t e4m3_from_float(float x) {
+    if (x != x) return 0x7f;
+    const uint8_t sign = signbit(x) ? 0x80 : 0x00;
+    const float a = fabsf(x);
+    if (a >= 448.0f) return sign | 0x7e;
+    if (a < 0.015625f) return sign | (uint8_t)rintf(a * 512.0f);        /* subnormals: units of 2^-9; 8 = the smallest normal */
+    int ex;
+    (void)frexpf(a, &ex);                                               /* a = f * 2^ex, f in [0.5, 1) */
+    int e = ex - 1;
+    int m = (int)rintf((ldexpf(a, -e) - 1.0f) * 8.0f);                  /* exact before the rint */
+    if (m == 8) { m = 0; ++e; }
+    if (e > 8 || (e == 8 && m > 6)) return sign | 0x7e;
+    return sign | (uint8_t)(((e + 7) << 3) | m);
+}
+static float e4m3_to_float(uint8_t v) {
+    const int e = (v >> 3) & 15, m = v & 7;
+    float a;
+    if (e == 15 && m == 7) return NAN;
+    if (e == 0) a = ldexpf((float)m, -9);
+    else a = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+    return (v & 0x80) ? -a : a;
+}
+
+void oracle_store_kvcache_fp8(const float* key, const float* value, uint8_t* k_cache, uint8_t* v_cache,
+                              float* k_scale, float* v_scale, const int32_t* slot_mapping, int64_t num_tokens,
+                              int num_kv_heads, int head_dim, int64_t cache_rows) {
+    for (int64_t token = 0; token < num_tokens; ++token) {
+        const int64_t slot = slot_mapping[token];
+        if (slot < 0 || slot >= cache_rows) continue;
+        for (int which = 0; which < 2; ++which) {
+            for (int h = 0; h < num_kv_heads; ++h) {
+                const float* src = (which ? value : key) + (token * num_kv_heads + h) * head_dim;
+                uint8_t* dst = (which ? v_cache : k_cache) + (slot * num_kv_heads + h) * head_dim;
+                float absmax = 0.0f;
+                for (int d = 0; d < head_dim; ++d) absmax = fmaxf(absmax, fabsf(src[d]));
+                const float scale = fmaxf(absmax / 448.0f, 1.0e-10f);
+                const float inv_scale = 448.0f / fmaxf(absmax, 1.0e-10f);
+                for (int d = 0; d < head_dim; ++d) dst[d] = e4m3_from_float(src[d] * inv_scale);
+                (which ? v_scale : k_scale)[slot * num_kv_heads + h] = oracle_round_fp16(scale);
+            }
+        }
+    }
+}
+
+void oracle_decode_attention_paged_fp8(const float* query, const uint8_t* k_cache, const uint8_t* v_cache,
+                                       const float* k_scale, const float* v_scale, const int32_t* context_lens,
+                                       const int32_t* block_tables, int64_t batch, int64_t max_blocks, int num_heads,
+                                       int num_kv_heads, int head_dim, int block_size, float scale, float* output) {
+    for (int64_t seq = 0; seq < batch; ++seq) {
+        for (int head = 0; head < num_heads; ++head) {
+            float* out = output + (seq * num_heads + head) * head_dim;
+            const int32_t k_len = context_lens[seq];
+            if (k_len <= 0) { for (int d = 0; d < head_dim; ++d) out[d] = 0.0f; continue; }
+            const int kv_head = head * num_kv_heads / num_heads;
+            const float* q = query + (seq * num_heads + head) * head_dim;
+            float running_max = -INFINITY, running_sum = 0.0f;
+            for (int d = 0; d < head_dim; ++d) out[d] = 0.0f;
+            for (int32_t k = 0; k < k_len; ++k) {
+                const int64_t block = block_tables[seq * max_blocks + k / block_size];
+                const int64_t row = (block * block_size + k % block_size) * num_kv_heads + kv_head;
+                const uint8_t* k_ptr = k_cache + row * head_dim;
+                const uint8_t* v_ptr = v_cache + row * head_dim;
+                float dot = 0.0f;
+                for (int d = 0; d < head_dim; ++d) dot += q[d] * (e4m3_to_float(k_ptr[d]) * k_scale[row]);
+                const float qk = dot * scale;
+                const float old_max = running_max;
+                running_max = fmaxf(running_max, qk);
+                const float correction = expf(old_max - running_max);
+                const float e = expf(qk - running_max);
+                running_sum = running_sum * correction + e;
+                for (int d = 0; d < head_dim; ++d) out[d] = out[d] * correction + e * (e4m3_to_float(v_ptr[d]) * v_scale[row]);
+            }
+            const float inv = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
+            for (int d = 0; d < head_dim; ++d) out[d] *= inv;
+        }
+    }
+}

@@ -50,6 +50,17 @@ void oracle_decode_attention_paged_int8(const float* query, const int8_t* k_cach
                                         int64_t batch, int64_t max_blocks, int num_heads, int num_kv_heads,
                                         int head_dim, int block_size, float scale, float* output, int num_threads);
 
+/* fp8 (e4m3) KV cache: no counterpart in the reference (PARITY UNPINNED for this format); the layout and the arithmetic
+ * follow its int8 cache with the range of the type: scale = max(absmax / 448, 1e-10) as fp16 per (cache row, KV head),
+ * elements = e4m3(x * 448 / max(absmax, 1e-10)), round to nearest even, saturating. */
+void oracle_store_kvcache_fp8(const float* key, const float* value, uint8_t* k_cache, uint8_t* v_cache,
+                              float* k_scale, float* v_scale, const int32_t* slot_mapping, int64_t num_tokens,
+                              int num_kv_heads, int head_dim, int64_t cache_rows);
+void oracle_decode_attention_paged_fp8(const float* query, const uint8_t* k_cache, const uint8_t* v_cache,
+                                       const float* k_scale, const float* v_scale, const int32_t* context_lens,
+                                       const int32_t* block_tables, int64_t batch, int64_t max_blocks, int num_heads,
+                                       int num_kv_heads, int head_dim, int block_size, float scale, float* output);
+
 /* src/kernels/attention.cu:114-202 (prefill_dense_attention_kernel) with
  * locate_prefill_sequence (:27-54).  cu_seqlens_* may both be NULL: one sequence. */
 void oracle_prefill_attention_dense(const float* query, const float* key, const float* value,

@@ -26,7 +26,7 @@ def tiny(em, layers=2):
                             max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=2048)
 
 
-@pytest.mark.parametrize("kv_dtype,tol,linears", [("bf16", 0.03, "cublas"), ("int8", 0.06, "cublas"), ("bf16", 0.03, "fused")])
+@pytest.mark.parametrize("kv_dtype,tol,linears", [("bf16", 0.03, "cublas"), ("int8", 0.06, "cublas"), ("fp8", 0.12, "cublas"), ("bf16", 0.03, "fused")])
 def test_decode_continues_a_sequence_like_a_longer_prefill(mods, kv_dtype, tol, linears):
     torch, nvk, em, es, _ = mods
     dev = torch.device("cuda:0")
